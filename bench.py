@@ -1,0 +1,335 @@
+#!/usr/bin/env python
+"""Benchmark of the batched complex training step (forward + Wirtinger backward + SGD update).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload "mixer_dp4096": the token-mixing stack (8 x [FourierTrans(1024) -> Hadamard ->
+CGelu -> Linear(1024->1024) -> Residual] -> Linear(1024->10) -> CrossEntropy) at GLOBAL batch 4096,
+split evenly over the N ranks (strong scaling), weight gradients all-reduced over NCCL before the
+update.  One step = one pass over one synthetic batch.  Prints ONE JSON line on rank 0.
+
+`value`  : samples/s with the batch already resident in HBM.
+`e2e`    : samples/s through the public API with pinned HOST buffers: H2D of the batch and D2H of
+           the per-sample losses inside the timed region.
+`--impl reference`: the reference's own CPU implementation (oracle/_ref, built from the reference
+           sources) on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from cnet_b200 import configs  # noqa: E402
+
+WORKLOADS = {
+    # name: (builder, kwargs, global batch, input kind)
+    "mixer_dp4096": (configs.build_mixer, dict(n=1024, blocks=8, m=10), 4096, "normal"),
+    "mixer_b512": (configs.build_mixer, dict(n=1024, blocks=8, m=10), 512, "normal"),
+    "classifier_b64": (configs.build_classifier, dict(n=784, m=10), 64, "image"),
+    "embed_lm_b1024": (configs.build_embed_lm, dict(tokens=64, vocab=8192, dim=256, hidden=2048), 1024, None),
+}
+LR = 0.01
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def _gemm_flops(spec_kw, batch, name):
+    """Algorithmic real flops of the complex GEMMs of one step: 8*M*N*K each."""
+    if name.startswith("mixer"):
+        n, blocks, m = spec_kw["n"], spec_kw["blocks"], spec_kw["m"]
+        return blocks * 3 * 8 * batch * n * n + 3 * 8 * batch * n * m
+    if name.startswith("classifier"):
+        return 3 * 8 * batch * spec_kw["n"] * spec_kw["m"]
+    d = spec_kw["tokens"] * spec_kw["dim"]
+    return 3 * 8 * batch * (d * spec_kw["hidden"] + spec_kw["hidden"] * spec_kw["vocab"])
+
+
+class _Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.p is None:
+            return out
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(", ") for r in open(self.f.name).read().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.f.name)
+        if not rows:
+            return out
+        sm = sorted(float(r[1]) for r in rows)
+        out["sm_mhz"] = sm[len(sm) // 2]
+        out["sm_max_mhz"] = float(rows[0][2])
+        out["samples"] = len(rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for k, nme in enumerate(names):
+            if any(r[5 + k].strip() == "Active" for r in rows):
+                out["reasons"].append(nme)
+        return out
+
+
+def run_reference(args):
+    """The reference's own CPU path on the host cores, on a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref
+    builder, kw, gbatch, kind = WORKLOADS[args.workload]
+    if not ref.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libcnet_ref.so is not built"}))
+        return
+    net = ref.RefNet()
+    spec = builder(net, **kw)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    cores = ref.max_threads()
+    # size the per-step sample so K+W steps end within a few minutes
+    data, labels = configs.make_batch(spec, 2, 0, 0, kind)
+    t0 = time.perf_counter()
+    _run_ref(net, spec, data, labels)
+    per_sample = (time.perf_counter() - t0) / 2
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    sample = int(max(1, min(gbatch, budget / max(per_sample, 1e-6))))
+    times = []
+    for s in range(args.warmup + args.steps):
+        data, labels = configs.make_batch(spec, sample, 0, s, kind)
+        t0 = time.perf_counter()
+        _run_ref(net, spec, data, labels)
+        net.update(LR, sample)
+        if s >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = sample * len(times) / total
+    line = {
+        "impl": "reference", "metric": "train samples/sec (fwd+bwd+update)", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / len(times) * (gbatch / sample), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": gbatch, **kw},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "reference",
+                         "sample": "%d of %d samples per step, per-sample loop of the reference trainer "
+                                   "(setInput, forward, loss, backward(label)) + update; ms_per_step scaled to the full batch"
+                                   % (sample, gbatch)},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def _run_ref(net, spec, data, labels):
+    if spec.tokens:
+        net.run_batch(spec.main, tokens=data, labels=labels, record=False)
+    else:
+        net.run_batch(spec.main, x=data, labels=labels, record=False)
+
+
+def cpu_baseline(workload, seconds=15.0):
+    from oracle import ref
+    if not ref.available():
+        return None
+    builder, kw, gbatch, kind = WORKLOADS[workload]
+    net = ref.RefNet()
+    spec = builder(net, **kw)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    data, labels = configs.make_batch(spec, 2, 0, 0, kind)
+    t0 = time.perf_counter()
+    _run_ref(net, spec, data, labels)
+    per = (time.perf_counter() - t0) / 2
+    k = int(max(2, min(gbatch, seconds / max(per, 1e-6))))
+    data, labels = configs.make_batch(spec, k, 0, 1, kind)
+    t0 = time.perf_counter()
+    _run_ref(net, spec, data, labels)
+    net.update(LR, k)
+    dt = time.perf_counter() - t0
+    return {"value": k / dt, "unit": "samples/s", "cores": ref.max_threads(), "kind": "reference",
+            "sample": "%d of %d samples of the workload through the unmodified reference CPU path "
+                      "(oracle/_ref), %.1f s" % (k, gbatch, dt)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from cnet_b200 import lib as cl
+    from cnet_b200.dp import DataParallelTrainer
+    from cnet_b200.ops import Context
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    builder, kw, gbatch, kind = WORKLOADS[args.workload]
+    assert gbatch % world == 0
+    B = gbatch // world
+    lib = cl.load()
+
+    trainer = DataParallelTrainer(builder, kw, global_batch=gbatch, lr=LR, device=local, seed=0)
+    spec = trainer.spec
+    # pinned host staging of this rank's shard (the e2e leg copies from here every step)
+    data, labels = configs.make_batch(spec, gbatch, 0, 0, kind)
+    lo, hi = rank * B, (rank + 1) * B
+    if spec.tokens:
+        host_in = (torch.from_numpy(data[lo:hi].copy()).pin_memory(),)
+        h2d = host_in[0].numel() * 4
+    else:
+        host_in = (torch.from_numpy(data[0][lo:hi].copy()).pin_memory(),
+                   torch.from_numpy(data[1][lo:hi].copy()).pin_memory())
+        h2d = 2 * host_in[0].numel() * 4
+    host_labels = torch.from_numpy(labels[lo:hi].copy()).pin_memory()
+    h2d += host_labels.numel() * 4
+    host_loss = torch.empty(B, dtype=torch.float32).pin_memory()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    trainer.upload(host_in, host_labels)
+    for _ in range(max(3, args.warmup)):
+        trainer.step_resident()
+    clocks = _Clocks(local) if rank == 0 else None
+    l0 = lib.cnb_launch_count()
+    ms = timed(trainer.step_resident, args.steps)
+    launches = lib.cnb_launch_count() - l0
+    clk = clocks.stop() if clocks else None
+    trainer.net.sync()
+
+    def e2e_step():
+        trainer.upload(host_in, host_labels)
+        trainer.step_resident()
+        trainer.net.losses_into(host_loss, B)      # D2H of the step's per-sample losses (synchronises)
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    loss_mean = float(host_loss.mean())
+
+    # dominant kernel: the complex GEMM of the Linear layers, timed alone on this rank's shape
+    roof = None
+    if rank == 0:
+        peaks = _peaks()
+        ctx = Context(device=local, arena_bytes=1 << 30)
+        n = kw.get("n", 1024)
+        if args.workload.startswith("embed"):
+            n_in, n_out = kw["tokens"] * kw["dim"], kw["hidden"]
+        elif args.workload.startswith("classifier"):
+            n_in, n_out = kw["n"], kw["m"]
+        else:
+            n_in, n_out = n, n
+        x = tuple(torch.randn(B, n_in, device="cuda") for _ in range(2))
+        w = tuple(torch.randn(n_out, n_in, device="cuda") * n_in ** -0.5 for _ in range(2))
+        for _ in range(3):
+            ctx.linear_fwd(x, w)
+        reps = 10
+        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+        tot = 0.0
+        for _ in range(reps):
+            flush.zero_()                               # L2 flush between timed launches
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ctx.linear_fwd(x, w)
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        engine = ctx.last_gemm_engine()
+        dur_ms = tot / reps
+        flops = 8.0 * B * n_in * n_out
+        achieved = flops / (dur_ms * 1e-3) / 1e12
+        # 3xTF32: three TF32 MMAs per real product; dense TF32 runs at half the bf16 rate
+        peak = peaks["bf16"] / 6.0 if engine == 1 else peaks["bf16"] / 6.0
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "kernel": "cgemm_tc_3xtf32" if engine == 1 else "cgemm_simt_fp32",
+                "shape": [B, n_out, n_in], "ms_per_launch": dur_ms,
+                "peak_note": "measured bf16 burst %.1f TFLOP/s / 6 (TF32 = bf16/2, three MMAs per product), %s"
+                             % (peaks["bf16"], peaks["source"]),
+                "step_gemm_tflops": _gemm_flops(kw, gbatch, args.workload) / (ms / args.steps * 1e-3) / 1e12}
+        ctx.close()
+
+    if rank == 0:
+        per_step = ms / args.steps
+        line = {
+            "metric": "train samples/sec (fwd+bwd+update)", "value": gbatch / (per_step * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "global_batch": gbatch, "per_gpu_batch": B, **kw,
+                       "parallelism": "dp%d" % world, "lr": LR,
+                       "l2": "per-step working set (activations + gradients, > 1 GB) exceeds the 126 MB L2"},
+            "e2e": {"value": gbatch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * 4},
+            "gpu_launches": int(launches), "clocks": clk, "roofline": roof, "loss": loss_mean,
+            "cpu_baseline": cpu_baseline(args.workload) if world == 1 and not args.no_cpu_baseline else None,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mixer_dp4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,72 @@
+// Shared declarations of the device library: context, error plumbing, launch helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <map>
+#include <string>
+
+#include "../../include/cnet_b200.h"
+
+struct cnb_twiddle {
+    float* re = nullptr;   // [N, N] planes, F[p,q] = N^-1/2 e^{-2 pi i pq/N}
+    float* im = nullptr;
+};
+
+struct cnb_ctx {
+    int device = 0;
+    int sm_count = 148;
+    char* base = nullptr;
+    size_t size = 0;
+    size_t used = 0;
+    bool owns = false;
+    int* d_status = nullptr;          // device error word (bounded waits report here)
+    float* scratch = nullptr;         // column-reduction partials and GEMM operand staging
+    size_t scratch_bytes = 0;
+    std::map<int, cnb_twiddle> twiddles;
+    void* gemm_ws = nullptr;          // tensor-core GEMM workspace (see cgemm_tc.cu)
+};
+
+namespace cnb {
+
+int set_error(int code, const char* fmt, ...);
+void count_launch();
+int ensure_scratch(cnb_ctx* ctx, size_t bytes, float** out);
+extern thread_local int g_last_engine;
+
+inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// fp32 SIMT complex GEMM on generic strides:
+//   D[m,n] (+)= sum_k A(m,k) * (conjB ? conj(B(n,k)) : B(n,k)) (+ R[m,n])
+//   A(m,k) = a[m*sam + k*sak], B(n,k) = b[n*sbn + k*sbk], D/R row-major with ld = N.
+int cgemm_simt(cnb_ctx* ctx, const float* a_re, const float* a_im, long sam, long sak,
+               const float* b_re, const float* b_im, long sbn, long sbk, int conjB,
+               const float* r_re, const float* r_im, float* d_re, float* d_im,
+               int M, int N, int K, int accumulate, cudaStream_t st);
+
+// tcgen05 3xTF32 complex GEMM, K-major operands only:
+//   D[m,n] (+)= sum_k A[m,k] * (conjB ? conj(B[n,k]) : B[n,k]) (+ R[m,n]); A [M,K], B [N,K] row-major.
+// Returns CNB_ERR_UNSUPPORTED when the shape does not fit its tiles.
+int cgemm_tc_nt(cnb_ctx* ctx, const float* a_re, const float* a_im,
+                const float* b_re, const float* b_im, int conjB,
+                const float* r_re, const float* r_im, float* d_re, float* d_im,
+                int M, int N, int K, int accumulate, cudaStream_t st);
+bool cgemm_tc_shape_ok(int M, int N, int K);
+void cgemm_tc_release(cnb_ctx* ctx);
+
+// [R, C] -> [C, R] transpose of a re/im plane pair (operand staging for the K-major GEMM).
+int transpose_planes(const float* s_re, const float* s_im, float* d_re, float* d_im,
+                     int R, int C, cudaStream_t st);
+
+}  // namespace cnb
+
+#define CNB_CHECK_ARG(cond, ...) \
+    do { if (!(cond)) return cnb::set_error(CNB_ERR_ARG, __VA_ARGS__); } while (0)
+
+#define CNB_CUDA(call) \
+    do { cudaError_t e_ = (call); \
+         if (e_ != cudaSuccess) return cnb::set_error(CNB_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); } while (0)
+
+#define CNB_LAUNCH_CHECK(name) \
+    do { cnb::count_launch(); cudaError_t e_ = cudaGetLastError(); \
+         if (e_ != cudaSuccess) return cnb::set_error(CNB_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e_)); } while (0)

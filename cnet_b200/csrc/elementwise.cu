@@ -1,0 +1,429 @@
+// HBM-bound element-wise layers of the complex training step: Hadamard, CGelu (and the
+// fused pair), Residual, gradient pass-through, SGD update, plane transposes.
+// All kernels stream each plane once with 16-byte accesses where the row length allows
+// it (W = 4), else scalar (W = 1); grids are sized in multiples of the SM count.
+#include "common.cuh"
+
+namespace {
+
+constexpr float kGeluK = 0.7978845608028654f;   // sqrtf(2/pi)
+constexpr float kGeluC = 0.044715f;
+
+template <int W> struct Pack { float v[W]; };
+
+template <int W> __device__ __forceinline__ Pack<W> ld(const float* p, size_t i) {
+    Pack<W> r;
+    if constexpr (W == 4) {
+        float4 t = *reinterpret_cast<const float4*>(p + i);
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else {
+        r.v[0] = p[i];
+    }
+    return r;
+}
+
+template <int W> __device__ __forceinline__ void st(float* p, size_t i, const Pack<W>& r) {
+    if constexpr (W == 4) {
+        *reinterpret_cast<float4*>(p + i) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    } else {
+        p[i] = r.v[0];
+    }
+}
+
+__device__ __forceinline__ float gelu_f(float x) {
+    float t = tanhf(kGeluK * (x + kGeluC * x * x * x));
+    return 0.5f * x * (1.0f + t);
+}
+
+// gelu'(x) with sech^2 = 1 - tanh^2
+__device__ __forceinline__ float dgelu_f(float x) {
+    float x2 = x * x;
+    float t = tanhf(kGeluK * (x + kGeluC * x * x2));
+    float sech2 = 1.0f - t * t;
+    return 0.5f * (1.0f + t) + 0.5f * x * sech2 * kGeluK * (1.0f + 3.0f * kGeluC * x2);
+}
+
+inline int grid_for(size_t work_items, int threads, int sm_count) {
+    size_t blocks = (work_items + threads - 1) / threads;
+    size_t cap = (size_t) sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int) blocks;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ------------------------------------------------------------------ Hadamard
+template <int W>
+__global__ void hadamard_fwd_k(const float* __restrict__ ur, const float* __restrict__ ui,
+                               const float* __restrict__ vr, const float* __restrict__ vi, int v_batched,
+                               float* __restrict__ yr, float* __restrict__ yi, size_t total, int N) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        size_t j = v_batched ? i : i % N;
+        Pack<W> a = ld<W>(ur, i), b = ld<W>(ui, i), c = ld<W>(vr, j), d = ld<W>(vi, j), r, s;
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            r.v[k] = a.v[k] * c.v[k] - b.v[k] * d.v[k];
+            s.v[k] = a.v[k] * d.v[k] + b.v[k] * c.v[k];
+        }
+        st<W>(yr, i, r); st<W>(yi, i, s);
+    }
+}
+
+// dst (+)= g o conj(o): the element-wise half of the Hadamard backward
+template <int W>
+__global__ void hadamard_bwd_elem_k(const float* __restrict__ gr, const float* __restrict__ gi,
+                                    const float* __restrict__ orr, const float* __restrict__ oi, int o_batched,
+                                    float* __restrict__ dr, float* __restrict__ di, int accumulate,
+                                    size_t total, int N) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        size_t j = o_batched ? i : i % N;
+        Pack<W> a = ld<W>(gr, i), b = ld<W>(gi, i), c = ld<W>(orr, j), d = ld<W>(oi, j), r, s;
+        if (accumulate) { r = ld<W>(dr, i); s = ld<W>(di, i); }
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            float pr = a.v[k] * c.v[k] + b.v[k] * d.v[k];     // (a+ib)(c-id)
+            float pi = b.v[k] * c.v[k] - a.v[k] * d.v[k];
+            r.v[k] = accumulate ? r.v[k] + pr : pr;
+            s.v[k] = accumulate ? s.v[k] + pi : pi;
+        }
+        st<W>(dr, i, r); st<W>(di, i, s);
+    }
+}
+
+// Column reduction stage 1: partial[c][n] = sum over the rows of chunk c of t[b,n] o conj(u[b,n]).
+// MODE 0: t = g (plain Hadamard).  MODE 1: t = CGelu backward of g at a (fused pair); then
+// du (+)= t o conj(h) is written in the same pass.
+// Block = (32 columns) x (8 row lanes); a warp reads 128 contiguous bytes of each plane per row.
+template <int MODE>
+__global__ void colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
+                                   const float* __restrict__ ar, const float* __restrict__ ai,
+                                   const float* __restrict__ ur, const float* __restrict__ ui,
+                                   const float* __restrict__ hr, const float* __restrict__ hi,
+                                   float* __restrict__ dur, float* __restrict__ dui, int accumulate_u,
+                                   float* __restrict__ pr, float* __restrict__ pi,
+                                   int B, int N, int rows_per_chunk) {
+    __shared__ float sr[8][33], si[8][33];
+    int col = blockIdx.x * 32 + threadIdx.x;
+    int r0 = blockIdx.y * rows_per_chunk;
+    int r1 = min(B, r0 + rows_per_chunk);
+    float accr = 0.f, acci = 0.f;
+    if (col < N) {
+        float hre = 0.f, him = 0.f;
+        if (MODE == 1) { hre = hr[col]; him = hi[col]; }
+        for (int b = r0 + threadIdx.y; b < r1; b += 8) {
+            size_t i = (size_t) b * N + col;
+            float tr = gr[i], ti = gi[i];
+            if (MODE == 1) {
+                float dx = 0.5f * dgelu_f(ar[i]), dy = 0.5f * dgelu_f(ai[i]);
+                float p = dx + dy, m = dx - dy;
+                // dz* = conj(g*) (dx-dy) + g* (dx+dy)
+                float nr = tr * m + tr * p, ni = -ti * m + ti * p;
+                tr = nr; ti = ni;
+                if (dur) {
+                    float vr = tr * hre + ti * him, vi = ti * hre - tr * him;   // t o conj(h)
+                    if (accumulate_u) { vr += dur[i]; vi += dui[i]; }
+                    dur[i] = vr; dui[i] = vi;
+                }
+            }
+            float xr = ur[i], xi = ui[i];
+            accr += tr * xr + ti * xi;        // t o conj(u)
+            acci += ti * xr - tr * xi;
+        }
+    }
+    sr[threadIdx.y][threadIdx.x] = accr;
+    si[threadIdx.y][threadIdx.x] = acci;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < N) {
+#pragma unroll
+        for (int k = 1; k < 8; ++k) { accr += sr[k][threadIdx.x]; acci += si[k][threadIdx.x]; }
+        pr[(size_t) blockIdx.y * N + col] = accr;
+        pi[(size_t) blockIdx.y * N + col] = acci;
+    }
+}
+
+// Stage 2: dv[n] (+)= sum_c partial[c][n] in a fixed order (deterministic).
+__global__ void colreduce_stage2_k(const float* __restrict__ pr, const float* __restrict__ pi,
+                                   float* __restrict__ dr, float* __restrict__ di, int accumulate,
+                                   int chunks, int N) {
+    int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= N) return;
+    float a = 0.f, b = 0.f;
+    for (int c = 0; c < chunks; ++c) { a += pr[(size_t) c * N + col]; b += pi[(size_t) c * N + col]; }
+    if (accumulate) { a += dr[col]; b += di[col]; }
+    dr[col] = a; di[col] = b;
+}
+
+// --------------------------------------------------------------------- CGelu
+template <int W>
+__global__ void gelu_fwd_k(const float* __restrict__ zr, const float* __restrict__ zi,
+                           float* __restrict__ yr, float* __restrict__ yi, size_t total) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        Pack<W> a = ld<W>(zr, i), b = ld<W>(zi, i);
+#pragma unroll
+        for (int k = 0; k < W; ++k) { a.v[k] = gelu_f(a.v[k]); b.v[k] = gelu_f(b.v[k]); }
+        st<W>(yr, i, a); st<W>(yi, i, b);
+    }
+}
+
+template <int W>
+__global__ void gelu_bwd_k(const float* __restrict__ gr, const float* __restrict__ gi,
+                           const float* __restrict__ zr, const float* __restrict__ zi,
+                           float* __restrict__ dr, float* __restrict__ di, int accumulate, size_t total) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        Pack<W> a = ld<W>(gr, i), b = ld<W>(gi, i), x = ld<W>(zr, i), y = ld<W>(zi, i), r, s;
+        if (accumulate) { r = ld<W>(dr, i); s = ld<W>(di, i); }
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            float dx = 0.5f * dgelu_f(x.v[k]), dy = 0.5f * dgelu_f(y.v[k]);
+            float p = dx + dy, m = dx - dy;
+            float nr = a.v[k] * m + a.v[k] * p;       // Re(conj(g) m + g p)
+            float ni = -b.v[k] * m + b.v[k] * p;      // Im
+            r.v[k] = accumulate ? r.v[k] + nr : nr;
+            s.v[k] = accumulate ? s.v[k] + ni : ni;
+        }
+        st<W>(dr, i, r); st<W>(di, i, s);
+    }
+}
+
+template <int W>
+__global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* __restrict__ ui,
+                                    const float* __restrict__ hr, const float* __restrict__ hi,
+                                    float* __restrict__ ar, float* __restrict__ ai,
+                                    float* __restrict__ yr, float* __restrict__ yi, size_t total, int N) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        size_t j = i % N;
+        Pack<W> a = ld<W>(ur, i), b = ld<W>(ui, i), c = ld<W>(hr, j), d = ld<W>(hi, j), r, s;
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            r.v[k] = a.v[k] * c.v[k] - b.v[k] * d.v[k];
+            s.v[k] = a.v[k] * d.v[k] + b.v[k] * c.v[k];
+        }
+        st<W>(ar, i, r); st<W>(ai, i, s);
+#pragma unroll
+        for (int k = 0; k < W; ++k) { r.v[k] = gelu_f(r.v[k]); s.v[k] = gelu_f(s.v[k]); }
+        st<W>(yr, i, r); st<W>(yi, i, s);
+    }
+}
+
+// ------------------------------------------------- Residual, pass-through, SGD
+template <int W>
+__global__ void add2_k(const float* __restrict__ ur, const float* __restrict__ ui,
+                       const float* __restrict__ vr, const float* __restrict__ vi,
+                       float* __restrict__ yr, float* __restrict__ yi, size_t total) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        Pack<W> a = ld<W>(ur, i), b = ld<W>(ui, i), c = ld<W>(vr, i), d = ld<W>(vi, i);
+#pragma unroll
+        for (int k = 0; k < W; ++k) { a.v[k] += c.v[k]; b.v[k] += d.v[k]; }
+        st<W>(yr, i, a); st<W>(yi, i, b);
+    }
+}
+
+template <int W>
+__global__ void sgd_k(float* __restrict__ w, float* __restrict__ g, size_t total, float lr, int zero_grad) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        Pack<W> a = ld<W>(w, i), b = ld<W>(g, i);
+#pragma unroll
+        for (int k = 0; k < W; ++k) { a.v[k] -= lr * b.v[k]; b.v[k] = 0.f; }
+        st<W>(w, i, a);
+        if (zero_grad) st<W>(g, i, b);
+    }
+}
+
+// 32x32 smem-tiled transpose of a plane pair: dst[c][r] = src[r][c]
+__global__ void transpose_k(const float* __restrict__ sr, const float* __restrict__ si,
+                            float* __restrict__ dr, float* __restrict__ di, int R, int C) {
+    __shared__ float tr[32][33], ti[32][33];
+    int c = blockIdx.x * 32 + threadIdx.x;
+    for (int k = threadIdx.y; k < 32; k += 8) {
+        int r = blockIdx.y * 32 + k;
+        if (r < R && c < C) {
+            tr[k][threadIdx.x] = sr[(size_t) r * C + c];
+            ti[k][threadIdx.x] = si[(size_t) r * C + c];
+        }
+    }
+    __syncthreads();
+    int r = blockIdx.y * 32 + threadIdx.x;
+    for (int k = threadIdx.y; k < 32; k += 8) {
+        int cc = blockIdx.x * 32 + k;
+        if (r < R && cc < C) {
+            dr[(size_t) cc * R + r] = tr[threadIdx.x][k];
+            di[(size_t) cc * R + r] = ti[threadIdx.x][k];
+        }
+    }
+}
+
+template <typename... P> bool all_aligned(P... p) { return (aligned16(p) && ...); }
+
+int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, const float* ar, const float* ai,
+                     const float* ur, const float* ui, const float* hr, const float* hi,
+                     float* dur, float* dui, int acc_u, float* dvr, float* dvi, int acc_v,
+                     int B, int N, cudaStream_t stm) {
+    int col_blocks = (N + 31) / 32;
+    int chunks = (ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
+    int max_chunks = (B + 7) / 8;
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks > 128) chunks = 128;
+    if (chunks < 1) chunks = 1;
+    int rows = (B + chunks - 1) / chunks;
+    chunks = (B + rows - 1) / rows;
+    float* part = nullptr;
+    int rc = cnb::ensure_scratch(ctx, (size_t) chunks * N * 2 * sizeof(float), &part);
+    if (rc != CNB_OK) return rc;
+    float* pr = part;
+    float* pi = part + (size_t) chunks * N;
+    dim3 grid(col_blocks, chunks), block(32, 8);
+    if (mode == 0)
+        colreduce_stage1_k<0><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows);
+    else
+        colreduce_stage1_k<1><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows);
+    CNB_LAUNCH_CHECK("colreduce_stage1");
+    colreduce_stage2_k<<<(N + 255) / 256, 256, 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
+    CNB_LAUNCH_CHECK("colreduce_stage2");
+    return CNB_OK;
+}
+
+}  // namespace
+
+namespace cnb {
+int transpose_planes(const float* s_re, const float* s_im, float* d_re, float* d_im, int R, int C,
+                     cudaStream_t st) {
+    dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+    transpose_k<<<grid, block, 0, st>>>(s_re, s_im, d_re, d_im, R, C);
+    CNB_LAUNCH_CHECK("transpose");
+    return CNB_OK;
+}
+}  // namespace cnb
+
+#define DISPATCH_W(vec_ok, KERNEL, total, ...)                                              \
+    do {                                                                                    \
+        if (vec_ok) {                                                                       \
+            KERNEL<4><<<grid_for(((total) + 3) / 4, 256, ctx->sm_count), 256, 0, stm>>>(__VA_ARGS__); \
+        } else {                                                                            \
+            KERNEL<1><<<grid_for((total), 256, ctx->sm_count), 256, 0, stm>>>(__VA_ARGS__); \
+        }                                                                                   \
+        CNB_LAUNCH_CHECK(#KERNEL);                                                          \
+    } while (0)
+
+extern "C" {
+
+int cnb_hadamard_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im, const float* v_re, const float* v_im,
+                     int v_batched, float* y_re, float* y_im, int B, int N, void* stream) {
+    CNB_CHECK_ARG(ctx && u_re && u_im && v_re && v_im && y_re && y_im, "cnb_hadamard_fwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_fwd: B=%d N=%d", B, N);
+    cudaStream_t stm = cnb::S(stream);
+    size_t total = (size_t) B * N;
+    bool vec = (N % 4 == 0) && all_aligned(u_re, u_im, v_re, v_im, y_re, y_im);
+    DISPATCH_W(vec, hadamard_fwd_k, total, u_re, u_im, v_re, v_im, v_batched, y_re, y_im, total, N);
+    return CNB_OK;
+}
+
+int cnb_hadamard_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* u_re, const float* u_im,
+                     const float* v_re, const float* v_im, int v_batched, float* du_re, float* du_im,
+                     int accumulate_u, float* dv_re, float* dv_im, int accumulate_v, int B, int N, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && u_re && u_im && v_re && v_im, "cnb_hadamard_bwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_bwd: B=%d N=%d", B, N);
+    CNB_CHECK_ARG((du_re == nullptr) == (du_im == nullptr) && (dv_re == nullptr) == (dv_im == nullptr),
+                  "cnb_hadamard_bwd: re/im output planes must be given in pairs");
+    cudaStream_t stm = cnb::S(stream);
+    size_t total = (size_t) B * N;
+    if (du_re) {
+        bool vec = (N % 4 == 0) && all_aligned(g_re, g_im, v_re, v_im, du_re, du_im);
+        DISPATCH_W(vec, hadamard_bwd_elem_k, total, g_re, g_im, v_re, v_im, v_batched, du_re, du_im, accumulate_u,
+                   total, N);
+    }
+    if (dv_re) {
+        if (v_batched) {
+            bool vec = (N % 4 == 0) && all_aligned(g_re, g_im, u_re, u_im, dv_re, dv_im);
+            DISPATCH_W(vec, hadamard_bwd_elem_k, total, g_re, g_im, u_re, u_im, 1, dv_re, dv_im, accumulate_v,
+                       total, N);
+        } else {
+            return colreduce_launch(ctx, 0, g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr, nullptr,
+                                    nullptr, 0, dv_re, dv_im, accumulate_v, B, N, stm);
+        }
+    }
+    return CNB_OK;
+}
+
+int cnb_gelu_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float* y_re, float* y_im, size_t n,
+                 void* stream) {
+    CNB_CHECK_ARG(ctx && z_re && z_im && y_re && y_im && n > 0, "cnb_gelu_fwd: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    bool vec = (n % 4 == 0) && all_aligned(z_re, z_im, y_re, y_im);
+    DISPATCH_W(vec, gelu_fwd_k, n, z_re, z_im, y_re, y_im, n);
+    return CNB_OK;
+}
+
+int cnb_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* z_re, const float* z_im,
+                 float* dz_re, float* dz_im, size_t n, int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && z_re && z_im && dz_re && dz_im && n > 0, "cnb_gelu_bwd: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    bool vec = (n % 4 == 0) && all_aligned(g_re, g_im, z_re, z_im, dz_re, dz_im);
+    DISPATCH_W(vec, gelu_bwd_k, n, g_re, g_im, z_re, z_im, dz_re, dz_im, accumulate, n);
+    return CNB_OK;
+}
+
+int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im, const float* h_re,
+                          const float* h_im, float* a_re, float* a_im, float* y_re, float* y_im, int B, int N,
+                          void* stream) {
+    CNB_CHECK_ARG(ctx && u_re && u_im && h_re && h_im && a_re && a_im && y_re && y_im,
+                  "cnb_hadamard_gelu_fwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_gelu_fwd: B=%d N=%d", B, N);
+    cudaStream_t stm = cnb::S(stream);
+    size_t total = (size_t) B * N;
+    bool vec = (N % 4 == 0) && all_aligned(u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im);
+    DISPATCH_W(vec, hadamard_gelu_fwd_k, total, u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im, total, N);
+    return CNB_OK;
+}
+
+int cnb_hadamard_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* a_re,
+                          const float* a_im, const float* u_re, const float* u_im, const float* h_re,
+                          const float* h_im, float* du_re, float* du_im, int accumulate_u, float* dh_re,
+                          float* dh_im, int accumulate_h, int B, int N, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && a_re && a_im && u_re && u_im && h_re && h_im && dh_re && dh_im,
+                  "cnb_hadamard_gelu_bwd: null pointer");
+    CNB_CHECK_ARG((du_re == nullptr) == (du_im == nullptr), "cnb_hadamard_gelu_bwd: du planes must be a pair");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_gelu_bwd: B=%d N=%d", B, N);
+    return colreduce_launch(ctx, 1, g_re, g_im, a_re, a_im, u_re, u_im, h_re, h_im, du_re, du_im, accumulate_u,
+                            dh_re, dh_im, accumulate_h, B, N, cnb::S(stream));
+}
+
+int cnb_residual_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im, const float* v_re, const float* v_im,
+                     float* y_re, float* y_im, size_t n, void* stream) {
+    CNB_CHECK_ARG(ctx && u_re && u_im && v_re && v_im && y_re && y_im && n > 0, "cnb_residual_fwd: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    bool vec = (n % 4 == 0) && all_aligned(u_re, u_im, v_re, v_im, y_re, y_im);
+    DISPATCH_W(vec, add2_k, n, u_re, u_im, v_re, v_im, y_re, y_im, n);
+    return CNB_OK;
+}
+
+int cnb_axpy(cnb_ctx* ctx, const float* src_re, const float* src_im, float* dst_re, float* dst_im, size_t n,
+             int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && src_re && src_im && dst_re && dst_im && n > 0, "cnb_axpy: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    if (!accumulate) {
+        CNB_CUDA(cudaMemcpyAsync(dst_re, src_re, n * sizeof(float), cudaMemcpyDeviceToDevice, stm));
+        CNB_CUDA(cudaMemcpyAsync(dst_im, src_im, n * sizeof(float), cudaMemcpyDeviceToDevice, stm));
+        return CNB_OK;
+    }
+    bool vec = (n % 4 == 0) && all_aligned(src_re, src_im, dst_re, dst_im);
+    DISPATCH_W(vec, add2_k, n, src_re, src_im, dst_re, dst_im, dst_re, dst_im, n);
+    return CNB_OK;
+}
+
+int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad, void* stream) {
+    CNB_CHECK_ARG(ctx && w && g && n > 0, "cnb_sgd_update: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    bool vec = (n % 4 == 0) && all_aligned(w, g);
+    DISPATCH_W(vec, sgd_k, n, w, g, n, lr, zero_grad);
+    return CNB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,142 @@
+// Complex Linear (forward, dX*, dW*) and FourierTrans as a complex GEMM against a
+// twiddle matrix: shape dispatch between the tcgen05 3xTF32 tiles and the fp32 SIMT tiles.
+#include <cmath>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+// F[p,q] = N^-1/2 e^{-2 pi i (pq mod N)/N}, angles reduced exactly in integers and evaluated
+// in double with sincospi; the matrix is symmetric.
+__global__ void twiddle_k(float* __restrict__ fr, float* __restrict__ fi, int N) {
+    size_t total = (size_t) N * N;
+    double scale = 1.0 / sqrt((double) N);
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t) gridDim.x * blockDim.x) {
+        long p = (long) (i / N), q = (long) (i % N);
+        long r = (p * q) % N;
+        double s, c;
+        sincospi(-2.0 * (double) r / (double) N, &s, &c);
+        fr[i] = (float) (c * scale);
+        fi[i] = (float) (s * scale);
+    }
+}
+
+int get_twiddle(cnb_ctx* ctx, int N, cudaStream_t st, cnb_twiddle* out) {
+    auto it = ctx->twiddles.find(N);
+    if (it != ctx->twiddles.end()) { *out = it->second; return CNB_OK; }
+    cnb_twiddle t;
+    void* p = nullptr;
+    int rc = cnb_alloc(ctx, (size_t) N * N * sizeof(float), &p);
+    if (rc != CNB_OK) return rc;
+    t.re = static_cast<float*>(p);
+    rc = cnb_alloc(ctx, (size_t) N * N * sizeof(float), &p);
+    if (rc != CNB_OK) return rc;
+    t.im = static_cast<float*>(p);
+    twiddle_k<<<ctx->sm_count * 4, 256, 0, st>>>(t.re, t.im, N);
+    CNB_LAUNCH_CHECK("twiddle");
+    ctx->twiddles[N] = t;
+    *out = t;
+    return CNB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cnb_linear_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, const float* w_re, const float* w_im,
+                   const float* res_re, const float* res_im, float* y_re, float* y_im, int B, int in, int out,
+                   void* stream) {
+    CNB_CHECK_ARG(ctx && x_re && x_im && w_re && w_im && y_re && y_im, "cnb_linear_fwd: null pointer");
+    CNB_CHECK_ARG((res_re == nullptr) == (res_im == nullptr), "cnb_linear_fwd: residual planes must be a pair");
+    CNB_CHECK_ARG(B > 0 && in > 0 && out > 0, "cnb_linear_fwd: B=%d in=%d out=%d", B, in, out);
+    cudaStream_t st = cnb::S(stream);
+    if (cnb::cgemm_tc_shape_ok(B, out, in)) {
+        cnb::g_last_engine = 1;
+        return cnb::cgemm_tc_nt(ctx, x_re, x_im, w_re, w_im, 0, res_re, res_im, y_re, y_im, B, out, in, 0, st);
+    }
+    cnb::g_last_engine = 2;
+    return cnb::cgemm_simt(ctx, x_re, x_im, in, 1, w_re, w_im, in, 1, 0, res_re, res_im, y_re, y_im, B, out, in,
+                           0, st);
+}
+
+int cnb_linear_bwd_x(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* w_re, const float* w_im,
+                     float* dx_re, float* dx_im, int B, int in, int out, int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && w_re && w_im && dx_re && dx_im, "cnb_linear_bwd_x: null pointer");
+    CNB_CHECK_ARG(B > 0 && in > 0 && out > 0, "cnb_linear_bwd_x: B=%d in=%d out=%d", B, in, out);
+    cudaStream_t st = cnb::S(stream);
+    // dX*[b,i] = sum_o G[b,o] conj(W[o,i]) : M = B, N = in, K = out; B-operand(n=i,k=o) = W[o,i]
+    if (cnb::cgemm_tc_shape_ok(B, in, out)) {
+        // stage W^T [in, out] so both operands are K-major
+        float* ws = nullptr;
+        int rc = cnb::ensure_scratch(ctx, (size_t) 2 * in * out * sizeof(float), &ws);
+        if (rc != CNB_OK) return rc;
+        float* wt_re = ws;
+        float* wt_im = ws + (size_t) in * out;
+        rc = cnb::transpose_planes(w_re, w_im, wt_re, wt_im, out, in, st);
+        if (rc != CNB_OK) return rc;
+        cnb::g_last_engine = 1;
+        return cnb::cgemm_tc_nt(ctx, g_re, g_im, wt_re, wt_im, 1, nullptr, nullptr, dx_re, dx_im, B, in, out,
+                                accumulate, st);
+    }
+    cnb::g_last_engine = 2;
+    return cnb::cgemm_simt(ctx, g_re, g_im, out, 1, w_re, w_im, 1, in, 1, nullptr, nullptr, dx_re, dx_im, B, in,
+                           out, accumulate, st);
+}
+
+int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* x_re, const float* x_im,
+                     float* dw_re, float* dw_im, int B, int in, int out, int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && x_re && x_im && dw_re && dw_im, "cnb_linear_bwd_w: null pointer");
+    CNB_CHECK_ARG(B > 0 && in > 0 && out > 0, "cnb_linear_bwd_w: B=%d in=%d out=%d", B, in, out);
+    cudaStream_t st = cnb::S(stream);
+    // dW*[o,i] = sum_b G[b,o] conj(X[b,i]) : M = out, N = in, K = B
+    if (cnb::cgemm_tc_shape_ok(out, in, B)) {
+        float* ws = nullptr;
+        size_t ng = (size_t) B * out, nx = (size_t) B * in;
+        int rc = cnb::ensure_scratch(ctx, 2 * (ng + nx) * sizeof(float), &ws);
+        if (rc != CNB_OK) return rc;
+        float *gt_re = ws, *gt_im = ws + ng, *xt_re = ws + 2 * ng, *xt_im = ws + 2 * ng + nx;
+        rc = cnb::transpose_planes(g_re, g_im, gt_re, gt_im, B, out, st);
+        if (rc != CNB_OK) return rc;
+        rc = cnb::transpose_planes(x_re, x_im, xt_re, xt_im, B, in, st);
+        if (rc != CNB_OK) return rc;
+        cnb::g_last_engine = 1;
+        return cnb::cgemm_tc_nt(ctx, gt_re, gt_im, xt_re, xt_im, 1, nullptr, nullptr, dw_re, dw_im, out, in, B,
+                                accumulate, st);
+    }
+    cnb::g_last_engine = 2;
+    return cnb::cgemm_simt(ctx, g_re, g_im, 1, out, x_re, x_im, 1, in, 1, nullptr, nullptr, dw_re, dw_im, out, in,
+                           B, accumulate, st);
+}
+
+int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, float* y_re, float* y_im, int B, int N,
+                void* stream) {
+    CNB_CHECK_ARG(ctx && x_re && x_im && y_re && y_im, "cnb_dft_fwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0 && N <= 16384, "cnb_dft_fwd: B=%d N=%d (N <= 16384)", B, N);
+    cnb_twiddle t;
+    int rc = get_twiddle(ctx, N, cnb::S(stream), &t);
+    if (rc != CNB_OK) return rc;
+    // Y = X F^T with F symmetric: the Linear forward with W = F
+    return cnb_linear_fwd(ctx, x_re, x_im, t.re, t.im, nullptr, nullptr, y_re, y_im, B, N, N, stream);
+}
+
+int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re, float* dx_im, int B, int N,
+                int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && dx_re && dx_im, "cnb_dft_bwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0 && N <= 16384, "cnb_dft_bwd: B=%d N=%d (N <= 16384)", B, N);
+    cudaStream_t st = cnb::S(stream);
+    cnb_twiddle t;
+    int rc = get_twiddle(ctx, N, st, &t);
+    if (rc != CNB_OK) return rc;
+    // dX* = G* conj(F); F symmetric, so F itself is the K-major [N(in), N(out)] operand: no staging copy
+    if (cnb::cgemm_tc_shape_ok(B, N, N)) {
+        cnb::g_last_engine = 1;
+        return cnb::cgemm_tc_nt(ctx, g_re, g_im, t.re, t.im, 1, nullptr, nullptr, dx_re, dx_im, B, N, N, accumulate,
+                                st);
+    }
+    cnb::g_last_engine = 2;
+    return cnb::cgemm_simt(ctx, g_re, g_im, N, 1, t.re, t.im, N, 1, 1, nullptr, nullptr, dx_re, dx_im, B, N, N,
+                           accumulate, st);
+}
+
+}  // extern "C"

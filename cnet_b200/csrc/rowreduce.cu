@@ -1,0 +1,134 @@
+// Row reductions of the complex training step: L2 normalisation (the reference's
+// "SoftMax") forward/backward and the fused CrossEntropy forward + backward seed.
+// One CTA per sample row; warp-shuffle tree + one shared-memory hop.  Rows are read once
+// for the reduction and once (from L2/L1) for the element-wise pass.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum over the CTA; result valid in every thread.  blockDim.x is a multiple of 32, <= 1024.
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+    v = warp_sum(v);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? smem[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+
+__global__ void softmax_fwd_k(const float* __restrict__ zr, const float* __restrict__ zi,
+                              float* __restrict__ yr, float* __restrict__ yi, float* __restrict__ inv_norm, int N) {
+    __shared__ float sm[32];
+    size_t base = (size_t) blockIdx.x * N;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float a = zr[base + i], b = zi[base + i];
+        s += a * a + b * b;
+    }
+    s = block_sum(s, sm);
+    float n = fmaxf(sqrtf(s), 1e-15f);
+    float inv = 1.0f / n;
+    if (threadIdx.x == 0) inv_norm[blockIdx.x] = inv;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        yr[base + i] = zr[base + i] * inv;
+        yi[base + i] = zi[base + i] * inv;
+    }
+}
+
+__global__ void softmax_bwd_k(const float* __restrict__ gr, const float* __restrict__ gi,
+                              const float* __restrict__ zr, const float* __restrict__ zi,
+                              const float* __restrict__ inv_norm, float* __restrict__ dr, float* __restrict__ di,
+                              int N, int accumulate) {
+    __shared__ float sm[32];
+    size_t base = (size_t) blockIdx.x * N;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x)   // Re(g* conj(z))
+        s += gr[base + i] * zr[base + i] + gi[base + i] * zi[base + i];
+    s = block_sum(s, sm);
+    float inv = inv_norm[blockIdx.x];
+    float c = s * inv * inv * inv;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float a = gr[base + i] * inv - zr[base + i] * c;
+        float b = gi[base + i] * inv - zi[base + i] * c;
+        if (accumulate) { a += dr[base + i]; b += di[base + i]; }
+        dr[base + i] = a; di[base + i] = b;
+    }
+}
+
+__global__ void crossent_k(const float* __restrict__ zr, const float* __restrict__ zi,
+                           const int32_t* __restrict__ labels, float* __restrict__ loss,
+                           float* __restrict__ dr, float* __restrict__ di, int M) {
+    __shared__ float sm[32];
+    size_t base = (size_t) blockIdx.x * M;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < M; i += blockDim.x) {
+        float a = zr[base + i], b = zi[base + i];
+        s += a * a + b * b;
+    }
+    s = block_sum(s, sm);
+    float S = fmaxf(s, 1e-15f);
+    int l = labels[blockIdx.x];
+    l = min(max(l, 0), M - 1);
+    float lr = zr[base + l], li = zi[base + l];
+    float m2 = lr * lr + li * li;
+    if (threadIdx.x == 0) loss[blockIdx.x] = -logf(fmaxf(m2 / S, 1e-15f));
+    if (dr == nullptr) return;
+    float m = fmaxf(m2, 1e-15f);
+    float cl = -(S - m) / (m * S), co = 1.0f / S;
+    for (int i = threadIdx.x; i < M; i += blockDim.x) {
+        float c = (i == l) ? cl : co;
+        dr[base + i] = zr[base + i] * c;
+        di[base + i] = zi[base + i] * c;
+    }
+}
+
+inline int threads_for(int n) {
+    int t = 32;
+    while (t < n / 4 && t < 512) t <<= 1;
+    return t;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cnb_softmax_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float* y_re, float* y_im,
+                    float* inv_norm, int B, int N, void* stream) {
+    CNB_CHECK_ARG(ctx && z_re && z_im && y_re && y_im && inv_norm, "cnb_softmax_fwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_softmax_fwd: B=%d N=%d", B, N);
+    softmax_fwd_k<<<B, threads_for(N), 0, cnb::S(stream)>>>(z_re, z_im, y_re, y_im, inv_norm, N);
+    CNB_LAUNCH_CHECK("softmax_fwd");
+    return CNB_OK;
+}
+
+int cnb_softmax_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* z_re, const float* z_im,
+                    const float* inv_norm, float* dz_re, float* dz_im, int B, int N, int accumulate,
+                    void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && z_re && z_im && inv_norm && dz_re && dz_im,
+                  "cnb_softmax_bwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_softmax_bwd: B=%d N=%d", B, N);
+    softmax_bwd_k<<<B, threads_for(N), 0, cnb::S(stream)>>>(g_re, g_im, z_re, z_im, inv_norm, dz_re, dz_im, N,
+                                                           accumulate);
+    CNB_LAUNCH_CHECK("softmax_bwd");
+    return CNB_OK;
+}
+
+int cnb_crossent_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im, const int32_t* labels, float* loss,
+                         float* dz_re, float* dz_im, int B, int M, void* stream) {
+    CNB_CHECK_ARG(ctx && z_re && z_im && labels && loss, "cnb_crossent_fwd_bwd: null pointer");
+    CNB_CHECK_ARG((dz_re == nullptr) == (dz_im == nullptr), "cnb_crossent_fwd_bwd: dz planes must be a pair");
+    CNB_CHECK_ARG(B > 0 && M > 0, "cnb_crossent_fwd_bwd: B=%d M=%d", B, M);
+    crossent_k<<<B, threads_for(M), 0, cnb::S(stream)>>>(z_re, z_im, labels, loss, dz_re, dz_im, M);
+    CNB_LAUNCH_CHECK("crossent");
+    return CNB_OK;
+}
+
+}  // extern "C"

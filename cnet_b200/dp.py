@@ -1,0 +1,98 @@
+"""Data-parallel training of a CNet: the only sharded path.
+
+The batch is split evenly over the ranks (one process per GPU); weights are replicated
+(identical seeded init); during the backward pass every finished bucket of the contiguous
+weight-gradient arena is summed over the ranks with an asynchronous all-reduce
+(torch.distributed: NCCL over NVLink on GPUs, gloo in the CPU tests) that overlaps the rest of
+the backward; the fused SGD update runs after the last bucket with lr / global_batch — the
+multi-GPU analogue of the reference's gpu_grad_from_clones + gpuUpdateInputs(l_rate / batch)
+(gpu/kernels.cpp:566-598, cnet.cpp:147).
+"""
+import numpy as np
+
+from . import configs
+
+
+def shard_bounds(global_batch, world, rank):
+    """Rows [lo, hi) of the global batch owned by `rank` (even split required)."""
+    if global_batch % world != 0:
+        raise ValueError("global batch %d is not divisible by %d ranks" % (global_batch, world))
+    per = global_batch // world
+    return rank * per, (rank + 1) * per
+
+
+class GradBucketReducer:
+    """Sums gradient buckets over the ranks as they complete; `finish()` waits for all of them.
+
+    Works on any torch tensor views (CUDA with NCCL, CPU with gloo).  With world size 1 it
+    does nothing.
+    """
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.group = group
+        self.works = []
+        self.buckets_seen = 0
+
+    def on_bucket(self, view):
+        self.buckets_seen += 1
+        if self.active:
+            self.works.append(self.dist.all_reduce(view, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self):
+        for w in self.works:
+            w.wait()
+        self.works = []
+
+
+class DataParallelTrainer:
+    def __init__(self, builder, builder_kwargs, global_batch, lr, device=0, seed=0, fuse=True):
+        import torch
+        import torch.distributed as dist
+        from .net import Net
+        self.torch = torch
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.global_batch = global_batch
+        self.lo, self.hi = shard_bounds(global_batch, self.world, self.rank)
+        self.local_batch = self.hi - self.lo
+        self.lr = lr
+        self.net = Net(device=device)
+        self.spec = builder(self.net, **builder_kwargs)
+        for uid, (re, im) in configs.init_weights(self.spec, seed).items():
+            self.net.set_values(uid, re, im)
+        self.net.allocate(self.local_batch, fuse=fuse)
+        self.reducer = GradBucketReducer()
+        if self.reducer.active:
+            arena = self.net.arena
+            base = arena.data_ptr()
+
+            def hook(ptr, count, bucket, n_buckets):
+                off = ptr - base
+                self.reducer.on_bucket(arena[off:off + 4 * count].view(torch.float32))
+                return 0
+            self.net.set_bucket_hook(hook)
+
+    def upload(self, host_in, host_labels):
+        """Copies this rank's shard (pinned host tensors or numpy arrays) to the device."""
+        if self.spec.tokens:
+            self.net.upload(tokens=host_in[0], labels=host_labels, batch=self.local_batch)
+        else:
+            self.net.upload(x=host_in, labels=host_labels, batch=self.local_batch)
+
+    def step_resident(self):
+        """forward + backward (+ overlapped gradient all-reduce) + update on the resident batch."""
+        self.net.forward()
+        self.net.backward()
+        self.reducer.finish()
+        self.net.update_inputs(self.lr / self.global_batch)
+
+    def step(self, host_in, host_labels):
+        self.upload(host_in, host_labels)
+        self.step_resident()
+        return self.net.losses(self.local_batch)
+
+    def shard(self, arr):
+        return np.ascontiguousarray(arr[self.lo:self.hi])

@@ -1,0 +1,97 @@
+// Flat C binding of the host facade (declared in include/cnet_b200_host.h).
+#include "../../include/cnet_b200_host.h"
+#include "cnet.h"
+
+using namespace cnet_b200;
+
+struct cnh_net {
+	CNet net;
+	std::string err;
+};
+
+namespace {
+int status(cnh_net* n) {
+	if (n->net.ok()) return 0;
+	n->err = n->net.error();
+	return CNB_ERR_ARG;
+}
+}  // namespace
+
+extern "C" {
+
+cnh_net* cnh_create(int device, size_t arena_bytes, void* ext_arena) {
+	cnh_net* n = new cnh_net();
+	n->net.setDevice(device, arena_bytes, ext_arena);
+	return n;
+}
+
+void cnh_destroy(cnh_net* n) { delete n; }
+
+int cnh_set_device(cnh_net* n, int device, size_t arena_bytes, void* ext_arena) {
+	n->net.setDevice(device, arena_bytes, ext_arena);
+	return 0;
+}
+
+const char* cnh_error(cnh_net* n) { return n ? n->net.error().c_str() : "null net"; }
+
+void cnh_clear_error(cnh_net* n) { n->net.clearError(); }
+
+int cnh_add(cnh_net* n, int type, int a, int b, int c, const int* prev, int nprev) {
+	CFunc* f = nullptr;
+	switch (type) {
+	case isInput:        f = new CInput(OutSize(a)); break;
+	case isEmbedding:    f = new CEmbedding(a, b, c); break;
+	case isFourier:      f = new FourierTrans(InSize(a)); break;
+	case isHadamard:     f = new Hadamard(InSize(a), InSize(a)); break;
+	case isGelu:         f = new CGelu(InSize(a)); break;
+	case isLinear:
+		if (a <= 0 || b % a != 0) return CNB_ERR_ARG;
+		f = new Linear(InSize(a), InSize(b));
+		break;
+	case isResidual:     f = new Residual(InSize(a)); break;
+	case isSoftMax:      f = new SoftMax(InSize(a)); break;
+	case isCrossEntropy: f = new CrossEntropy(InSize(a)); break;
+	default: return CNB_ERR_UNSUPPORTED;
+	}
+	int uid = n->net.add(f, std::vector<int>(prev, prev + nprev));
+	if (uid < 0) { delete f; return CNB_ERR_ARG; }
+	return uid;
+}
+
+int cnh_out_size(cnh_net* n, int uid) { CFunc* f = n->net[uid]; return f ? f->outSize() : CNB_ERR_ARG; }
+int cnh_init_inputs(cnh_net* n, uint64_t seed) { n->net.init_inputs(seed); return status(n); }
+int cnh_set_values(cnh_net* n, int uid, const float* re, const float* im, int len) {
+	n->net.setInputValues(uid, re, im, len); return status(n);
+}
+int cnh_get_values(cnh_net* n, int uid, float* re, float* im, int len) {
+	n->net.getInputValues(uid, re, im, len); return status(n);
+}
+int cnh_get_wgrad(cnh_net* n, int uid, float* re, float* im, int len) {
+	n->net.getInputGradients(uid, re, im, len); return status(n);
+}
+int cnh_set_stream(cnh_net* n, void* s) { n->net.setStream(s); return 0; }
+int cnh_set_fusion(cnh_net* n, int on) { n->net.setFusion(on != 0); return 0; }
+int cnh_set_bucket_hook(cnh_net* n, cnh_bucket_hook h, void* user) { n->net.setBucketHook(h, user); return 0; }
+size_t cnh_required_arena(cnh_net* n, int batch) { return n->net.requiredArenaBytes(batch); }
+int cnh_allocate(cnh_net* n, int batch) { n->net.allocateOnGpu(batch); return status(n); }
+int cnh_upload(cnh_net* n, const float* re, const float* im, const int32_t* tokens, const int32_t* labels, int batch) {
+	n->net.batchToGpu(re, im, tokens, labels, batch); return status(n);
+}
+int cnh_forward(cnh_net* n) { n->net.forward(); return status(n); }
+int cnh_backward(cnh_net* n) { n->net.backward(); return status(n); }
+int cnh_backward_label(cnh_net* n, int label) { n->net.backward(label); return status(n); }
+int cnh_update(cnh_net* n, float lr) { n->net.updateInputs(lr); return status(n); }
+int cnh_get_losses(cnh_net* n, float* out, int cnt) { n->net.getLosses(out, cnt); return status(n); }
+int cnh_sync(cnh_net* n) { n->net.sync(); return status(n); }
+int cnh_read_output(cnh_net* n, int uid, int what, float* re, float* im) {
+	n->net.readOutput(uid, what, re, im); return status(n);
+}
+int cnh_grad_arena(cnh_net* n, void** p, size_t* count, int* nb) {
+	*p = n->net.gradArena(count);
+	if (nb) *nb = n->net.noBuckets();
+	return 0;
+}
+int cnh_weight_arena(cnh_net* n, void** p, size_t* count) { *p = n->net.weightArena(count); return 0; }
+void* cnh_context(cnh_net* n) { return n->net.context(); }
+
+}  // extern "C"

@@ -1,0 +1,766 @@
+// Host orchestration of the batched complex training step: graph bookkeeping, device
+// tensor planning in the arena, layer -> C-ABI kernel calls, fusion planning, gradient
+// buckets for data parallelism.  See cnet.h for the contract and its reference citations.
+#include "cnet.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <iostream>
+
+namespace cnet_b200 {
+
+namespace {
+
+inline size_t pad64(size_t n) { return (n + 63) & ~size_t(63); }   // floats -> 256-byte multiples
+
+// splitmix64: deterministic host generator for init_inputs
+struct SplitMix {
+	uint64_t s;
+	explicit SplitMix(uint64_t seed) : s(seed) {}
+	uint64_t next() {
+		uint64_t z = (s += 0x9E3779B97F4A7C15ull);
+		z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+		z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+		return z ^ (z >> 31);
+	}
+	double uniform() { return (next() >> 11) * (1.0 / 9007199254740992.0); }
+};
+
+}  // namespace
+
+// ------------------------------------------------------------------ batches
+void InputBatch::add(const std::vector<std::complex<float> >& sample, int label) {
+	for (auto c : sample) { real_data_.push_back(c.real()); imag_data_.push_back(c.imag()); }
+	while (real_data_.size() < (size_t) (1 + current_pos_) * sample_dim_) {
+		real_data_.push_back(0.f); imag_data_.push_back(0.f);
+	}
+	labels_.push_back(label);
+	current_pos_++;
+}
+
+void InputBatch::assign(const float* re, const float* im, const int* labels, int batch) {
+	batch_size_ = batch;
+	size_t n = (size_t) batch * sample_dim_;
+	real_data_.assign(re, re + n);
+	imag_data_.assign(im, im + n);
+	labels_.assign(labels, labels + batch);
+	current_pos_ = batch;
+}
+
+void EmbeddingBatch::add(const std::vector<int>& sample, int label) {
+	token_.insert(token_.end(), sample.begin(), sample.end());
+	while (token_.size() < (size_t) (1 + current_pos_) * sample_dim_) token_.push_back(NO_TOKEN);
+	labels_.push_back(label);
+	current_pos_++;
+}
+
+void EmbeddingBatch::assign(const int* tokens, const int* labels, int batch) {
+	batch_size_ = batch;
+	token_.assign(tokens, tokens + (size_t) batch * sample_dim_);
+	labels_.assign(labels, labels + batch);
+	current_pos_ = batch;
+}
+
+// -------------------------------------------------------------------- CFunc
+cnb_ctx* CFunc::ctx() const { return net_ ? net_->ctx_ : nullptr; }
+void* CFunc::stream() const { return net_ ? net_->stream_ : nullptr; }
+int CFunc::batch() const { return net_ ? net_->cur_batch_ : 0; }
+
+void CFunc::check(int status) {
+	if (status != CNB_OK && net_) net_->fail(status, getName());
+}
+
+int CFunc::accumulate_into(CFunc* p) {
+	if (!p->batched_) return 1;                 // weight gradients accumulate until updateInputs
+	int acc = p->grad_written_ ? 1 : 0;
+	p->grad_written_ = true;
+	return acc;
+}
+
+void CFunc::addOutput(CFunc* next, int offset) {
+	next_func_.push_back(next);
+	offset_.push_back(offset);
+	if (next->depth_ <= depth_) next->depth_ = depth_ + 1;
+}
+
+void CFunc::updateInput(float lr) {
+	if (!is_input_ || !out_.dz_star_real_ || batched_) return;
+	check(cnb_sgd_update(ctx(), out_.real_, out_.dz_star_real_, out_.count(), lr, 1, stream()));
+	check(cnb_sgd_update(ctx(), out_.imag_, out_.dz_star_imag_, out_.count(), lr, 1, stream()));
+}
+
+void CFunc::init_inputs(uint64_t seed) {
+	SplitMix r(seed);
+	host_re_.resize(out_size_);
+	host_im_.resize(out_size_);
+	for (int i = 0; i < out_size_; ++i) {
+		float re = (float) r.uniform() - 0.5f;
+		host_re_[i] = re / out_size_;
+		host_im_[i] = std::sqrt(1 - re * re) / out_size_;
+	}
+}
+
+// --------------------------------------------------------------- CEmbedding
+size_t CEmbedding::extraBytes(int batch) const {
+	return (((size_t) batch * no_out_tokens_ * sizeof(int32_t)) + 255) & ~size_t(255);
+}
+
+void CEmbedding::bindExtra(char* mem, int) { tokens_ = reinterpret_cast<int32_t*>(mem); }
+
+void CEmbedding::forward() {
+	check(cnb_embed_fwd(ctx(), table_.real_, table_.imag_, tokens_, out_.real_, out_.imag_, batch(),
+			no_out_tokens_, embedding_dim_, no_embeddings_, stream()));
+}
+
+void CEmbedding::backward() {
+	if (!grad_written_) return;                 // no consumer produced a gradient
+	check(cnb_embed_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, tokens_, table_.dz_star_real_,
+			table_.dz_star_imag_, batch(), no_out_tokens_, embedding_dim_, no_embeddings_, stream()));
+}
+
+void CEmbedding::updateInput(float lr) {
+	check(cnb_sgd_update(ctx(), table_.real_, table_.dz_star_real_, table_.count(), lr, 1, stream()));
+	check(cnb_sgd_update(ctx(), table_.imag_, table_.dz_star_imag_, table_.count(), lr, 1, stream()));
+}
+
+void CEmbedding::init_inputs(uint64_t seed) {
+	SplitMix r(seed);
+	host_re_.resize(in_size_);
+	host_im_.resize(in_size_);
+	float s = std::sqrt((float) embedding_dim_);
+	for (int i = 0; i < in_size_; ++i) {
+		float re = (float) r.uniform() - 0.5f;
+		host_re_[i] = re / s;
+		host_im_[i] = std::sqrt(1 - re * re) / s;
+	}
+}
+
+// ------------------------------------------------------------- FourierTrans
+void FourierTrans::forward() {
+	const Vars& x = in(0);
+	check(cnb_dft_fwd(ctx(), x.real_, x.imag_, out_.real_, out_.imag_, batch(), in_size_, stream()));
+}
+
+void FourierTrans::backward() {
+	CFunc* p = prev_func_[0];
+	int acc = accumulate_into(p);
+	check(cnb_dft_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, p->out_.dz_star_real_, p->out_.dz_star_imag_,
+			batch(), in_size_, acc, stream()));
+}
+
+// ----------------------------------------------------------------- Hadamard
+void Hadamard::forward() {
+	const Vars& u = in(0);
+	const Vars& v = in(1);
+	if (fused_gelu_) {
+		Vars& y = fused_gelu_->out_;
+		check(cnb_hadamard_gelu_fwd(ctx(), u.real_, u.imag_, v.real_, v.imag_, out_.real_, out_.imag_, y.real_,
+				y.imag_, batch(), out_size_, stream()));
+		return;
+	}
+	check(cnb_hadamard_fwd(ctx(), u.real_, u.imag_, v.real_, v.imag_, prev_func_[1]->batched_ ? 1 : 0, out_.real_,
+			out_.imag_, batch(), out_size_, stream()));
+}
+
+void Hadamard::backward() {
+	CFunc* pu = prev_func_[0];
+	CFunc* pv = prev_func_[1];
+	int acc_u = accumulate_into(pu), acc_v = accumulate_into(pv);
+	if (fused_gelu_) {
+		const Vars& g = fused_gelu_->out_;
+		check(cnb_hadamard_gelu_bwd(ctx(), g.dz_star_real_, g.dz_star_imag_, out_.real_, out_.imag_, pu->out_.real_,
+				pu->out_.imag_, pv->out_.real_, pv->out_.imag_, pu->out_.dz_star_real_, pu->out_.dz_star_imag_, acc_u,
+				pv->out_.dz_star_real_, pv->out_.dz_star_imag_, acc_v, batch(), out_size_, stream()));
+		return;
+	}
+	check(cnb_hadamard_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, pu->out_.real_, pu->out_.imag_,
+			pv->out_.real_, pv->out_.imag_, pv->batched_ ? 1 : 0, pu->out_.dz_star_real_, pu->out_.dz_star_imag_, acc_u,
+			pv->out_.dz_star_real_, pv->out_.dz_star_imag_, acc_v, batch(), out_size_, stream()));
+}
+
+// -------------------------------------------------------------------- CGelu
+void CGelu::forward() {
+	const Vars& z = in(0);
+	check(cnb_gelu_fwd(ctx(), z.real_, z.imag_, out_.real_, out_.imag_, (size_t) batch() * out_size_, stream()));
+}
+
+void CGelu::backward() {
+	CFunc* p = prev_func_[0];
+	int acc = accumulate_into(p);
+	check(cnb_gelu_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, p->out_.real_, p->out_.imag_,
+			p->out_.dz_star_real_, p->out_.dz_star_imag_, (size_t) batch() * out_size_, acc, stream()));
+}
+
+// ------------------------------------------------------------------- Linear
+Linear::Linear(Uid uid, InSize in1, InSize in2)
+	: CFunc(uid, InSize(in1.value() + in2.value()), OutSize(in2.value() / in1.value())), in1_len(in1.value()),
+	  in2_len(in2.value()) {}
+
+Linear::Linear(InSize in1, InSize in2)
+	: CFunc(InSize(in1.value() + in2.value()), OutSize(in2.value() / in1.value())), in1_len(in1.value()),
+	  in2_len(in2.value()) {}
+
+void Linear::forward() {
+	const Vars& x = in(0);
+	const Vars& w = in(1);
+	const float *rr = nullptr, *ri = nullptr;
+	if (fused_residual_) {
+		const Vars& r = fused_residual_->previous(residual_operand_)->output();
+		rr = r.real_; ri = r.imag_;
+	}
+	check(cnb_linear_fwd(ctx(), x.real_, x.imag_, w.real_, w.imag_, rr, ri, out_.real_, out_.imag_, batch(), in1_len,
+			out_size_, stream()));
+}
+
+void Linear::backward() {
+	CFunc* px = prev_func_[0];
+	CFunc* pw = prev_func_[1];
+	int acc_x = accumulate_into(px), acc_w = accumulate_into(pw);
+	check(cnb_linear_bwd_w(ctx(), out_.dz_star_real_, out_.dz_star_imag_, px->out_.real_, px->out_.imag_,
+			pw->out_.dz_star_real_, pw->out_.dz_star_imag_, batch(), in1_len, out_size_, acc_w, stream()));
+	check(cnb_linear_bwd_x(ctx(), out_.dz_star_real_, out_.dz_star_imag_, pw->out_.real_, pw->out_.imag_,
+			px->out_.dz_star_real_, px->out_.dz_star_imag_, batch(), in1_len, out_size_, acc_x, stream()));
+}
+
+// ----------------------------------------------------------------- Residual
+void Residual::forward() {
+	const Vars& u = in(0);
+	const Vars& v = in(1);
+	check(cnb_residual_fwd(ctx(), u.real_, u.imag_, v.real_, v.imag_, out_.real_, out_.imag_,
+			(size_t) batch() * out_size_, stream()));
+}
+
+void Residual::backward() {
+	for (int k = 0; k < 2; ++k) {
+		CFunc* p = prev_func_[k];
+		if (p->out_.dz_star_real_ == out_.dz_star_real_) {   // fused Linear shares this gradient tensor
+			p->grad_written_ = true;
+			continue;
+		}
+		int acc = accumulate_into(p);
+		check(cnb_axpy(ctx(), out_.dz_star_real_, out_.dz_star_imag_, p->out_.dz_star_real_, p->out_.dz_star_imag_,
+				(size_t) batch() * out_size_, acc, stream()));
+	}
+}
+
+// ------------------------------------------------------------------ SoftMax
+void SoftMax::forward() {
+	const Vars& z = in(0);
+	check(cnb_softmax_fwd(ctx(), z.real_, z.imag_, out_.real_, out_.imag_, inv_norm_, batch(), in_size_, stream()));
+}
+
+void SoftMax::backward() {
+	CFunc* p = prev_func_[0];
+	int acc = accumulate_into(p);
+	check(cnb_softmax_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, p->out_.real_, p->out_.imag_, inv_norm_,
+			p->out_.dz_star_real_, p->out_.dz_star_imag_, batch(), in_size_, acc, stream()));
+}
+
+// ------------------------------------------------------------- CrossEntropy
+void CrossEntropy::bindExtra(char* mem, int batch) {
+	loss_ = reinterpret_cast<float*>(mem);
+	labels_ = reinterpret_cast<int32_t*>(mem + (((size_t) batch * 4 + 255) & ~size_t(255)));
+}
+
+void CrossEntropy::forward() {
+	CFunc* p = prev_func_[0];
+	check(cnb_crossent_fwd_bwd(ctx(), p->out_.real_, p->out_.imag_, labels_, loss_, p->out_.dz_star_real_,
+			p->out_.dz_star_imag_, batch(), in_size_, stream()));
+}
+
+void CrossEntropy::backward(int label) {
+	std::vector<int32_t> l(batch(), label);
+	check(cnb_h2d(ctx(), labels_, l.data(), l.size() * sizeof(int32_t), stream()));
+	check(cnb_sync(ctx(), stream()));
+	forward();
+}
+
+float CrossEntropy::loss(int sample) {
+	float v = 0.f;
+	if (sample < 0 || sample >= batch()) return NAN;
+	check(cnb_d2h(ctx(), &v, loss_ + sample, sizeof(float), stream()));
+	return v;
+}
+
+// --------------------------------------------------------------------- CNet
+CNet::CNet() {}
+
+CNet::~CNet() {
+	for (auto f : func_list_) delete f;
+	if (ctx_) cnb_destroy(ctx_);
+}
+
+void CNet::setDevice(int device, size_t arena_bytes, void* ext_arena) {
+	device_ = device;
+	arena_bytes_ = arena_bytes;
+	ext_arena_ = ext_arena;
+}
+
+void CNet::fail(int status, const std::string& where) {
+	if (!ok_) return;                           // keep the first error
+	ok_ = false;
+	error_ = where + ": status " + std::to_string(status) + ": " + cnb_last_error();
+}
+
+int CNet::getType(CFunc* f) {
+	if (dynamic_cast<CInput*>(f)) return isInput;
+	if (dynamic_cast<Hadamard*>(f)) return isHadamard;
+	if (dynamic_cast<Linear*>(f)) return isLinear;
+	if (dynamic_cast<CEmbedding*>(f)) return isEmbedding;
+	if (dynamic_cast<FourierTrans*>(f)) return isFourier;
+	if (dynamic_cast<Residual*>(f)) return isResidual;
+	if (dynamic_cast<SoftMax*>(f)) return isSoftMax;
+	if (dynamic_cast<CrossEntropy*>(f)) return isCrossEntropy;
+	if (dynamic_cast<CGelu*>(f)) return isGelu;
+	return 0x7fffffff;
+}
+
+int CNet::add(CFunc* f) {
+	if (!f) return -1;
+	if (f->uid_ == 0) f->uid_ = ++next_uid_;
+	else next_uid_ = std::max(next_uid_, f->uid_);
+	if (map_.count(f->uid_)) { fail(CNB_ERR_ARG, "add: duplicate uid " + std::to_string(f->uid_)); return -1; }
+	f->type_ = getType(f);
+	f->net_ = this;
+	func_list_.push_back(f);
+	map_[f->uid_] = f;
+	if (f->is_input_) inputs_.push_back(f);
+	if (f->is_output_) outputs_.push_back(f);
+	return f->uid_;
+}
+
+int CNet::add(CFunc* f, const std::vector<int>& in_uids) {
+	if (!f) return -1;
+	// validate before registering, so a rejected function is still the caller's to delete
+	int total = 0;
+	for (int in_uid : in_uids) {
+		auto it = map_.find(in_uid);
+		if (it == map_.end()) { fail(CNB_ERR_ARG, "add: unknown producer uid " + std::to_string(in_uid)); return -1; }
+		total += it->second->out_size_;
+	}
+	if (total > f->in_size_) {
+		fail(CNB_ERR_ARG, f->getName() + ": producers give " + std::to_string(total) + " > input length " +
+				std::to_string(f->in_size_));
+		return -1;
+	}
+	int uid = add(f);
+	if (uid < 0) return uid;
+	int offset = 0;
+	for (int in_uid : in_uids) {
+		CFunc* p = map_[in_uid];
+		p->addOutput(f, offset);
+		offset += p->out_size_;
+		f->prev_func_.push_back(p);
+	}
+	return uid;
+}
+
+int CNet::add(CFunc* f, std::initializer_list<int> in_uids) { return add(f, std::vector<int>(in_uids)); }
+
+CFunc* CNet::findFirstOfType(int t) {
+	for (auto f : func_list_) if (f->type_ == t) return f;
+	return nullptr;
+}
+
+CFunc* CNet::findFirstInput() {
+	for (auto f : func_list_) if (dynamic_cast<InputFunc*>(f)) return f;
+	return nullptr;
+}
+
+CFunc* CNet::findFirstOutput() {
+	for (auto f : func_list_) if (dynamic_cast<OutputFunc*>(f)) return f;
+	return nullptr;
+}
+
+void CNet::init_inputs() { init_inputs(0x243F6A8885A308D3ull); }
+
+void CNet::init_inputs(uint64_t seed) {
+	uint64_t k = 0;
+	for (auto f : inputs_) {
+		f->init_inputs(seed + k++);
+		if (ctx_ && f != main_in_) setInputValues(f->uid_, f->host_re_.data(), f->host_im_.data(), (int) f->host_re_.size());
+	}
+}
+
+void CNet::init_exec_graph(bool print_status) {
+	if (!func_at_depth_.empty()) return;
+	int max_depth = 0;
+	for (auto f : func_list_) max_depth = std::max(max_depth, f->depth_);
+	func_at_depth_.assign(max_depth + 1, std::vector<CFunc*>());
+	for (auto f : func_list_) func_at_depth_[f->depth_].push_back(f);
+	if (print_status) {
+		for (size_t d = 0; d < func_at_depth_.size(); ++d) {
+			std::cout << "Depth " << d << ": ";
+			for (auto f : func_at_depth_[d]) std::cout << f->getName() << " " << f->sizeInBytes() << ", ";
+			std::cout << std::endl;
+		}
+	}
+}
+
+bool CNet::planFusion() {
+	for (auto f : func_list_) {
+		if (Hadamard* h = dynamic_cast<Hadamard*>(f)) {
+			if (h->prev_func_.size() == 2 && !h->prev_func_[1]->batched_ && h->prev_func_[0]->batched_ &&
+					h->next_func_.size() == 1) {
+				CGelu* g = dynamic_cast<CGelu*>(h->next_func_[0]);
+				if (g && g->prev_func_.size() == 1) { h->fused_gelu_ = g; g->fused_away_ = true; }
+			}
+		}
+		if (Linear* l = dynamic_cast<Linear*>(f)) {
+			if (l->next_func_.size() == 1) {
+				Residual* r = dynamic_cast<Residual*>(l->next_func_[0]);
+				if (r && r->prev_func_.size() == 2 && r->prev_func_[0] != r->prev_func_[1]) {
+					int mine = r->prev_func_[0] == l ? 0 : 1;
+					CFunc* other = r->prev_func_[1 - mine];
+					if (other->batched_ && !dynamic_cast<Linear*>(other)) {
+						l->fused_residual_ = r;
+						l->residual_operand_ = 1 - mine;
+						r->fused_away_ = true;
+					}
+				}
+			}
+		}
+	}
+	return true;
+}
+
+size_t CNet::requiredArenaBytes(int B) const {
+	size_t floats = 0, extra = 0, dft = 0;
+	size_t scratch = 64u << 20;
+	for (auto f : func_list_) {
+		bool weight = dynamic_cast<CInput*>(f) && f != func_list_.front();
+		if (weight) floats += 4 * pad64(f->out_size_);
+		else floats += 4 * pad64((size_t) B * f->out_size_);
+		if (CEmbedding* e = dynamic_cast<CEmbedding*>(f)) floats += 4 * pad64((size_t) e->inSize());
+		if (dynamic_cast<FourierTrans*>(f)) dft = std::max(dft, (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512);
+		if (Linear* l = dynamic_cast<Linear*>(f)) {
+			size_t ws = 2 * ((size_t) B * l->outSize() + (size_t) B * l->firstInputLength()) * 4;
+			ws = std::max(ws, (size_t) 2 * l->secondInputLength() * 4);
+			scratch = std::max(scratch, ws * 3);
+		}
+		extra += f->extraBytes(B) + 256;
+	}
+	return floats * sizeof(float) + extra + dft * 4 + scratch + (16u << 20);
+}
+
+bool CNet::allocateOnGpu(int B) {
+	if (ctx_) { fail(CNB_ERR_ARG, "allocateOnGpu: already allocated"); return false; }
+	if (B <= 0 || func_list_.empty()) { fail(CNB_ERR_ARG, "allocateOnGpu: empty net or batch"); return false; }
+	main_in_ = findFirstInput();
+	main_out_ = dynamic_cast<CrossEntropy*>(findFirstOutput());
+	if (!main_in_ || !main_out_) { fail(CNB_ERR_ARG, "allocateOnGpu: net needs an InputFunc and a CrossEntropy output"); return false; }
+	dynamic_cast<InputFunc*>(main_in_)->setIsMainInput(true);
+	main_out_->setIsMainOutput(true);
+	init_exec_graph();
+	// topology checks: what the batched kernels support
+	for (auto f : func_list_) {
+		f->batched_ = !(dynamic_cast<CInput*>(f) && f != main_in_);
+		size_t want = (f->type_ == isHadamard || f->type_ == isLinear || f->type_ == isResidual) ? 2
+				: (f->is_input_ ? 0 : 1);
+		if (f->prev_func_.size() != want) {
+			fail(CNB_ERR_UNSUPPORTED, f->getName() + ": expected " + std::to_string(want) + " producers");
+			return false;
+		}
+		if (!f->is_output_ && f->next_func_.empty()) {
+			fail(CNB_ERR_ARG, f->getName() + ": has no consumer and is not an output"); return false;
+		}
+	}
+	for (auto f : func_list_) {
+		if (Linear* l = dynamic_cast<Linear*>(f)) {
+			if (!l->prev_func_[0]->batched_ || l->prev_func_[1]->batched_ ||
+					l->prev_func_[0]->out_size_ != l->in1_len || l->prev_func_[1]->out_size_ != l->in2_len) {
+				fail(CNB_ERR_UNSUPPORTED, l->getName() + ": needs (batched x of in1, weight CInput of in2)"); return false;
+			}
+		} else if (f->type_ == isHadamard || f->type_ == isResidual) {
+			if (f->prev_func_[0]->out_size_ != f->out_size_ || f->prev_func_[1]->out_size_ != f->out_size_ ||
+					!f->prev_func_[0]->batched_ || (f->type_ == isResidual && !f->prev_func_[1]->batched_)) {
+				fail(CNB_ERR_UNSUPPORTED, f->getName() + ": operand shapes"); return false;
+			}
+		} else if (!f->is_input_) {
+			if (!f->prev_func_[0]->batched_ || f->prev_func_[0]->out_size_ != f->in_size_) {
+				fail(CNB_ERR_UNSUPPORTED, f->getName() + ": needs one batched producer of its input length"); return false;
+			}
+		}
+	}
+	if (fuse_) planFusion();
+	if (arena_bytes_ == 0) arena_bytes_ = requiredArenaBytes(B);
+	int rc = ext_arena_ ? cnb_create_external(device_, ext_arena_, arena_bytes_, &ctx_)
+			: cnb_create(device_, arena_bytes_, &ctx_);
+	if (rc != CNB_OK) { fail(rc, "allocateOnGpu"); ctx_ = nullptr; return false; }
+	batch_ = cur_batch_ = B;
+
+	// 1. weights: one block of value planes and one block of dz* planes with the same layout,
+	//    in backward order (reverse insertion), so gradient buckets complete front to back.
+	std::vector<CFunc*> weights;
+	for (auto it = func_list_.rbegin(); it != func_list_.rend(); ++it) {
+		CFunc* f = *it;
+		if (!f->batched_ || dynamic_cast<CEmbedding*>(f)) weights.push_back(f);
+	}
+	size_t total = 0;
+	for (auto f : weights) total += 2 * pad64(f->is_input_ && f->batched_ ? f->in_size_ : f->out_size_);
+	void* p = nullptr;
+	if (total) {
+		if ((rc = cnb_alloc(ctx_, total * sizeof(float), &p)) != CNB_OK) { fail(rc, "weights"); return false; }
+		weight_base_ = static_cast<float*>(p);
+		if ((rc = cnb_alloc(ctx_, total * sizeof(float), &p)) != CNB_OK) { fail(rc, "weight gradients"); return false; }
+		wgrad_base_ = static_cast<float*>(p);
+		wgrad_count_ = total;
+		cnb_memset0(ctx_, weight_base_, total * sizeof(float), stream_);
+		cnb_memset0(ctx_, wgrad_base_, total * sizeof(float), stream_);
+	}
+	size_t off = 0;
+	const size_t bucket_floats = 1u << 20;
+	size_t bucket_begin = 0, bucket_first = 0;
+	for (size_t k = 0; k < weights.size(); ++k) {
+		CFunc* f = weights[k];
+		CEmbedding* e = dynamic_cast<CEmbedding*>(f);
+		size_t len = e ? (size_t) f->in_size_ : (size_t) f->out_size_;
+		Vars v;
+		v.length_ = e ? e->embeddingDim() : (int) len;
+		v.rows_ = e ? e->noEmbeddings() : 1;
+		v.real_ = weight_base_ + off;            v.dz_star_real_ = wgrad_base_ + off;
+		v.imag_ = weight_base_ + off + pad64(len); v.dz_star_imag_ = wgrad_base_ + off + pad64(len);
+		off += 2 * pad64(len);
+		if (e) e->table_ = v; else f->out_ = v;
+		if (off - bucket_begin >= bucket_floats || k + 1 == weights.size()) {
+			// complete once the earliest-inserted consumer of any of its weights has run backward
+			CFunc* last = nullptr;
+			size_t best = func_list_.size();
+			for (size_t j = bucket_first; j <= k; ++j) {
+				CFunc* w = weights[j];
+				std::vector<CFunc*> users = w->next_func_;
+				if (dynamic_cast<CEmbedding*>(w)) users.assign(1, w);
+				for (auto u : users) {
+					size_t pos = std::find(func_list_.begin(), func_list_.end(), u) - func_list_.begin();
+					if (pos < best) { best = pos; last = u; }
+				}
+			}
+			buckets_.push_back(Bucket{bucket_begin, off - bucket_begin, last});
+			bucket_begin = off;
+			bucket_first = k + 1;
+		}
+	}
+	// 2. activations and their dL/dz* planes
+	for (auto f : func_list_) {
+		if (!f->batched_) continue;
+		size_t n = pad64((size_t) B * f->out_size_);
+		f->out_.length_ = f->out_size_;
+		f->out_.rows_ = B;
+		if (f->is_output_) continue;            // the loss has no output tensor
+		bool alias = false;
+		if (Linear* l = dynamic_cast<Linear*>(f)) alias = l->fused_residual_ != nullptr;
+		if (alias) continue;                    // bound to the Residual's tensors below
+		bool need_grad = !(dynamic_cast<Hadamard*>(f) && static_cast<Hadamard*>(f)->fused_gelu_);
+		size_t planes = need_grad ? 4 : 2;
+		if ((rc = cnb_alloc(ctx_, planes * n * sizeof(float), &p)) != CNB_OK) { fail(rc, f->getName()); return false; }
+		float* base = static_cast<float*>(p);
+		f->out_.real_ = base; f->out_.imag_ = base + n;
+		if (need_grad) { f->out_.dz_star_real_ = base + 2 * n; f->out_.dz_star_imag_ = base + 3 * n; }
+	}
+	for (auto f : func_list_) {
+		if (Linear* l = dynamic_cast<Linear*>(f)) {
+			if (l->fused_residual_) {
+				Vars v = l->fused_residual_->out_;
+				l->out_ = v;
+			}
+		}
+		size_t eb = f->extraBytes(B);
+		if (eb) {
+			if ((rc = cnb_alloc(ctx_, eb, &p)) != CNB_OK) { fail(rc, f->getName()); return false; }
+			f->bindExtra(static_cast<char*>(p), B);
+		}
+	}
+	// 3. upload the host copies of the weights
+	for (auto f : inputs_) {
+		if (f == main_in_ && !dynamic_cast<CEmbedding*>(f)) continue;
+		if (!f->host_re_.empty())
+			setInputValues(f->uid_, f->host_re_.data(), f->host_im_.data(), (int) f->host_re_.size());
+	}
+	cnb_sync(ctx_, stream_);
+	return ok_;
+}
+
+bool CNet::setInputValues(int uid, const float* re, const float* im, int len) {
+	auto it = map_.find(uid);
+	if (it == map_.end() || !it->second->is_input_) { fail(CNB_ERR_ARG, "setInputValues: uid is not an input"); return false; }
+	CFunc* f = it->second;
+	CEmbedding* e = dynamic_cast<CEmbedding*>(f);
+	int want = e ? f->in_size_ : f->out_size_;
+	if (len != want) { fail(CNB_ERR_ARG, f->getName() + ": setInputValues length"); return false; }
+	f->host_re_.assign(re, re + len);
+	f->host_im_.assign(im, im + len);
+	if (!ctx_) return true;
+	const Vars& v = e ? e->table_ : f->out_;
+	if (f->batched_ && !e) return true;         // data input: filled per batch
+	int rc = cnb_h2d(ctx_, v.real_, re, (size_t) len * sizeof(float), stream_);
+	if (rc == CNB_OK) rc = cnb_h2d(ctx_, v.imag_, im, (size_t) len * sizeof(float), stream_);
+	if (rc == CNB_OK) rc = cnb_sync(ctx_, stream_);
+	if (rc != CNB_OK) { fail(rc, "setInputValues"); return false; }
+	return true;
+}
+
+bool CNet::getInputValues(int uid, float* re, float* im, int len) {
+	auto it = map_.find(uid);
+	if (it == map_.end() || !it->second->is_input_ || !ctx_) { fail(CNB_ERR_ARG, "getInputValues: bad uid / not allocated"); return false; }
+	CFunc* f = it->second;
+	CEmbedding* e = dynamic_cast<CEmbedding*>(f);
+	const Vars& v = e ? e->table_ : f->out_;
+	if ((size_t) len != v.count()) { fail(CNB_ERR_ARG, "getInputValues: length"); return false; }
+	int rc = cnb_d2h(ctx_, re, v.real_, (size_t) len * sizeof(float), stream_);
+	if (rc == CNB_OK) rc = cnb_d2h(ctx_, im, v.imag_, (size_t) len * sizeof(float), stream_);
+	if (rc != CNB_OK) { fail(rc, "getInputValues"); return false; }
+	return true;
+}
+
+bool CNet::getInputGradients(int uid, float* re, float* im, int len) {
+	auto it = map_.find(uid);
+	if (it == map_.end() || !it->second->is_input_ || !ctx_) { fail(CNB_ERR_ARG, "getInputGradients: bad uid / not allocated"); return false; }
+	CFunc* f = it->second;
+	CEmbedding* e = dynamic_cast<CEmbedding*>(f);
+	const Vars& v = e ? e->table_ : f->out_;
+	if ((size_t) len != v.count() || !v.dz_star_real_) { fail(CNB_ERR_ARG, "getInputGradients: length"); return false; }
+	int rc = cnb_d2h(ctx_, re, v.dz_star_real_, (size_t) len * sizeof(float), stream_);
+	if (rc == CNB_OK) rc = cnb_d2h(ctx_, im, v.dz_star_imag_, (size_t) len * sizeof(float), stream_);
+	if (rc != CNB_OK) { fail(rc, "getInputGradients"); return false; }
+	return true;
+}
+
+bool CNet::getInputsFromGpu() {
+	for (auto f : inputs_) {
+		CEmbedding* e = dynamic_cast<CEmbedding*>(f);
+		if (f->batched_ && !e) continue;
+		size_t n = e ? e->table_.count() : f->out_.count();
+		f->host_re_.resize(n);
+		f->host_im_.resize(n);
+		if (!getInputValues(f->uid_, f->host_re_.data(), f->host_im_.data(), (int) n)) return false;
+	}
+	return true;
+}
+
+bool CNet::batchToGpu(const float* re, const float* im, const int* tokens, const int* labels, int B) {
+	if (!ctx_) { fail(CNB_ERR_ARG, "batchToGpu: allocateOnGpu first"); return false; }
+	if (B <= 0 || B > batch_) { fail(CNB_ERR_ARG, "batchToGpu: batch " + std::to_string(B) + " exceeds the allocated " + std::to_string(batch_)); return false; }
+	cur_batch_ = B;
+	int rc = CNB_OK;
+	if (CEmbedding* e = dynamic_cast<CEmbedding*>(main_in_)) {
+		if (!tokens) { fail(CNB_ERR_ARG, "batchToGpu: token ids expected"); return false; }
+		rc = cnb_h2d(ctx_, e->tokens_, tokens, (size_t) B * e->noOutTokens() * sizeof(int32_t), stream_);
+	} else {
+		if (!re || !im) { fail(CNB_ERR_ARG, "batchToGpu: re/im planes expected"); return false; }
+		size_t bytes = (size_t) B * main_in_->out_size_ * sizeof(float);
+		rc = cnb_h2d(ctx_, main_in_->out_.real_, re, bytes, stream_);
+		if (rc == CNB_OK) rc = cnb_h2d(ctx_, main_in_->out_.imag_, im, bytes, stream_);
+	}
+	if (rc == CNB_OK && labels) rc = cnb_h2d(ctx_, main_out_->labels_, labels, (size_t) B * sizeof(int32_t), stream_);
+	if (rc != CNB_OK) { fail(rc, "batchToGpu"); return false; }
+	return true;
+}
+
+void CNet::forward() {
+	if (!ctx_) { fail(CNB_ERR_ARG, "forward: allocateOnGpu first (there is no CPU path)"); return; }
+	for (auto f : func_list_) {
+		if (f->fused_away_) continue;
+		f->forward();
+		if (!ok_) return;
+	}
+}
+
+void CNet::backward() {
+	if (!ctx_) { fail(CNB_ERR_ARG, "backward: allocateOnGpu first (there is no CPU path)"); return; }
+	for (auto f : func_list_) f->grad_written_ = false;
+	main_out_->prev_func_[0]->grad_written_ = true;        // seeded by CrossEntropy::forward
+	size_t next_bucket = 0;
+	for (auto it = func_list_.rbegin(); it != func_list_.rend(); ++it) {
+		CFunc* f = *it;
+		if (!f->fused_away_ || dynamic_cast<Residual*>(f)) f->backward();
+		if (!ok_) return;
+		while (hook_ && next_bucket < buckets_.size() && buckets_[next_bucket].last_writer == f) {
+			const Bucket& b = buckets_[next_bucket];
+			int rc = hook_(hook_user_, wgrad_base_ + b.begin, b.count, (int) next_bucket, (int) buckets_.size());
+			if (rc != 0) { fail(CNB_ERR_DEVICE, "gradient bucket hook returned " + std::to_string(rc)); return; }
+			++next_bucket;
+		}
+	}
+	while (hook_ && next_bucket < buckets_.size()) {
+		const Bucket& b = buckets_[next_bucket];
+		int rc = hook_(hook_user_, wgrad_base_ + b.begin, b.count, (int) next_bucket, (int) buckets_.size());
+		if (rc != 0) { fail(CNB_ERR_DEVICE, "gradient bucket hook returned " + std::to_string(rc)); return; }
+		++next_bucket;
+	}
+}
+
+void CNet::backward(int label) {
+	if (!ctx_) { fail(CNB_ERR_ARG, "backward: allocateOnGpu first (there is no CPU path)"); return; }
+	main_out_->backward(label);
+	backward();
+}
+
+void CNet::updateInputs(float lr) {
+	if (!ctx_ || !wgrad_count_) return;
+	int rc = cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_);
+	if (rc != CNB_OK) fail(rc, "updateInputs");
+}
+
+bool CNet::gpuForward(InputFunc* inp, OutputFunc* outp, InputBatch& b) {
+	if (dynamic_cast<CFunc*>(inp) != main_in_ || dynamic_cast<CFunc*>(outp) != main_out_) {
+		fail(CNB_ERR_ARG, "gpuForward: not the main input / output"); return false;
+	}
+	if (!batchToGpu(b.realDataPtr(), b.imagDataPtr(), nullptr, b.labelsPtr(), b.size())) return false;
+	forward();
+	return ok_;
+}
+
+bool CNet::gpuForward(InputFunc* inp, OutputFunc* outp, EmbeddingBatch& b) {
+	if (dynamic_cast<CFunc*>(inp) != main_in_ || dynamic_cast<CFunc*>(outp) != main_out_) {
+		fail(CNB_ERR_ARG, "gpuForward: not the main input / output"); return false;
+	}
+	if (!batchToGpu(nullptr, nullptr, b.tokensPtr(), b.labelsPtr(), b.size())) return false;
+	forward();
+	return ok_;
+}
+
+bool CNet::gpuBackward() { backward(); return ok_; }
+
+bool CNet::getLosses(float* out, int n) {
+	if (!ctx_ || n > cur_batch_) { fail(CNB_ERR_ARG, "getLosses: bad count"); return false; }
+	int rc = cnb_d2h(ctx_, out, main_out_->loss_, (size_t) n * sizeof(float), stream_);
+	if (rc != CNB_OK) { fail(rc, "getLosses"); return false; }
+	return true;
+}
+
+float CNet::getLoss(OutputFunc* outp, Batch* batch) {
+	if (dynamic_cast<CFunc*>(outp) != main_out_) { fail(CNB_ERR_ARG, "getLoss: not the main output"); return NAN; }
+	std::vector<float> l(cur_batch_);
+	if (!getLosses(l.data(), cur_batch_)) return NAN;
+	double s = 0;
+	for (float v : l) s += v;
+	if (batch) batch->losses_ = l;
+	return (float) (s / cur_batch_);
+}
+
+bool CNet::sync() {
+	int rc = cnb_sync(ctx_, stream_);
+	if (rc != CNB_OK) { fail(rc, "sync"); return false; }
+	rc = cnb_check_device_status(ctx_, stream_);
+	if (rc != CNB_OK) { fail(rc, "device status"); return false; }
+	return ok_;
+}
+
+bool CNet::readOutput(int uid, int what, float* re, float* im) {
+	auto it = map_.find(uid);
+	if (it == map_.end() || !ctx_) { fail(CNB_ERR_ARG, "readOutput: bad uid / not allocated"); return false; }
+	CFunc* f = it->second;
+	const Vars& v = f->out_;
+	const float* sr = what == 0 ? v.real_ : v.dz_star_real_;
+	const float* si = what == 0 ? v.imag_ : v.dz_star_imag_;
+	if (!sr) { fail(CNB_ERR_ARG, f->getName() + ": tensor not materialised (fused)"); return false; }
+	size_t n = (size_t) (f->batched_ ? cur_batch_ : 1) * f->out_size_;
+	int rc = cnb_d2h(ctx_, re, sr, n * sizeof(float), stream_);
+	if (rc == CNB_OK) rc = cnb_d2h(ctx_, im, si, n * sizeof(float), stream_);
+	if (rc != CNB_OK) { fail(rc, "readOutput"); return false; }
+	return true;
+}
+
+}  // namespace cnet_b200

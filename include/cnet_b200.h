@@ -1,0 +1,208 @@
+/*
+ * cnet_b200 — C ABI of the B200 (sm_100a) device path of CNet's batched complex
+ * training step.
+ *
+ * Every entry point is `extern "C"`, takes raw device pointers to fp32 planes
+ * (the reference's split real_/imag_ storage, impl/vars.h:16-46), explicit
+ * dimensions and the CUDA stream to launch on (passed as void*; NULL = legacy
+ * default stream), and returns an int status: 0 = ok, negative = error class
+ * below; the message is available from cnb_last_error().  Nothing here calls
+ * exit(), abort() or traps; nothing blocks except cnb_sync and cnb_d2h.
+ *
+ * Layout conventions (row-major, sample-major):
+ *   activations / activation gradients : two planes [B, N]   (re, im)
+ *   Linear weights                     : two planes [out, in] exactly as inside the
+ *                                        reference's Linear block (impl/linear.h:58)
+ *   broadcast vectors (Hadamard h)     : two planes [N]
+ *   embedding table                    : two planes [V, D]
+ * Only the dL/dz* gradient chain is stored; dL/dz is its conjugate for the
+ * real-valued losses of this path (impl/crossent.h:95-101).
+ *
+ * Each declaration cites the reference interface it replaces (file:line within
+ * the reference project).
+ */
+#ifndef CNET_B200_H_
+#define CNET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status */
+#define CNB_OK            0
+#define CNB_ERR_ARG      -1   /* bad dimension / null pointer / misalignment      */
+#define CNB_ERR_ARENA    -2   /* device arena exhausted                           */
+#define CNB_ERR_CUDA     -3   /* a CUDA runtime / driver call failed              */
+#define CNB_ERR_DEVICE   -4   /* a kernel reported an error word (bounded wait)   */
+#define CNB_ERR_UNSUPPORTED -5
+
+typedef struct cnb_ctx cnb_ctx;
+
+/* Replaces gpuErrchk's print-and-exit (gpu/kernels.h:18-28) and the allocator's
+ * CHECK macros (gpu/allocator.h:19-28): last error message of the calling thread. */
+const char* cnb_last_error(void);
+
+/* ----------------------------------------------------------- context, arena
+ * Replaces GpuHelper (gpu/allocator.h:97-408) and the per-call cudaMalloc /
+ * cudaFree of scratch in gpu/reduce.cpp:382-393, 581-604 and
+ * gpu/reducegrad.cpp:309-322: ONE device block, bump sub-allocation (256-byte
+ * aligned), no allocation on the step path. */
+int cnb_create(int device, size_t arena_bytes, cnb_ctx** out);
+/* Same, over memory the caller owns (e.g. a framework tensor); never freed here. */
+int cnb_create_external(int device, void* arena, size_t arena_bytes, cnb_ctx** out);
+int cnb_destroy(cnb_ctx* ctx);
+int cnb_alloc(cnb_ctx* ctx, size_t bytes, void** out);        /* GpuHelper::allocate, gpu/allocator.h:121-137 */
+int cnb_reset(cnb_ctx* ctx);                                  /* GpuHelper::deallocate, gpu/allocator.h:330-346 */
+size_t cnb_arena_used(const cnb_ctx* ctx);
+size_t cnb_arena_size(const cnb_ctx* ctx);
+int cnb_device_info(int device, int* sm_count, int* cc_major, int* cc_minor,
+                    size_t* total_mem);                       /* PrintInfo, gpu/gpu_func.cpp:52-77 */
+
+/* float_copy_to_gpu / float_copy_from_gpu / int_copy_to_gpu (gpu/allocator.h:308-322, 375-388).
+ * Asynchronous on `stream` when the host buffer is pinned; cnb_d2h synchronises the stream. */
+int cnb_h2d(cnb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes, void* stream);
+int cnb_d2h(cnb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes, void* stream);
+int cnb_memset0(cnb_ctx* ctx, void* dst_dev, size_t bytes, void* stream);  /* gpu_zero_gradients, gpu/kernels.cpp:444-469 */
+int cnb_sync(cnb_ctx* ctx, void* stream);                     /* cudaDeviceSynchronize after every launch, gpu/kernels.cpp:45-46 */
+/* Reads and clears the device error word kernels with bounded waits may set. */
+int cnb_check_device_status(cnb_ctx* ctx, void* stream);
+
+/* ------------------------------------------------------------ complex Linear
+ * Y[b,o] = sum_i X[b,i] * W[o,i] (+ R[b,o] if res_* != NULL: the Residual add fused).
+ * Replaces LinearGpu::gpu_linear_forward (gpu/reduce.h:57, gpu/reduce.cpp:581-604:
+ * reducing_kernel + new_l_kernel_end) and, with res_*, gpu_residual_forward
+ * (gpu/kernels.cpp:145-166).  CPU semantics: impl/linear.h:51-71. */
+int cnb_linear_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
+                   const float* w_re, const float* w_im,
+                   const float* res_re, const float* res_im,
+                   float* y_re, float* y_im, int B, int in, int out, void* stream);
+/* dX*[b,i] (+)= sum_o G*[b,o] * conj(W[o,i]).  Replaces the activation half of
+ * LinearGpu::gpu_linear_backward (gpu/reduce.h:59, gpu/reducegrad.cpp:309-322,
+ * 77-155, 216-245).  CPU semantics: impl/linear.h:73-93. */
+int cnb_linear_bwd_x(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                     const float* w_re, const float* w_im,
+                     float* dx_re, float* dx_im, int B, int in, int out,
+                     int accumulate, void* stream);
+/* dW*[o,i] (+)= sum_b G*[b,o] * conj(X[b,i]).  Replaces the atomicAdd side effect of
+ * Fdz (gpu/reducegrad.cpp:20-44) and gpu_grad_from_clones (gpu/kernels.cpp:566-598).
+ * CPU semantics: impl/linear.h:95-106 summed over samples by impl/cinput.h:54-65. */
+int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                     const float* x_re, const float* x_im,
+                     float* dw_re, float* dw_im, int B, int in, int out,
+                     int accumulate, void* stream);
+/* Which GEMM engine the last cnb_linear_* call on this thread used:
+ * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (skinny / ragged shapes). */
+int cnb_last_gemm_engine(void);
+
+/* ---------------------------------------------------------------- FourierTrans
+ * Y[b,p] = N^-1/2 sum_q X[b,q] e^{-2 pi i pq/N}.  Replaces FourierGpu::gpu_fft_forward
+ * (gpu/reduce.h:79, gpu/reduce.cpp:382-393: dense one-thread-per-term DFT) and
+ * u_roots_allocate_and_copy_on_gpu (gpu/allocator.h:389-407).  CPU: impl/ft.h:37-55. */
+int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
+                float* y_re, float* y_im, int B, int N, void* stream);
+/* dX*[b,q] (+)= N^-1/2 sum_p G*[b,p] e^{+2 pi i pq/N}.  Replaces
+ * FourierGpu::gpu_fft_backward (gpu/reduce.h:85, gpu/reducegrad.cpp:324-336).
+ * CPU: impl/ft.h:57-80. */
+int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
+
+/* --------------------------------------------------------- element-wise layers
+ * Hadamard y = u o v; v is one vector [N] shared by the batch (v_batched = 0) or [B,N].
+ * Replaces HadamardGpu::gpu_hadamard_forward (gpu/kernels.h:217, gpu/kernels.cpp:204-241).
+ * CPU: impl/hadamard.h:34-44. */
+int cnb_hadamard_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im,
+                     const float* v_re, const float* v_im, int v_batched,
+                     float* y_re, float* y_im, int B, int N, void* stream);
+/* du* (+)= g* o conj(v); dv* (+)= g* o conj(u), summed over the batch when v is shared
+ * (deterministic two-stage column reduction; scratch from the arena).  du_* or dv_* may
+ * be NULL to skip that operand.  Replaces gpu_hadamard_backward (gpu/kernels.cpp:243-274)
+ * + gpu_input_backward / gpu_grad_from_clones for the shared vector.  CPU: impl/hadamard.h:46-68. */
+int cnb_hadamard_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                     const float* u_re, const float* u_im,
+                     const float* v_re, const float* v_im, int v_batched,
+                     float* du_re, float* du_im, int accumulate_u,
+                     float* dv_re, float* dv_im, int accumulate_v,
+                     int B, int N, void* stream);
+/* CGelu: y = gelu(re) + i gelu(im) (tanh form).  Replaces GeluGpu::gpu_gelu_forward /
+ * gpu_gelu_backward (gpu/kernels.h:262-268, gpu/kernels.cpp:276-360).  CPU: impl/relu.h:119-168.
+ * Backward: dz* (+)= conj(g*) (dx-dy) + g* (dx+dy), dx = gelu'(re)/2, dy = gelu'(im)/2. */
+int cnb_gelu_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im,
+                 float* y_re, float* y_im, size_t n, void* stream);
+int cnb_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                 const float* z_re, const float* z_im,
+                 float* dz_re, float* dz_im, size_t n, int accumulate, void* stream);
+/* Fused Hadamard(shared h) -> CGelu: a = u o h (kept for the backward), y = gelu(a).
+ * Same reference kernels as the two above, one pass over HBM. */
+int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im,
+                          const float* h_re, const float* h_im,
+                          float* a_re, float* a_im, float* y_re, float* y_im,
+                          int B, int N, void* stream);
+/* Fused backward of the pair: t = gelu_bwd(g*, a); du* (+)= t o conj(h); dh* (+)= sum_b t o conj(u). */
+int cnb_hadamard_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                          const float* a_re, const float* a_im,
+                          const float* u_re, const float* u_im,
+                          const float* h_re, const float* h_im,
+                          float* du_re, float* du_im, int accumulate_u,
+                          float* dh_re, float* dh_im, int accumulate_h,
+                          int B, int N, void* stream);
+/* Residual y = u + v (gpu_residual_forward, gpu/kernels.cpp:145-166; CPU impl/residual.h:40-50);
+ * its backward is a pass-through to both operands = cnb_axpy below. */
+int cnb_residual_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im,
+                     const float* v_re, const float* v_im,
+                     float* y_re, float* y_im, size_t n, void* stream);
+/* dst = (accumulate ? dst : 0) + src on both planes: gradient pass-through
+ * (gpu_residual_backward gpu/kernels.cpp:168-202, gpu_input_backward :120-143). */
+int cnb_axpy(cnb_ctx* ctx, const float* src_re, const float* src_im,
+             float* dst_re, float* dst_im, size_t n, int accumulate, void* stream);
+
+/* ------------------------------------------------------------ row reductions
+ * Reference "SoftMax" = L2 normalisation y = z / max(||z||, 1e-15); inv_norm[b] is kept
+ * for the backward.  Replaces SoftMaxGpu::gpu_soft_max_forward (gpu/reduce.h:123,
+ * gpu/reduce.cpp:189-230).  CPU: impl/softmax.h:33-59. */
+int cnb_softmax_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im,
+                    float* y_re, float* y_im, float* inv_norm, int B, int N, void* stream);
+/* dz*_i (+)= g*_i / n - z_i / n^3 * Re sum_j g*_j conj(z_j): closed form of the generic
+ * Jacobian loop.  Replaces gpu_soft_max_backward (gpu/reduce.h:129,
+ * gpu/reducegrad.cpp:10-19, 60-66, 268-286).  CPU: impl/softmax.h:61-73 via impl/cfunc.h:290-325. */
+int cnb_softmax_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                    const float* z_re, const float* z_im, const float* inv_norm,
+                    float* dz_re, float* dz_im, int B, int N, int accumulate, void* stream);
+/* CrossEntropy forward + backward seed in one pass: loss[b] = -log(max(|z_l|^2/S, 1e-15)),
+ * S = max(sum|z|^2, 1e-15); dz*_k = z_k/S (k != l), dz*_l = -z_l (S-m)/(m S), m = max(|z_l|^2, 1e-15).
+ * dz_* may be NULL (forward only).  Replaces CrossEntropyGpu::gpu_cross_ent_forward / _backward
+ * (gpu/reduce.h:150-156, gpu/reduce.cpp:469-530, 609-655).  CPU: impl/crossent.h:50-104. */
+int cnb_crossent_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im,
+                         const int32_t* labels, float* loss,
+                         float* dz_re, float* dz_im, int B, int M, void* stream);
+
+/* ------------------------------------------------------------------ embedding
+ * out[b, t*D + d] = table[tok[b,t], d]; tok < 0 (NO_TOKEN, impl/batch.h:11) gives zeros.
+ * Replaces EmbeddingGpu::gpu_embedding_forward (gpu/kernels.h:183, gpu/kernels.cpp:362-403).
+ * CPU: impl/embed.h:109-131. */
+int cnb_embed_fwd(cnb_ctx* ctx, const float* tab_re, const float* tab_im,
+                  const int32_t* tokens, float* out_re, float* out_im,
+                  int B, int T, int D, int V, void* stream);
+/* dtable[tok[b,t], d] += g*[b, t*D + d] (fp32 atomics: order of equal-token sums is not
+ * fixed).  Replaces gpu_embedding_backward (gpu/kernels.h:200, gpu/kernels.cpp:405-442).
+ * CPU: impl/embed.h:133-148. */
+int cnb_embed_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                  const int32_t* tokens, float* dtab_re, float* dtab_im,
+                  int B, int T, int D, int V, void* stream);
+
+/* --------------------------------------------------------------------- update
+ * w -= lr * g over n floats (re and im planes are just floats here); g is zeroed when
+ * zero_grad != 0.  Replaces gpu_update_input (gpu/kernels.h:75, gpu/kernels.cpp:471-492).
+ * CPU: impl/cfunc.h:147-152 + impl/cnet.h:413-421. */
+int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
+                   void* stream);
+
+/* Number of kernels this library has launched in this process (diagnostics / benches). */
+unsigned long long cnb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CNET_B200_H_ */

@@ -1,0 +1,60 @@
+/*
+ * Flat C binding of the host facade (cnet_b200/host/cnet.h) for callers that cannot
+ * include C++ — the Python package binds these with ctypes.  One handle = one CNet
+ * (gpu/gpu_func.h:41-1113 in the reference).  Every function returns 0 / a positive uid on
+ * success and a negative cnb status on failure; cnh_error() gives the message.
+ * Host pointers unless said otherwise.
+ */
+#ifndef CNET_B200_HOST_H_
+#define CNET_B200_HOST_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cnh_net cnh_net;
+typedef int (*cnh_bucket_hook)(void* user, float* dev_grads, size_t count, int bucket, int n_buckets);
+
+cnh_net* cnh_create(int device, size_t arena_bytes, void* ext_arena_dev);   /* CNet() + device choice */
+void cnh_destroy(cnh_net* net);
+/* Device and arena to use (ext_arena_dev != NULL: caller-owned device memory); before cnh_allocate. */
+int cnh_set_device(cnh_net* net, int device, size_t arena_bytes, void* ext_arena_dev);
+const char* cnh_error(cnh_net* net);
+void cnh_clear_error(cnh_net* net);
+
+/* CNet::add(CFunc*, {uids}) (gpu/gpu_func.h:1013-1019).  type = the reference's type id
+ * (impl/cnet.h:31-44); (a,b,c): CInput(a) | CEmbedding(dim a, tokens b, vocab c) |
+ * FourierTrans(a) | Hadamard(a,a) | CGelu(a) | Linear(in1 a, in2 b) | Residual(a) |
+ * SoftMax(a) | CrossEntropy(a). */
+int cnh_add(cnh_net* net, int type, int a, int b, int c, const int* prev, int nprev);
+int cnh_out_size(cnh_net* net, int uid);
+int cnh_init_inputs(cnh_net* net, uint64_t seed);                            /* CNet::init_inputs(seed) */
+int cnh_set_values(cnh_net* net, int uid, const float* re, const float* im, int len);
+int cnh_get_values(cnh_net* net, int uid, float* re, float* im, int len);   /* getInputsFromGpu, one input */
+int cnh_get_wgrad(cnh_net* net, int uid, float* re, float* im, int len);
+int cnh_set_stream(cnh_net* net, void* stream);
+int cnh_set_fusion(cnh_net* net, int on);
+int cnh_set_bucket_hook(cnh_net* net, cnh_bucket_hook hook, void* user);
+size_t cnh_required_arena(cnh_net* net, int batch);
+int cnh_allocate(cnh_net* net, int batch);                                   /* CNet::allocateOnGpu */
+/* batchToGpu (gpu/gpu_func.h:368-427): planes [B, n] or tokens [B, T]; labels [B] */
+int cnh_upload(cnh_net* net, const float* re, const float* im, const int32_t* tokens,
+               const int32_t* labels, int batch);
+int cnh_forward(cnh_net* net);                                               /* GpuForward, :645-657 */
+int cnh_backward(cnh_net* net);                                              /* gpuBackward, :1096-1101 */
+int cnh_backward_label(cnh_net* net, int label);                             /* CNet::backward(label) */
+int cnh_update(cnh_net* net, float lr);                                      /* gpuUpdateInputs, :491-495 */
+int cnh_get_losses(cnh_net* net, float* out, int n);                         /* getLoss, :906-926 */
+int cnh_sync(cnh_net* net);
+int cnh_read_output(cnh_net* net, int uid, int what, float* re, float* im); /* testDataFromGpu, :840-862 */
+int cnh_grad_arena(cnh_net* net, void** dev_ptr, size_t* count, int* n_buckets);
+int cnh_weight_arena(cnh_net* net, void** dev_ptr, size_t* count);
+void* cnh_context(cnh_net* net);                                             /* the cnb_ctx* of the net */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CNET_B200_HOST_H_ */

@@ -1,0 +1,110 @@
+"""GPU parity of whole training steps: the device net (through the host facade and the
+C ABI) against the float64 restatement and against the fixtures produced by the
+unmodified reference CPU path.  Tolerances (norm-relative per tensor): 1e-4 on
+activations, losses and post-update weights, 1e-3 on gradients."""
+import numpy as np
+import pytest
+
+import util
+from cnet_b200 import configs
+from cnet_b200.net import Net
+from oracle import cnet_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL_ACT, TOL_GRAD = 1e-4, 1e-3
+# The reference's own fp32 Bluestein FFT is ~1e-4 off an exact DFT at these lengths, so
+# against its fixtures the activation bound is its error plus ours.
+GOLDEN_ACT = {"classifier_784": 3e-4, "classifier_100_train": 3e-4}
+
+
+def _device_case(name, fuse):
+    return util.run_case(Net(), name, post_alloc=lambda n, B: n.allocate(B, fuse=fuse))
+
+
+@pytest.mark.parametrize("fuse", [False, True])
+@pytest.mark.parametrize("name", sorted(util.CASES))
+def test_step_matches_restatement_and_reference(name, fuse):
+    got = _device_case(name, fuse)
+    want = util.run_case(cnet_oracle.OracleNet(), name)
+    util.compare(got, want, TOL_ACT, TOL_GRAD, label=name + " vs float64 restatement")
+    golden = util.load_golden(name)
+    util.compare(got, golden, GOLDEN_ACT.get(name, TOL_ACT), TOL_GRAD, label=name + " vs reference fixture")
+
+
+def test_fused_and_unfused_agree():
+    a = _device_case("mixer_64x2", False)
+    b = _device_case("mixer_64x2", True)
+    util.compare(b, a, 1e-5, 1e-5, label="fused vs unfused")
+
+
+def test_gradients_accumulate_until_update():
+    """Two backward passes without an update sum the weight gradients (impl/cinput.h:54-65)."""
+    net = Net()
+    spec = configs.build_classifier(net, n=64, m=10)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    net.allocate(8)
+    x, labels = configs.make_batch(spec, 8, 0)
+    net.run_batch(spec.main, x=x, labels=labels)
+    g1 = net.get_wgrad(spec.layers["w"])
+    net.run_batch(spec.main, x=x, labels=labels)
+    g2 = net.get_wgrad(spec.layers["w"])
+    assert util.relerr(g2, (2 * g1[0], 2 * g1[1])) < 1e-6
+    net.update(0.01, 8)
+    g3 = net.get_wgrad(spec.layers["w"])
+    assert np.all(g3[0] == 0) and np.all(g3[1] == 0)
+
+
+def test_partial_batch_and_batch_of_one():
+    net = Net()
+    spec = configs.build_mixer(net, n=32, blocks=1, m=10)
+    w = configs.init_weights(spec, 0)
+    for uid, (re, im) in w.items():
+        net.set_values(uid, re, im)
+    net.allocate(6)
+    x, labels = configs.make_batch(spec, 6, 0)
+    ora = cnet_oracle.OracleNet()
+    ospec = configs.build_mixer(ora, n=32, blocks=1, m=10)
+    for uid, (re, im) in w.items():
+        ora.set_values(uid, re, im)
+    for B in (1, 5):
+        xs = (x[0][:B].copy(), x[1][:B].copy())
+        got = net.run_batch(spec.main, x=xs, labels=labels[:B].copy())
+        want = ora.run_batch(ospec.main, x=xs, labels=labels[:B])
+        assert got.shape == (B,)
+        assert util.relerr(got, want) < TOL_ACT
+        net.update(0.0, 1)
+
+
+def test_oversized_batch_is_rejected():
+    from cnet_b200.lib import CnetError
+    net = Net()
+    spec = configs.build_classifier(net, n=16, m=4)
+    net.init_inputs(1)
+    net.allocate(2)
+    x, labels = configs.make_batch(spec, 3, 0)
+    with pytest.raises(CnetError, match="exceeds"):
+        net.upload(x=x, labels=labels)
+
+
+def test_loss_curve_follows_reference_training():
+    """100-step SGD on the classifier shape (reduced width so the CPU checker is quick):
+    the device loss curve tracks the float64 restatement."""
+    n, m, B, steps = 196, 10, 16, 30
+    dev, ora = Net(), cnet_oracle.OracleNet()
+    sd, so = configs.build_classifier(dev, n=n, m=m), configs.build_classifier(ora, n=n, m=m)
+    w = configs.init_weights(sd, 0)
+    for uid, (re, im) in w.items():
+        dev.set_values(uid, re, im)
+        ora.set_values(uid, re, im)
+    dev.allocate(B)
+    ld, lo = [], []
+    for s in range(steps):
+        x, labels = configs.make_batch(sd, B, 0, step=s)
+        ld.append(dev.run_batch(sd.main, x=x, labels=labels).mean())
+        lo.append(ora.run_batch(so.main, x=x, labels=labels).mean())
+        dev.update(0.5, B)
+        ora.update(0.5, B)
+    assert util.relerr(np.array(ld), np.array(lo)) < 1e-4
+    assert ld[-1] < ld[0]
