@@ -1,12 +1,416 @@
-// tcgen05 3xTF32 complex GEMM (placeholder until the tensor-core tiles land: reports every
-// shape as unsupported so the dispatch uses the fp32 SIMT tiles).
+// tcgen05 complex GEMM with a 3xTF32 error-compensated split, for sm_100a.
+//
+//   D[m,n] (+)= sum_k A[m,k] * (conjB ? conj(B[n,k]) : B[n,k]) (+ R[m,n])
+//   A [M,K], B [N,K] complex, both K-major (row-major) fp32 re/im planes.
+//
+// Numerics.  Every fp32 operand x is split once, before the GEMM, into hi = x with the 13 low
+// mantissa bits cleared (exactly a TF32 value) and lo = x - hi (exact in fp32).  Each real
+// product is then three TF32 tensor-core MMAs with fp32 accumulation in tensor memory:
+// hi*hi + hi*lo + lo*hi (the dropped lo*lo term is ~2^-22 relative).
+//
+// Tiling.  One CTA computes a 128 x 128 complex tile.  The B tile is staged as ONE 256-row
+// operand [B_re rows ; B_im rows], so every MMA is 128 x 256 x 8 and the complex structure
+// costs two accumulators instead of four MMA shapes:
+//     acc1 = A_re * [B_re ; B_im]^T      (TMEM columns   0..255)
+//     acc2 = A_im * [B_re ; B_im]^T      (TMEM columns 256..511)
+//     D_re = acc1[:, :128] -/+ acc2[:, 128:],   D_im = acc1[:, 128:] +/- acc2[:, :128]   (epilogue)
+// Per 16-deep k-block a stage holds 8 operand planes of 8 KB (A hi/lo re/im, B hi/lo re/im) =
+// 64 KB, 64-byte swizzled; 3 stages.  Each CTA issues its own plain TMA tile loads; their zero fill
+// handles every M/N/K edge.
+//
+// Roles.  warp 0: TMA producer; warp 1: TMEM allocation + MMA issue (one elected thread);
+// warps 2..5: epilogue (tcgen05.ld, combine, residual / accumulate, global stores).
+// Every mbarrier wait is bounded (2 s); on expiry the kernel records an error word, skips to
+// the common exit, frees its tensor memory and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 
-namespace cnb {
-bool cgemm_tc_shape_ok(int, int, int) { return false; }
-int cgemm_tc_nt(cnb_ctx*, const float*, const float*, const float*, const float*, int, const float*, const float*,
-                float*, float*, int, int, int, int, cudaStream_t) {
-    return set_error(CNB_ERR_UNSUPPORTED, "tensor-core GEMM not built");
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 16, STAGES = 3;
+constexpr int PLANE_BYTES = BM * BK * 4;             // 8 KB: one operand plane of one stage
+constexpr int STAGE_BYTES = 8 * PLANE_BYTES;         // 64 KB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct TcParams {
+    float* d_re; float* d_im;
+    const float* r_re; const float* r_im;
+    int M, N, K, conjB, accumulate;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: false (and the error word set) if the phase did not complete in WAIT_LIMIT_NS
+// or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            atomicExch(status + 1, (int) blockIdx.x);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// K-major operand tile, 64-byte swizzle: rows of 64 B, 8-row groups 512 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((addr >> 4) & 0x3FFF);           // start address, 16-byte units
+    d |= (uint64_t) 1 << 16;                          // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t) (512 >> 4) << 32;                 // stride byte offset between 8-row groups
+    d |= (uint64_t) 1 << 46;                          // descriptor version of sm_100
+    d |= (uint64_t) 4 << 61;                          // layout type: 64-byte swizzle
+    return d;
+}
+
+// kind::tf32, fp32 accumulate, A and B K-major, M = 128, N = 256
+constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
+           const __grid_constant__ CUtensorMap a_lo_re, const __grid_constant__ CUtensorMap a_lo_im,
+           const __grid_constant__ CUtensorMap b_hi_re, const __grid_constant__ CUtensorMap b_hi_im,
+           const __grid_constant__ CUtensorMap b_lo_re, const __grid_constant__ CUtensorMap b_lo_im,
+           const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // operand stages need the alignment of their swizzle pattern; 1024 B covers every mode
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulators ready
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int m0 = (blockIdx.x / tiles_n) * BM, n0 = (blockIdx.x % tiles_n) * BN;
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    const uint32_t acc_bar = bar_base + 8u * (2 * STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // whole warp: allocate all 512 tensor-memory columns (1 CTA per SM by shared-memory size)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_lo_re, &a_lo_im, &b_hi_re, &b_hi_im, &b_lo_re, &b_lo_im};
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                int s = kb % STAGES;
+                uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, 1)) break;
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                uint32_t dst = smem_base + s * STAGE_BYTES;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    tma_load_2d(dst + q * PLANE_BYTES, maps[q], full_bar(s), kb * BK, q < 4 ? m0 : n0);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                int s = kb % STAGES;
+                uint32_t phase = (kb / STAGES) & 1;
+                ok = mbar_wait(full_bar(s), phase, abort_flag, p.status, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t st = smem_base + s * STAGE_BYTES;
+#pragma unroll
+                for (int j = 0; j < BK / 8; ++j) {
+                    uint32_t ko = j * 32;            // 8 TF32 = 32 bytes along K inside the swizzled row
+                    uint64_t a_hr = smem_desc_sw64(st + 0 * PLANE_BYTES + ko), a_hi_ = smem_desc_sw64(st + 1 * PLANE_BYTES + ko);
+                    uint64_t a_lr = smem_desc_sw64(st + 2 * PLANE_BYTES + ko), a_li = smem_desc_sw64(st + 3 * PLANE_BYTES + ko);
+                    uint64_t b_h = smem_desc_sw64(st + 4 * PLANE_BYTES + ko), b_l = smem_desc_sw64(st + 6 * PLANE_BYTES + ko);
+                    uint32_t first = (kb == 0 && j == 0) ? 0u : 1u;
+                    umma_tf32(tmem_base, a_lr, b_h, first);          // small terms first
+                    umma_tf32(tmem_base, a_hr, b_l, 1u);
+                    umma_tf32(tmem_base, a_hr, b_h, 1u);
+                    umma_tf32(tmem_base + 256, a_li, b_h, first);
+                    umma_tf32(tmem_base + 256, a_hi_, b_l, 1u);
+                    umma_tf32(tmem_base + 256, a_hi_, b_h, 1u);
+                }
+                umma_commit(empty_bar(s));           // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_bar);
+        }
+    } else {
+        // -------------------------------------------------------------------- epilogue
+        const int q = warp & 3;                      // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        const int gm = m0 + row;
+        bool ok = mbar_wait(acc_bar, 0, abort_flag, p.status, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const uint32_t tl = tmem_base + ((uint32_t) (q * 32) << 16);
+            const float sgn = p.conjB ? 1.f : -1.f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float a[16], b[16], e[16], f[16];
+                tmem_ld16(tl + c, a);               // A_re.B_re
+                tmem_ld16(tl + 128 + c, b);         // A_re.B_im
+                tmem_ld16(tl + 256 + c, e);         // A_im.B_re
+                tmem_ld16(tl + 384 + c, f);         // A_im.B_im
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (gm < p.M) {
+                    size_t o = (size_t) gm * p.N + n0 + c;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        if (n0 + c + i >= p.N) break;
+                        float vr = a[i] + sgn * f[i];          // re: ar.br -/+ ai.bi
+                        float vi = e[i] - sgn * b[i];          // im: ai.br +/- ar.bi
+                        if (p.r_re) { vr += p.r_re[o + i]; vi += p.r_im[o + i]; }
+                        if (p.accumulate) { vr += p.d_re[o + i]; vi += p.d_im[o + i]; }
+                        p.d_re[o + i] = vr;
+                        p.d_im[o + i] = vi;
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// hi = x with the low 13 mantissa bits cleared, lo = x - hi; optionally transposed ([R,C] -> [C,R]).
+__global__ void split_k(const float* __restrict__ s0, const float* __restrict__ s1, float* __restrict__ hi0,
+                        float* __restrict__ hi1, float* __restrict__ lo0, float* __restrict__ lo1, size_t n) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * 4;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+        if (i + 3 < n) {
+            float4 x = *reinterpret_cast<const float4*>(s0 + i), y = *reinterpret_cast<const float4*>(s1 + i);
+            float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w}, xh[4], yh[4], xl[4], yl[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                xh[k] = __uint_as_float(__float_as_uint(xs[k]) & 0xFFFFE000u); xl[k] = xs[k] - xh[k];
+                yh[k] = __uint_as_float(__float_as_uint(ys[k]) & 0xFFFFE000u); yl[k] = ys[k] - yh[k];
+            }
+            *reinterpret_cast<float4*>(hi0 + i) = make_float4(xh[0], xh[1], xh[2], xh[3]);
+            *reinterpret_cast<float4*>(hi1 + i) = make_float4(yh[0], yh[1], yh[2], yh[3]);
+            *reinterpret_cast<float4*>(lo0 + i) = make_float4(xl[0], xl[1], xl[2], xl[3]);
+            *reinterpret_cast<float4*>(lo1 + i) = make_float4(yl[0], yl[1], yl[2], yl[3]);
+        } else {
+            for (size_t j = i; j < n; ++j) {
+                float h = __uint_as_float(__float_as_uint(s0[j]) & 0xFFFFE000u);
+                hi0[j] = h; lo0[j] = s0[j] - h;
+                h = __uint_as_float(__float_as_uint(s1[j]) & 0xFFFFE000u);
+                hi1[j] = h; lo1[j] = s1[j] - h;
+            }
+        }
+    }
+}
+
+__global__ void split_transpose_k(const float* __restrict__ s0, const float* __restrict__ s1,
+                                  float* __restrict__ hi0, float* __restrict__ hi1, float* __restrict__ lo0,
+                                  float* __restrict__ lo1, int R, int C) {
+    __shared__ float t0[32][33], t1[32][33];
+    int c = blockIdx.x * 32 + threadIdx.x;
+    for (int k = threadIdx.y; k < 32; k += 8) {
+        int r = blockIdx.y * 32 + k;
+        if (r < R && c < C) { t0[k][threadIdx.x] = s0[(size_t) r * C + c]; t1[k][threadIdx.x] = s1[(size_t) r * C + c]; }
+    }
+    __syncthreads();
+    int r = blockIdx.y * 32 + threadIdx.x;
+    for (int k = threadIdx.y; k < 32; k += 8) {
+        int cc = blockIdx.x * 32 + k;
+        if (r < R && cc < C) {
+            size_t o = (size_t) cc * R + r;
+            float x = t0[threadIdx.x][k], y = t1[threadIdx.x][k];
+            float xh = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+            float yh = __uint_as_float(__float_as_uint(y) & 0xFFFFE000u);
+            hi0[o] = xh; lo0[o] = x - xh;
+            hi1[o] = yh; lo1[o] = y - yh;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows, K] fp32 row-major plane; box = BK x 128 rows; 64-byte swizzle; zero fill outside.
+int make_map(CUtensorMap* m, const float* base, int rows, int K) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t) K, (cuuint64_t) rows};
+    cuuint64_t strides[1] = {(cuuint64_t) K * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t) BK, 128u};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a [%d,%d] plane", (int) r, rows, K);
+    return CNB_OK;
+}
+
+}  // namespace
+
+namespace cnb {
+
+bool cgemm_tc_shape_ok(int M, int N, int K) {
+    // TMA needs 16-byte row pitch; small or skinny problems are faster on the SIMT tiles
+    return (K % 4 == 0) && K >= 32 && M >= 64 && N >= 64;
+}
+
 void cgemm_tc_release(cnb_ctx*) {}
+
+size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
+    return 4 * ((size_t) M * K + (size_t) N * K) * sizeof(float) + 4096;
+}
+
+// Operands are split into scratch ([rows,K] hi/lo re/im planes each); a_trans / b_trans say the
+// source is stored [K, rows] and must be transposed on the way.
+int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
+                 const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
+                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set = true;
+    }
+    if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
+        return set_error(CNB_ERR_ARG, "cgemm_tc: misaligned output");
+    float* ws = nullptr;
+    int rc = ensure_scratch(ctx, cgemm_tc_workspace_bytes(M, N, K), &ws);
+    if (rc != CNB_OK) return rc;
+    size_t na = ((size_t) M * K + 63) & ~size_t(63), nb = ((size_t) N * K + 63) & ~size_t(63);
+    float* ap[4] = {ws, ws + na, ws + 2 * na, ws + 3 * na};          // hi_re, hi_im, lo_re, lo_im
+    float* bp[4] = {ws + 4 * na, ws + 4 * na + nb, ws + 4 * na + 2 * nb, ws + 4 * na + 3 * nb};
+    auto split = [&](const float* s0, const float* s1, float** dst, int rows, int trans) -> int {
+        if (trans) {   // source is [K, rows]
+            dim3 grid((rows + 31) / 32, (K + 31) / 32), block(32, 8);
+            split_transpose_k<<<grid, block, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], K, rows);
+        } else {
+            size_t n = (size_t) rows * K;
+            bool al = ((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) == 0;
+            if (!al) return set_error(CNB_ERR_ARG, "cgemm_tc: operand planes must be 16-byte aligned");
+            size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
+            split_k<<<(int) (blocks < cap ? blocks : cap), 256, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], n);
+        }
+        CNB_LAUNCH_CHECK("split");
+        return CNB_OK;
+    };
+    if ((rc = split(a_re, a_im, ap, M, a_trans)) != CNB_OK) return rc;
+    if ((rc = split(b_re, b_im, bp, N, b_trans)) != CNB_OK) return rc;
+    alignas(64) CUtensorMap maps[8];
+    for (int q = 0; q < 4; ++q) {
+        if ((rc = make_map(&maps[q], ap[q], M, K)) != CNB_OK) return rc;
+        if ((rc = make_map(&maps[4 + q], bp[q], N, K)) != CNB_OK) return rc;
+    }
+    TcParams p;
+    p.d_re = d_re; p.d_im = d_im; p.r_re = r_re; p.r_im = r_im;
+    p.M = M; p.N = N; p.K = K; p.conjB = conjB; p.accumulate = accumulate;
+    p.status = ctx->d_status;
+    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    cgemm_tc_k<<<tiles, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
+                                                      maps[7], p);
+    CNB_LAUNCH_CHECK("cgemm_tc");
+    return CNB_OK;
+}
+
+int cgemm_tc_nt(cnb_ctx* ctx, const float* a_re, const float* a_im, const float* b_re, const float* b_im, int conjB,
+                const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K, int accumulate,
+                cudaStream_t st) {
+    return cgemm_tc_run(ctx, a_re, a_im, 0, b_re, b_im, 0, conjB, r_re, r_im, d_re, d_im, M, N, K, accumulate, st);
+}
+
 }  // namespace cnb

@@ -52,6 +52,11 @@ int cgemm_tc_nt(cnb_ctx* ctx, const float* a_re, const float* a_im,
                 const float* r_re, const float* r_im, float* d_re, float* d_im,
                 int M, int N, int K, int accumulate, cudaStream_t st);
 bool cgemm_tc_shape_ok(int M, int N, int K);
+// General form: a_trans / b_trans = the source planes are stored [K, rows] (transposed while splitting).
+int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
+                 const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
+                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st);
+size_t cgemm_tc_workspace_bytes(int M, int N, int K);
 void cgemm_tc_release(cnb_ctx* ctx);
 
 // [R, C] -> [C, R] transpose of a re/im plane pair (operand staging for the K-major GEMM).

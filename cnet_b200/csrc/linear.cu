@@ -1,5 +1,6 @@
 // Complex Linear (forward, dX*, dW*) and FourierTrans as a complex GEMM against a
 // twiddle matrix: shape dispatch between the tcgen05 3xTF32 tiles and the fp32 SIMT tiles.
+#include <algorithm>
 #include <cmath>
 #include <vector>
 
@@ -67,17 +68,10 @@ int cnb_linear_bwd_x(cnb_ctx* ctx, const float* g_re, const float* g_im, const f
     cudaStream_t st = cnb::S(stream);
     // dX*[b,i] = sum_o G[b,o] conj(W[o,i]) : M = B, N = in, K = out; B-operand(n=i,k=o) = W[o,i]
     if (cnb::cgemm_tc_shape_ok(B, in, out)) {
-        // stage W^T [in, out] so both operands are K-major
-        float* ws = nullptr;
-        int rc = cnb::ensure_scratch(ctx, (size_t) 2 * in * out * sizeof(float), &ws);
-        if (rc != CNB_OK) return rc;
-        float* wt_re = ws;
-        float* wt_im = ws + (size_t) in * out;
-        rc = cnb::transpose_planes(w_re, w_im, wt_re, wt_im, out, in, st);
-        if (rc != CNB_OK) return rc;
+        // the B operand (n = i, k = o) is W stored [K = out, N = in]: transposed while it is split
         cnb::g_last_engine = 1;
-        return cnb::cgemm_tc_nt(ctx, g_re, g_im, wt_re, wt_im, 1, nullptr, nullptr, dx_re, dx_im, B, in, out,
-                                accumulate, st);
+        return cnb::cgemm_tc_run(ctx, g_re, g_im, 0, w_re, w_im, 1, 1, nullptr, nullptr, dx_re, dx_im, B, in, out,
+                                 accumulate, st);
     }
     cnb::g_last_engine = 2;
     return cnb::cgemm_simt(ctx, g_re, g_im, out, 1, w_re, w_im, 1, in, 1, nullptr, nullptr, dx_re, dx_im, B, in,
@@ -91,18 +85,10 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im, const f
     cudaStream_t st = cnb::S(stream);
     // dW*[o,i] = sum_b G[b,o] conj(X[b,i]) : M = out, N = in, K = B
     if (cnb::cgemm_tc_shape_ok(out, in, B)) {
-        float* ws = nullptr;
-        size_t ng = (size_t) B * out, nx = (size_t) B * in;
-        int rc = cnb::ensure_scratch(ctx, 2 * (ng + nx) * sizeof(float), &ws);
-        if (rc != CNB_OK) return rc;
-        float *gt_re = ws, *gt_im = ws + ng, *xt_re = ws + 2 * ng, *xt_im = ws + 2 * ng + nx;
-        rc = cnb::transpose_planes(g_re, g_im, gt_re, gt_im, B, out, st);
-        if (rc != CNB_OK) return rc;
-        rc = cnb::transpose_planes(x_re, x_im, xt_re, xt_im, B, in, st);
-        if (rc != CNB_OK) return rc;
+        // both operands are stored [K = B, rows]: transposed while they are split
         cnb::g_last_engine = 1;
-        return cnb::cgemm_tc_nt(ctx, gt_re, gt_im, xt_re, xt_im, 1, nullptr, nullptr, dw_re, dw_im, out, in, B,
-                                accumulate, st);
+        return cnb::cgemm_tc_run(ctx, g_re, g_im, 1, x_re, x_im, 1, 1, nullptr, nullptr, dw_re, dw_im, out, in, B,
+                                 accumulate, st);
     }
     cnb::g_last_engine = 2;
     return cnb::cgemm_simt(ctx, g_re, g_im, 1, out, x_re, x_im, 1, in, 1, nullptr, nullptr, dw_re, dw_im, out, in,
@@ -137,6 +123,21 @@ int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re
     cnb::g_last_engine = 2;
     return cnb::cgemm_simt(ctx, g_re, g_im, N, 1, t.re, t.im, N, 1, 1, nullptr, nullptr, dx_re, dx_im, B, N, N,
                            accumulate, st);
+}
+
+/* Scratch the three Linear products and the column reductions of one layer may need. */
+size_t cnb_linear_workspace(int B, int in, int out) {
+    size_t w = 0;
+    if (cnb::cgemm_tc_shape_ok(B, out, in)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(B, out, in));
+    if (cnb::cgemm_tc_shape_ok(B, in, out)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(B, in, out));
+    if (cnb::cgemm_tc_shape_ok(out, in, B)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(out, in, B));
+    return w;
+}
+
+int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes) {
+    CNB_CHECK_ARG(ctx, "cnb_reserve_scratch: null context");
+    float* p = nullptr;
+    return cnb::ensure_scratch(ctx, bytes, &p);
 }
 
 }  // extern "C"

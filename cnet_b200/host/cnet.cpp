@@ -426,23 +426,29 @@ bool CNet::planFusion() {
 	return true;
 }
 
+size_t CNet::scratchBytes(int B) const {
+	size_t scratch = 8u << 20;
+	for (auto f : func_list_) {
+		if (Linear* l = dynamic_cast<Linear*>(f))
+			scratch = std::max(scratch, cnb_linear_workspace(B, l->firstInputLength(), l->outSize()));
+		if (dynamic_cast<FourierTrans*>(f))
+			scratch = std::max(scratch, cnb_linear_workspace(B, f->in_size_, f->in_size_));
+		if (f->type_ == isHadamard) scratch = std::max(scratch, (size_t) 128 * f->out_size_ * 2 * sizeof(float));
+	}
+	return scratch + 4096;
+}
+
 size_t CNet::requiredArenaBytes(int B) const {
 	size_t floats = 0, extra = 0, dft = 0;
-	size_t scratch = 64u << 20;
 	for (auto f : func_list_) {
 		bool weight = dynamic_cast<CInput*>(f) && f != func_list_.front();
 		if (weight) floats += 4 * pad64(f->out_size_);
 		else floats += 4 * pad64((size_t) B * f->out_size_);
 		if (CEmbedding* e = dynamic_cast<CEmbedding*>(f)) floats += 4 * pad64((size_t) e->inSize());
-		if (dynamic_cast<FourierTrans*>(f)) dft = std::max(dft, (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512);
-		if (Linear* l = dynamic_cast<Linear*>(f)) {
-			size_t ws = 2 * ((size_t) B * l->outSize() + (size_t) B * l->firstInputLength()) * 4;
-			ws = std::max(ws, (size_t) 2 * l->secondInputLength() * 4);
-			scratch = std::max(scratch, ws * 3);
-		}
+		if (dynamic_cast<FourierTrans*>(f)) dft += (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512;
 		extra += f->extraBytes(B) + 256;
 	}
-	return floats * sizeof(float) + extra + dft * 4 + scratch + (16u << 20);
+	return floats * sizeof(float) + extra + dft + scratchBytes(B) + (16u << 20);
 }
 
 bool CNet::allocateOnGpu(int B) {
@@ -490,6 +496,7 @@ bool CNet::allocateOnGpu(int B) {
 			: cnb_create(device_, arena_bytes_, &ctx_);
 	if (rc != CNB_OK) { fail(rc, "allocateOnGpu"); ctx_ = nullptr; return false; }
 	batch_ = cur_batch_ = B;
+	if ((rc = cnb_reserve_scratch(ctx_, scratchBytes(B))) != CNB_OK) { fail(rc, "scratch"); return false; }
 
 	// 1. weights: one block of value planes and one block of dz* planes with the same layout,
 	//    in backward order (reverse insertion), so gradient buckets complete front to back.
@@ -755,6 +762,9 @@ bool CNet::readOutput(int uid, int what, float* re, float* im) {
 	const Vars& v = f->out_;
 	const float* sr = what == 0 ? v.real_ : v.dz_star_real_;
 	const float* si = what == 0 ? v.imag_ : v.dz_star_imag_;
+	if (Linear* l = dynamic_cast<Linear*>(f)) {
+		if (l->fused_residual_ && what == 0) sr = nullptr;   // only the post-Residual sum exists
+	}
 	if (!sr) { fail(CNB_ERR_ARG, f->getName() + ": tensor not materialised (fused)"); return false; }
 	size_t n = (size_t) (f->batched_ ? cur_batch_ : 1) * f->out_size_;
 	int rc = cnb_d2h(ctx_, re, sr, n * sizeof(float), stream_);

@@ -361,6 +361,7 @@ public:
 	// device lifecycle (gpu/gpu_func.h:1071-1086): builds batched tensors, uploads weights
 	bool allocateOnGpu(int batch_size);
 	size_t requiredArenaBytes(int batch_size) const;
+	size_t scratchBytes(int batch_size) const;
 	bool setInputValues(int uid, const float* re, const float* im, int len);     // host -> weights
 	bool getInputValues(int uid, float* re, float* im, int len);
 	bool getInputGradients(int uid, float* re, float* im, int len);

@@ -38,6 +38,8 @@ SIGNATURES = {
     "cnb_linear_bwd_x": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] * 4 + [_vp]),
     "cnb_linear_bwd_w": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] * 4 + [_vp]),
     "cnb_last_gemm_engine": (C.c_int, []),
+    "cnb_linear_workspace": (_sz, [C.c_int, C.c_int, C.c_int]),
+    "cnb_reserve_scratch": (C.c_int, [_vp, _sz]),
     "cnb_dft_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 2 + [_vp]),
     "cnb_dft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
     "cnb_hadamard_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] + [_P] * 2 + [C.c_int] * 2 + [_vp]),

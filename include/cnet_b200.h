@@ -93,6 +93,12 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im,
                      const float* x_re, const float* x_im,
                      float* dw_re, float* dw_im, int B, int in, int out,
                      int accumulate, void* stream);
+/* Scratch bytes the three products of a Linear(B, in, out) may take from the arena (operand
+ * hi/lo split planes of the tensor-core GEMM), and a way to reserve the step's maximum up front
+ * so that no call on the step path grows the scratch region.  Replace the per-call cudaMalloc of
+ * gpu/reduce.cpp:594-598 and gpu/reducegrad.cpp:309-322. */
+size_t cnb_linear_workspace(int B, int in, int out);
+int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes);
 /* Which GEMM engine the last cnb_linear_* call on this thread used:
  * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (skinny / ragged shapes). */
 int cnb_last_gemm_engine(void);

@@ -48,6 +48,8 @@ def test_linear_three_products(ctx, B, n_in, n_out):
     X, W, G = _c(x), _c(w), _c(g)
     y = _host(ctx.linear_fwd(_dev(x), _dev(w)))
     assert util.relerr(y, _pair(X @ W.T)) < 1e-5
+    # square shapes run on the tcgen05 tiles, skinny / tiny ones on the fp32 SIMT tiles
+    assert ctx.last_gemm_engine() == (1 if (B >= 64 and n_out >= 64 and n_in >= 32 and n_in % 4 == 0) else 2)
     yr = _host(ctx.linear_fwd(_dev(x), _dev(w), res=_dev(r)))
     assert util.relerr(yr, _pair(X @ W.T + _c(r))) < 1e-5
     dx = _host(ctx.linear_bwd_x(_dev(g), _dev(w)))
