@@ -2,6 +2,9 @@
 // fused pair), Residual, gradient pass-through, SGD update, plane transposes.
 // All kernels stream each plane once with 16-byte accesses where the row length allows
 // it (W = 4), else scalar (W = 1); grids are sized in multiples of the SM count.
+#include <algorithm>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -427,3 +430,92 @@ int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zer
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Hadamard backward without any allocation.
+//
+// Some hosts of this library are not allowed to allocate device memory at the point where
+// they call it: a runtime that has already handed every byte of the device to its own pool
+// and must not let a foreign cudaMalloc fail or fragment it, or a latency-critical loop that
+// cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply.  For those, this
+// one entry point keeps the column-reduction partials in a fixed array that is part of the
+// loaded module instead of in an arena: 2 MiB per GPU that loads the library, held until the
+// process exits.  Limits: N <= CNB_STATIC_MAX_N, shared (non-batched) v only.
+//
+// In host code `g_static_partials` is only a handle for the symbol, not a device address, so
+// its address is looked up with cudaGetSymbolAddress once per device (with that device
+// current) and that pointer is what the kernels receive.
+namespace {
+
+constexpr int kStaticMaxN = 4096;
+constexpr int kStaticMaxChunks = 64;
+static __device__ __align__(256) float g_static_partials[2 * kStaticMaxChunks * kStaticMaxN];
+
+struct StaticScratch {
+    float* ptr = nullptr;
+    int sm_count = 0;
+};
+
+int static_scratch_for_current_device(StaticScratch* out) {
+    static StaticScratch per_device[64];
+    static std::mutex mu;
+    int dev = 0;
+    CNB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return cnb::set_error(CNB_ERR_ARG, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!per_device[dev].ptr) {
+        float* p = nullptr;
+        CNB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials));
+        int sms = 0;
+        CNB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        per_device[dev].sm_count = sms;
+        per_device[dev].ptr = p;
+    }
+    *out = per_device[dev];
+    return CNB_OK;
+}
+
+}  // namespace
+
+extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, const float* u_re, const float* u_im,
+                                       const float* v_re, const float* v_im, float* du_re, float* du_im,
+                                       int accumulate_u, float* dv_re, float* dv_im, int accumulate_v, int B, int N,
+                                       void* stream) {
+    CNB_CHECK_ARG(g_re && g_im && u_re && u_im && v_re && v_im && dv_re && dv_im,
+                  "cnb_hadamard_bwd_static: null pointer");
+    CNB_CHECK_ARG((du_re == nullptr) == (du_im == nullptr), "cnb_hadamard_bwd_static: du planes must be a pair");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_bwd_static: B=%d N=%d", B, N);
+    CNB_CHECK_ARG(N <= kStaticMaxN, "cnb_hadamard_bwd_static: N=%d exceeds the built-in scratch (N <= %d); "
+                  "use cnb_hadamard_bwd with an arena", N, kStaticMaxN);
+    StaticScratch sc;
+    int rc = static_scratch_for_current_device(&sc);
+    if (rc != CNB_OK) return rc;
+    cudaStream_t stm = cnb::S(stream);
+    size_t total = (size_t) B * N;
+    if (du_re) {
+        bool vec = (N % 4 == 0) && all_aligned(g_re, g_im, v_re, v_im, du_re, du_im);
+        if (vec)
+            hadamard_bwd_elem_k<4><<<grid_for((total + 3) / 4, 256, sc.sm_count), 256, 0, stm>>>(
+                g_re, g_im, v_re, v_im, 0, du_re, du_im, accumulate_u, total, N);
+        else
+            hadamard_bwd_elem_k<1><<<grid_for(total, 256, sc.sm_count), 256, 0, stm>>>(
+                g_re, g_im, v_re, v_im, 0, du_re, du_im, accumulate_u, total, N);
+        CNB_LAUNCH_CHECK("hadamard_bwd_elem");
+    }
+    int col_blocks = (N + 31) / 32;
+    int chunks = (sc.sm_count * 4 + col_blocks - 1) / col_blocks;
+    chunks = std::min(chunks, std::min((B + 7) / 8, kStaticMaxChunks));
+    chunks = std::max(chunks, 1);
+    int rows = (B + chunks - 1) / chunks;
+    chunks = (B + rows - 1) / rows;
+    // every partial that stage 2 reads is written by stage 1 of this call: nothing has to start at zero
+    float* pr = sc.ptr;
+    float* pi = sc.ptr + (size_t) kStaticMaxChunks * kStaticMaxN;
+    dim3 grid(col_blocks, chunks), block(32, 8);
+    colreduce_stage1_k<0><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
+                                                   nullptr, nullptr, 0, pr, pi, B, N, rows);
+    CNB_LAUNCH_CHECK("colreduce_stage1");
+    colreduce_stage2_k<<<(N + 255) / 256, 256, 0, stm>>>(pr, pi, dv_re, dv_im, accumulate_v, chunks, N);
+    CNB_LAUNCH_CHECK("colreduce_stage2");
+    return CNB_OK;
+}

@@ -44,6 +44,7 @@ SIGNATURES = {
     "cnb_dft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
     "cnb_hadamard_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] + [_P] * 2 + [C.c_int] * 2 + [_vp]),
     "cnb_hadamard_bwd": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] + [_P] * 2 + [C.c_int] + [_P] * 2 + [C.c_int] * 3 + [_vp]),
+    "cnb_hadamard_bwd_static": (C.c_int, [_P] * 8 + [C.c_int] + [_P] * 2 + [C.c_int] * 3 + [_vp]),
     "cnb_gelu_fwd": (C.c_int, [_vp] + [_P] * 4 + [_sz, _vp]),
     "cnb_gelu_bwd": (C.c_int, [_vp] + [_P] * 6 + [_sz, C.c_int, _vp]),
     "cnb_hadamard_gelu_fwd": (C.c_int, [_vp] + [_P] * 8 + [C.c_int] * 2 + [_vp]),

@@ -132,6 +132,22 @@ int cnb_hadamard_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                      float* du_re, float* du_im, int accumulate_u,
                      float* dv_re, float* dv_im, int accumulate_v,
                      int B, int N, void* stream);
+/* Allocation-free form of cnb_hadamard_bwd for a shared v (no counterpart in the reference,
+ * which allocates scratch per call).  For callers that must not allocate device memory when
+ * they call in — a host whose own pool already owns the whole device, or a loop that cannot
+ * take the device-wide stall of cudaMalloc/cudaFree: no context, no arena; the column-reduction
+ * partials live in a 2 MiB array built into the library (per GPU that loads it, until exit).
+ * Limit: N <= CNB_STATIC_MAX_N, else CNB_ERR_ARG with a message.  The first call on a device
+ * looks up the array's device address (make that call before any stream capture starts).
+ * All calls share the one array, so two calls that overlap on the GPU (different streams)
+ * race; contents from the previous call are never read. */
+#define CNB_STATIC_MAX_N 4096
+int cnb_hadamard_bwd_static(const float* g_re, const float* g_im,
+                            const float* u_re, const float* u_im,
+                            const float* v_re, const float* v_im,
+                            float* du_re, float* du_im, int accumulate_u,
+                            float* dv_re, float* dv_im, int accumulate_v,
+                            int B, int N, void* stream);
 /* CGelu: y = gelu(re) + i gelu(im) (tanh form).  Replaces GeluGpu::gpu_gelu_forward /
  * gpu_gelu_backward (gpu/kernels.h:262-268, gpu/kernels.cpp:276-360).  CPU: impl/relu.h:119-168.
  * Backward: dz* (+)= conj(g*) (dx-dy) + g* (dx+dy), dx = gelu'(re)/2, dy = gelu'(im)/2. */
