@@ -18,11 +18,19 @@
 // 64 KB, 64-byte swizzled; 3 stages.  Each CTA issues its own plain TMA tile loads; their zero fill
 // handles every M/N/K edge.
 //
+// Scheduling.  Stream-K: the (tile, k-block) work units are cut into equal consecutive runs, one
+// per CTA and one CTA per SM, so every SM finishes together whatever the tile count; a tile whose
+// k-range is shared by several CTAs is summed with fp32 atomics into a pre-zeroed output.
+//
 // Roles.  warp 0: TMA producer; warp 1: TMEM allocation + MMA issue (one elected thread);
-// warps 2..5: epilogue (tcgen05.ld, combine, residual / accumulate, global stores).
+// warps 2..5: epilogue (tcgen05.ld, combine, stage through shared memory, coalesced 16-byte
+// stores / atomics with residual or accumulate); tensor memory is handed back to the MMA warp as
+// soon as it has been read, so the write-out overlaps the next run of MMAs.
 // Every mbarrier wait is bounded (2 s); on expiry the kernel records an error word, skips to
 // the common exit, frees its tensor memory and returns.
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 
@@ -31,7 +39,8 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 16, STAGES = 3;
 constexpr int PLANE_BYTES = BM * BK * 4;             // 8 KB: one operand plane of one stage
 constexpr int STAGE_BYTES = 8 * PLANE_BYTES;         // 64 KB
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_BYTES = 2 * 128 * 32 * 4;           // 32 KB: one epilogue round, re and im staging
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -40,6 +49,7 @@ struct TcParams {
     float* d_re; float* d_im;
     const float* r_re; const float* r_im;
     int M, N, K, conjB, accumulate;
+    int units_per_cta;        // consecutive (tile, k-block) work units per CTA (stream-K)
     int* status;
 };
 
@@ -51,6 +61,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -131,6 +145,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Staging tile of one epilogue round: 128 rows x 32 floats per plane, 16-byte chunks XOR-swizzled
+// by the row so that both the row-per-thread writes and the row-segment reads are conflict-free.
+__device__ __forceinline__ int stage_off(int row, int chunk) { return row * 32 + ((chunk ^ (row & 7)) << 2); }
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
            const __grid_constant__ CUtensorMap a_lo_re, const __grid_constant__ CUtensorMap a_lo_im,
@@ -140,24 +160,31 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     // operand stages need the alignment of their swizzle pattern; 1024 B covers every mode
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-    // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulators ready
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    float* stage_re = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
+    float* stage_im = stage_re + 128 * 32;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_BYTES);
+    // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulators ready, bars[2S+1] accumulators drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (p.N + BN - 1) / BN;
-    const int m0 = (blockIdx.x / tiles_n) * BM, n0 = (blockIdx.x % tiles_n) * BN;
+    const int tiles_m = (p.M + BM - 1) / BM;
     const int k_blocks = (p.K + BK - 1) / BK;
+    const long total_units = (long) tiles_m * tiles_n * k_blocks;
+    const long u_begin = (long) blockIdx.x * p.units_per_cta;
+    const long u_end = min(total_units, u_begin + p.units_per_cta);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_base = smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-    const uint32_t acc_bar = bar_base + 8u * (2 * STAGES);
+    const uint32_t acc_full = bar_base + 8u * (2 * STAGES);
+    const uint32_t acc_empty = bar_base + 8u * (2 * STAGES + 1);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(acc_bar, 1);
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -175,9 +202,12 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_lo_re, &a_lo_im, &b_hi_re, &b_hi_im, &b_lo_re, &b_lo_im};
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                int s = kb % STAGES;
-                uint32_t phase = (kb / STAGES) & 1;
+            long it = 0;
+            for (long u = u_begin; u < u_end; ++u, ++it) {
+                int tile = (int) (u / k_blocks), kb = (int) (u % k_blocks);
+                int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+                int s = (int) (it % STAGES);
+                uint32_t phase = (uint32_t) (it / STAGES) & 1;
                 if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, 1)) break;
                 mbar_expect_tx(full_bar(s), STAGE_BYTES);
                 uint32_t dst = smem_base + s * STAGE_BYTES;
@@ -190,63 +220,143 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                int s = kb % STAGES;
-                uint32_t phase = (kb / STAGES) & 1;
-                ok = mbar_wait(full_bar(s), phase, abort_flag, p.status, 2);
+            long it = 0;
+            int seg = 0;
+            for (long u = u_begin; u < u_end && ok; ++seg) {
+                int kb0 = (int) (u % k_blocks);
+                int kb1 = (int) min((long) k_blocks, kb0 + (u_end - u));
+                // the epilogue must have drained the previous segment's accumulators
+                ok = mbar_wait(acc_empty, (uint32_t) (seg & 1) ^ 1, abort_flag, p.status, 4);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t st = smem_base + s * STAGE_BYTES;
+                for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+                    int s = (int) (it % STAGES);
+                    uint32_t phase = (uint32_t) (it / STAGES) & 1;
+                    ok = mbar_wait(full_bar(s), phase, abort_flag, p.status, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint32_t st = smem_base + s * STAGE_BYTES;
 #pragma unroll
-                for (int j = 0; j < BK / 8; ++j) {
-                    uint32_t ko = j * 32;            // 8 TF32 = 32 bytes along K inside the swizzled row
-                    uint64_t a_hr = smem_desc_sw64(st + 0 * PLANE_BYTES + ko), a_hi_ = smem_desc_sw64(st + 1 * PLANE_BYTES + ko);
-                    uint64_t a_lr = smem_desc_sw64(st + 2 * PLANE_BYTES + ko), a_li = smem_desc_sw64(st + 3 * PLANE_BYTES + ko);
-                    uint64_t b_h = smem_desc_sw64(st + 4 * PLANE_BYTES + ko), b_l = smem_desc_sw64(st + 6 * PLANE_BYTES + ko);
-                    uint32_t first = (kb == 0 && j == 0) ? 0u : 1u;
-                    umma_tf32(tmem_base, a_lr, b_h, first);          // small terms first
-                    umma_tf32(tmem_base, a_hr, b_l, 1u);
-                    umma_tf32(tmem_base, a_hr, b_h, 1u);
-                    umma_tf32(tmem_base + 256, a_li, b_h, first);
-                    umma_tf32(tmem_base + 256, a_hi_, b_l, 1u);
-                    umma_tf32(tmem_base + 256, a_hi_, b_h, 1u);
+                    for (int j = 0; j < BK / 8; ++j) {
+                        uint32_t ko = j * 32;        // 8 TF32 = 32 bytes along K inside the swizzled row
+                        uint64_t a_hr = smem_desc_sw64(st + 0 * PLANE_BYTES + ko), a_hi_ = smem_desc_sw64(st + 1 * PLANE_BYTES + ko);
+                        uint64_t a_lr = smem_desc_sw64(st + 2 * PLANE_BYTES + ko), a_li = smem_desc_sw64(st + 3 * PLANE_BYTES + ko);
+                        uint64_t b_h = smem_desc_sw64(st + 4 * PLANE_BYTES + ko), b_l = smem_desc_sw64(st + 6 * PLANE_BYTES + ko);
+                        uint32_t first = (kb == kb0 && j == 0) ? 0u : 1u;
+                        umma_tf32(tmem_base, a_lr, b_h, first);      // small terms first
+                        umma_tf32(tmem_base, a_hr, b_l, 1u);
+                        umma_tf32(tmem_base, a_hr, b_h, 1u);
+                        umma_tf32(tmem_base + 256, a_li, b_h, first);
+                        umma_tf32(tmem_base + 256, a_hi_, b_l, 1u);
+                        umma_tf32(tmem_base + 256, a_hi_, b_h, 1u);
+                    }
+                    umma_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                 }
-                umma_commit(empty_bar(s));           // the stage is free once these MMAs have read it
+                if (ok) umma_commit(acc_full);
+                u += kb1 - kb0;
             }
-            if (ok) umma_commit(acc_bar);
         }
     } else {
         // -------------------------------------------------------------------- epilogue
         const int q = warp & 3;                      // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;
-        const int gm = m0 + row;
-        bool ok = mbar_wait(acc_bar, 0, abort_flag, p.status, 3);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const uint32_t tl = tmem_base + ((uint32_t) (q * 32) << 16);
-            const float sgn = p.conjB ? 1.f : -1.f;
+        const int et = (warp - 2) * 32 + lane;       // 0..127 within the epilogue group
+        const uint32_t tl = tmem_base + ((uint32_t) (q * 32) << 16);
+        const float sgn = p.conjB ? 1.f : -1.f;
+        const bool vec_ok = (p.N % 4 == 0) &&
+            ((reinterpret_cast<uintptr_t>(p.d_re) | reinterpret_cast<uintptr_t>(p.d_im) |
+              reinterpret_cast<uintptr_t>(p.r_re) | reinterpret_cast<uintptr_t>(p.r_im)) & 15) == 0;
+        int seg = 0;
+        for (long u = u_begin; u < u_end; ++seg) {
+            int tile = (int) (u / k_blocks), kb0 = (int) (u % k_blocks);
+            int kb1 = (int) min((long) k_blocks, kb0 + (u_end - u));
+            int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const bool partial = !(kb0 == 0 && kb1 == k_blocks);   // split tiles are summed with atomics
+            const bool add_res = p.r_re != nullptr && kb0 == 0;
+            mbar_wait(acc_full, (uint32_t) seg & 1, abort_flag, p.status, 3);
+            epi_bar_sync();                          // everyone arrives, then agree on the outcome
+            if (*abort_flag) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float a[16], b[16], e[16], f[16];
-                tmem_ld16(tl + c, a);               // A_re.B_re
-                tmem_ld16(tl + 128 + c, b);         // A_re.B_im
-                tmem_ld16(tl + 256 + c, e);         // A_im.B_re
-                tmem_ld16(tl + 384 + c, f);         // A_im.B_im
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (gm < p.M) {
-                    size_t o = (size_t) gm * p.N + n0 + c;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                {
+                    float a[16], f[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        if (n0 + c + i >= p.N) break;
-                        float vr = a[i] + sgn * f[i];          // re: ar.br -/+ ai.bi
-                        float vi = e[i] - sgn * b[i];          // im: ai.br +/- ar.bi
-                        if (p.r_re) { vr += p.r_re[o + i]; vi += p.r_im[o + i]; }
-                        if (p.accumulate) { vr += p.d_re[o + i]; vi += p.d_im[o + i]; }
-                        p.d_re[o + i] = vr;
-                        p.d_im[o + i] = vi;
+                    for (int h = 0; h < 2; ++h) {
+                        tmem_ld16(tl + c0 + 16 * h, a);            // A_re.B_re
+                        tmem_ld16(tl + 384 + c0 + 16 * h, f);      // A_im.B_im
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4)
+                            *reinterpret_cast<float4*>(stage_re + stage_off(row, 4 * h + i / 4)) =
+                                make_float4(a[i] + sgn * f[i], a[i + 1] + sgn * f[i + 1], a[i + 2] + sgn * f[i + 2],
+                                            a[i + 3] + sgn * f[i + 3]);
                     }
                 }
+                {
+                    float b[16], e[16];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        tmem_ld16(tl + 128 + c0 + 16 * h, b);      // A_re.B_im
+                        tmem_ld16(tl + 256 + c0 + 16 * h, e);      // A_im.B_re
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4)
+                            *reinterpret_cast<float4*>(stage_im + stage_off(row, 4 * h + i / 4)) =
+                                make_float4(e[i] - sgn * b[i], e[i + 1] - sgn * b[i + 1], e[i + 2] - sgn * b[i + 2],
+                                            e[i + 3] - sgn * b[i + 3]);
+                    }
+                }
+                if (c0 + 32 == BN) {
+                    // last TMEM read of this segment done: hand the accumulators back to the MMA warp
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                }
+                epi_bar_sync();
+                if (c0 + 32 == BN && et == 0) mbar_arrive(acc_empty);
+                // coalesced write-out: each warp instruction covers 4 rows x 128 contiguous bytes
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    int idx = et + 128 * j;
+                    int r = idx >> 3, ch = idx & 7;
+                    int gm = m0 + r, gn = n0 + c0 + ch * 4;
+                    if (gm >= p.M || gn >= p.N) continue;
+                    float4 vr = *reinterpret_cast<const float4*>(stage_re + stage_off(r, ch));
+                    float4 vi = *reinterpret_cast<const float4*>(stage_im + stage_off(r, ch));
+                    size_t o = (size_t) gm * p.N + gn;
+                    if (vec_ok) {
+                        if (add_res) {
+                            float4 xr = *reinterpret_cast<const float4*>(p.r_re + o), xi = *reinterpret_cast<const float4*>(p.r_im + o);
+                            vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
+                            vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                        }
+                        if (partial) {
+                            atomicAdd(reinterpret_cast<float4*>(p.d_re + o), vr);
+                            atomicAdd(reinterpret_cast<float4*>(p.d_im + o), vi);
+                        } else {
+                            if (p.accumulate) {
+                                float4 xr = *reinterpret_cast<const float4*>(p.d_re + o), xi = *reinterpret_cast<const float4*>(p.d_im + o);
+                                vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
+                                vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                            }
+                            *reinterpret_cast<float4*>(p.d_re + o) = vr;
+                            *reinterpret_cast<float4*>(p.d_im + o) = vi;
+                        }
+                    } else {
+                        float wr[4] = {vr.x, vr.y, vr.z, vr.w}, wi[4] = {vi.x, vi.y, vi.z, vi.w};
+                        for (int k = 0; k < 4 && gn + k < p.N; ++k) {
+                            float xr = wr[k], xi = wi[k];
+                            if (add_res) { xr += p.r_re[o + k]; xi += p.r_im[o + k]; }
+                            if (partial) { atomicAdd(p.d_re + o + k, xr); atomicAdd(p.d_im + o + k, xi); }
+                            else {
+                                if (p.accumulate) { xr += p.d_re[o + k]; xi += p.d_im[o + k]; }
+                                p.d_re[o + k] = xr; p.d_im[o + k] = xi;
+                            }
+                        }
+                    }
+                }
+                epi_bar_sync();                      // staging is reused by the next round
             }
+            u += kb1 - kb0;
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
@@ -396,13 +506,29 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
         if ((rc = make_map(&maps[q], ap[q], M, K)) != CNB_OK) return rc;
         if ((rc = make_map(&maps[4 + q], bp[q], N, K)) != CNB_OK) return rc;
     }
+    // stream-K: the (tile, k-block) units are dealt out in equal consecutive runs, one run per CTA,
+    // one CTA per SM; a tile whose k-range is shared by several CTAs is summed with atomics
+    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int k_blocks = (K + BK - 1) / BK;
+    long total = (long) tiles * k_blocks;
+    long min_units = 8;                                  // do not split below 8 k-blocks per CTA
+    long ctas = std::min<long>(ctx->sm_count, std::max<long>(1, total / min_units));
+    if (tiles >= ctx->sm_count * 4) ctas = tiles;         // many tiles: whole tiles, no atomics
+    long upc = (total + ctas - 1) / ctas;
+    if (tiles >= ctx->sm_count * 4) upc = k_blocks;
+    ctas = (total + upc - 1) / upc;
+    bool splits_tiles = (upc % k_blocks) != 0;
+    if (splits_tiles && !accumulate) {
+        CNB_CUDA(cudaMemsetAsync(d_re, 0, (size_t) M * N * sizeof(float), st));
+        CNB_CUDA(cudaMemsetAsync(d_im, 0, (size_t) M * N * sizeof(float), st));
+    }
     TcParams p;
     p.d_re = d_re; p.d_im = d_im; p.r_re = r_re; p.r_im = r_im;
     p.M = M; p.N = N; p.K = K; p.conjB = conjB; p.accumulate = accumulate;
+    p.units_per_cta = (int) upc;
     p.status = ctx->d_status;
-    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    cgemm_tc_k<<<tiles, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
-                                                      maps[7], p);
+    cgemm_tc_k<<<(int) ctas, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
+                                                           maps[7], p);
     CNB_LAUNCH_CHECK("cgemm_tc");
     return CNB_OK;
 }

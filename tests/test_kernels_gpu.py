@@ -39,8 +39,11 @@ def _pair(z):
     return (z.real, z.imag)
 
 
+# the last rows exercise the tensor-core GEMM's schedules: k-split tiles summed with atomics,
+# runs that cover whole tiles plus a split remainder, one-tile-per-CTA grids, ragged M/N/K edges
 @pytest.mark.parametrize("B,n_in,n_out", [(1, 1, 1), (7, 48, 40), (64, 784, 10), (33, 100, 130), (256, 512, 384),
-                                          (128, 1024, 1024)])
+                                          (128, 1024, 1024), (4096, 256, 1024), (3072, 64, 3200), (200, 100, 72),
+                                          (1000, 36, 1000)])
 def test_linear_three_products(ctx, B, n_in, n_out):
     rng = np.random.default_rng(B * 1000 + n_in)
     x, w, g = _rand(rng, B, n_in), _rand(rng, n_out, n_in, scale=n_in ** -0.5), _rand(rng, B, n_out)
