@@ -24,7 +24,7 @@ struct cnb_ctx {
     float* scratch = nullptr;         // column-reduction partials and GEMM operand staging
     size_t scratch_bytes = 0;
     std::map<int, cnb_twiddle> twiddles;
-    void* gemm_ws = nullptr;          // tensor-core GEMM workspace (see cgemm_tc.cu)
+    bool force_dft_gemm = false;      // FourierTrans as a GEMM even where the FFT kernel applies
 };
 
 namespace cnb {
@@ -58,6 +58,11 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
                  float* d_im, int M, int N, int K, int accumulate, cudaStream_t st);
 size_t cgemm_tc_workspace_bytes(int M, int N, int K);
 void cgemm_tc_release(cnb_ctx* ctx);
+
+// Shared-memory FFT (N = 256, 1024, 4096); inverse = conjugate direction.
+bool fft_supported(int N);
+int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, int B, int N, int inverse,
+            int accumulate, cudaStream_t st);
 
 // [R, C] -> [C, R] transpose of a re/im plane pair (operand staging for the K-major GEMM).
 int transpose_planes(const float* s_re, const float* s_im, float* d_re, float* d_im,

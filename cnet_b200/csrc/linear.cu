@@ -99,6 +99,10 @@ int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, float* y_re,
                 void* stream) {
     CNB_CHECK_ARG(ctx && x_re && x_im && y_re && y_im, "cnb_dft_fwd: null pointer");
     CNB_CHECK_ARG(B > 0 && N > 0 && N <= 16384, "cnb_dft_fwd: B=%d N=%d (N <= 16384)", B, N);
+    if (cnb::fft_supported(N) && !ctx->force_dft_gemm) {
+        cnb::g_last_engine = 3;
+        return cnb::fft_run(ctx, x_re, x_im, y_re, y_im, B, N, 0, 0, cnb::S(stream));
+    }
     cnb_twiddle t;
     int rc = get_twiddle(ctx, N, cnb::S(stream), &t);
     if (rc != CNB_OK) return rc;
@@ -111,6 +115,10 @@ int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re
     CNB_CHECK_ARG(ctx && g_re && g_im && dx_re && dx_im, "cnb_dft_bwd: null pointer");
     CNB_CHECK_ARG(B > 0 && N > 0 && N <= 16384, "cnb_dft_bwd: B=%d N=%d (N <= 16384)", B, N);
     cudaStream_t st = cnb::S(stream);
+    if (cnb::fft_supported(N) && !ctx->force_dft_gemm) {
+        cnb::g_last_engine = 3;
+        return cnb::fft_run(ctx, g_re, g_im, dx_re, dx_im, B, N, 1, accumulate, st);
+    }
     cnb_twiddle t;
     int rc = get_twiddle(ctx, N, st, &t);
     if (rc != CNB_OK) return rc;
@@ -132,6 +140,12 @@ size_t cnb_linear_workspace(int B, int in, int out) {
     if (cnb::cgemm_tc_shape_ok(B, in, out)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(B, in, out));
     if (cnb::cgemm_tc_shape_ok(out, in, B)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(out, in, B));
     return w;
+}
+
+int cnb_set_dft_engine(cnb_ctx* ctx, int force_gemm) {
+    CNB_CHECK_ARG(ctx, "cnb_set_dft_engine: null context");
+    ctx->force_dft_gemm = force_gemm != 0;
+    return CNB_OK;
 }
 
 int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes) {

@@ -42,6 +42,7 @@ SIGNATURES = {
     "cnb_reserve_scratch": (C.c_int, [_vp, _sz]),
     "cnb_dft_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 2 + [_vp]),
     "cnb_dft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
+    "cnb_set_dft_engine": (C.c_int, [_vp, C.c_int]),
     "cnb_hadamard_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] + [_P] * 2 + [C.c_int] * 2 + [_vp]),
     "cnb_hadamard_bwd": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] + [_P] * 2 + [C.c_int] + [_P] * 2 + [C.c_int] * 3 + [_vp]),
     "cnb_hadamard_bwd_static": (C.c_int, [_P] * 8 + [C.c_int] + [_P] * 2 + [C.c_int] * 3 + [_vp]),

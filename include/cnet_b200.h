@@ -114,6 +114,10 @@ int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
  * CPU: impl/ft.h:57-80. */
 int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                 float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
+/* N = 256, 1024, 4096 run as a shared-memory FFT (one read + one write of the tensor); any other
+ * N, or every N after cnb_set_dft_engine(ctx, 1), as a complex GEMM against the twiddle matrix.
+ * cnb_last_gemm_engine() reports 3 after an FFT-kernel call. */
+int cnb_set_dft_engine(cnb_ctx* ctx, int force_gemm);
 
 /* --------------------------------------------------------- element-wise layers
  * Hadamard y = u o v; v is one vector [N] shared by the batch (v_batched = 0) or [B,N].

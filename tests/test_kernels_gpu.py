@@ -65,14 +65,30 @@ def test_linear_three_products(ctx, B, n_in, n_out):
     assert util.relerr(dw2, _pair(2 * (G.T @ np.conj(X)))) < 1e-5
 
 
-@pytest.mark.parametrize("B,N", [(3, 8), (5, 100), (64, 784), (32, 1024)])
+@pytest.mark.parametrize("B,N", [(3, 8), (5, 100), (64, 784), (32, 1024), (37, 1024), (5, 256), (3, 4096),
+                                 (600, 1024)])
 def test_fourier_forward_backward(ctx, B, N):
     rng = np.random.default_rng(N)
     x, g = _rand(rng, B, N), _rand(rng, B, N)
+    want_f = _pair(np.fft.fft(_c(x), axis=1) / np.sqrt(N))
+    want_b = _pair(np.fft.ifft(_c(g), axis=1) * np.sqrt(N))
     y = _host(ctx.dft_fwd(_dev(x)))
-    assert util.relerr(y, _pair(np.fft.fft(_c(x), axis=1) / np.sqrt(N))) < 1e-5
+    assert util.relerr(y, want_f) < 1e-5
+    # N = 256, 1024, 4096 use the shared-memory FFT kernel, everything else the DFT GEMM
+    assert (ctx.last_gemm_engine() == 3) == (N in (256, 1024, 4096))
     dx = _host(ctx.dft_bwd(_dev(g)))
-    assert util.relerr(dx, _pair(np.fft.ifft(_c(g), axis=1) * np.sqrt(N))) < 1e-5
+    assert util.relerr(dx, want_b) < 1e-5
+    acc = _dev((want_b[0].astype(np.float32), want_b[1].astype(np.float32)))
+    dx2 = _host(ctx.dft_bwd(_dev(g), out=acc))
+    assert util.relerr(dx2, (2 * want_b[0], 2 * want_b[1])) < 1e-5
+    if N in (256, 1024, 4096):       # the GEMM form of the same transform agrees
+        ctx.lib.cnb_set_dft_engine(ctx.h, 1)
+        try:
+            assert util.relerr(_host(ctx.dft_fwd(_dev(x))), want_f) < 1e-5
+            assert ctx.last_gemm_engine() != 3
+            assert util.relerr(_host(ctx.dft_bwd(_dev(g))), want_b) < 1e-5
+        finally:
+            ctx.lib.cnb_set_dft_engine(ctx.h, 0)
 
 
 @pytest.mark.parametrize("B,N", [(1, 1), (5, 7), (64, 784), (300, 1024), (9, 130)])
