@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <algorithm>
 #include <map>
 #include <string>
 
@@ -58,6 +59,16 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
                  float* d_im, int M, int N, int K, int accumulate, cudaStream_t st);
 size_t cgemm_tc_workspace_bytes(int M, int N, int K);
 void cgemm_tc_release(cnb_ctx* ctx);
+
+// Skinny Linear (out <= 16): HBM-bound fp32 kernels.
+bool skinny_ok(int B, int in, int out);
+size_t skinny_workspace_bytes(int B, int in, int out, int sm_count);
+int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, const float* wi, float* yr, float* yi,
+               int B, int in, int out, cudaStream_t st);
+int skinny_bwd_x(cnb_ctx* ctx, const float* gr, const float* gi, const float* wr, const float* wi, float* dr,
+                 float* di, int B, int in, int out, int accumulate, cudaStream_t st);
+int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr, const float* xi, float* dr,
+                 float* di, int B, int in, int out, int accumulate, cudaStream_t st);
 
 // Shared-memory FFT (N = 256, 1024, 4096); inverse = conjugate direction.
 bool fft_supported(int N);

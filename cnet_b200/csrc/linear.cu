@@ -52,6 +52,10 @@ int cnb_linear_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, const flo
     CNB_CHECK_ARG((res_re == nullptr) == (res_im == nullptr), "cnb_linear_fwd: residual planes must be a pair");
     CNB_CHECK_ARG(B > 0 && in > 0 && out > 0, "cnb_linear_fwd: B=%d in=%d out=%d", B, in, out);
     cudaStream_t st = cnb::S(stream);
+    if (cnb::skinny_ok(B, in, out) && !res_re) {
+        cnb::g_last_engine = 4;
+        return cnb::skinny_fwd(ctx, x_re, x_im, w_re, w_im, y_re, y_im, B, in, out, st);
+    }
     if (cnb::cgemm_tc_shape_ok(B, out, in)) {
         cnb::g_last_engine = 1;
         return cnb::cgemm_tc_nt(ctx, x_re, x_im, w_re, w_im, 0, res_re, res_im, y_re, y_im, B, out, in, 0, st);
@@ -67,6 +71,10 @@ int cnb_linear_bwd_x(cnb_ctx* ctx, const float* g_re, const float* g_im, const f
     CNB_CHECK_ARG(B > 0 && in > 0 && out > 0, "cnb_linear_bwd_x: B=%d in=%d out=%d", B, in, out);
     cudaStream_t st = cnb::S(stream);
     // dX*[b,i] = sum_o G[b,o] conj(W[o,i]) : M = B, N = in, K = out; B-operand(n=i,k=o) = W[o,i]
+    if (cnb::skinny_ok(B, in, out)) {
+        cnb::g_last_engine = 4;
+        return cnb::skinny_bwd_x(ctx, g_re, g_im, w_re, w_im, dx_re, dx_im, B, in, out, accumulate, st);
+    }
     if (cnb::cgemm_tc_shape_ok(B, in, out)) {
         // the B operand (n = i, k = o) is W stored [K = out, N = in]: transposed while it is split
         cnb::g_last_engine = 1;
@@ -84,6 +92,10 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im, const f
     CNB_CHECK_ARG(B > 0 && in > 0 && out > 0, "cnb_linear_bwd_w: B=%d in=%d out=%d", B, in, out);
     cudaStream_t st = cnb::S(stream);
     // dW*[o,i] = sum_b G[b,o] conj(X[b,i]) : M = out, N = in, K = B
+    if (cnb::skinny_ok(B, in, out)) {
+        cnb::g_last_engine = 4;
+        return cnb::skinny_bwd_w(ctx, g_re, g_im, x_re, x_im, dw_re, dw_im, B, in, out, accumulate, st);
+    }
     if (cnb::cgemm_tc_shape_ok(out, in, B)) {
         // both operands are stored [K = B, rows]: transposed while they are split
         cnb::g_last_engine = 1;
@@ -136,6 +148,7 @@ int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re
 /* Scratch the three Linear products and the column reductions of one layer may need. */
 size_t cnb_linear_workspace(int B, int in, int out) {
     size_t w = 0;
+    if (cnb::skinny_ok(B, in, out)) return cnb::skinny_workspace_bytes(B, in, out, 256);
     if (cnb::cgemm_tc_shape_ok(B, out, in)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(B, out, in));
     if (cnb::cgemm_tc_shape_ok(B, in, out)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(B, in, out));
     if (cnb::cgemm_tc_shape_ok(out, in, B)) w = std::max(w, cnb::cgemm_tc_workspace_bytes(out, in, B));

@@ -100,7 +100,8 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im,
 size_t cnb_linear_workspace(int B, int in, int out);
 int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes);
 /* Which GEMM engine the last cnb_linear_* call on this thread used:
- * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (skinny / ragged shapes). */
+ * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (ragged shapes),
+ * 4 = skinny fp32 kernels (out <= 16, HBM-bound). */
 int cnb_last_gemm_engine(void);
 
 /* ---------------------------------------------------------------- FourierTrans

@@ -41,7 +41,7 @@ def _pair(z):
 
 # the last rows exercise the tensor-core GEMM's schedules: k-split tiles summed with atomics,
 # runs that cover whole tiles plus a split remainder, one-tile-per-CTA grids, ragged M/N/K edges
-@pytest.mark.parametrize("B,n_in,n_out", [(1, 1, 1), (7, 48, 40), (64, 784, 10), (33, 100, 130), (256, 512, 384),
+@pytest.mark.parametrize("B,n_in,n_out", [(1, 1, 1), (7, 48, 40), (64, 784, 10), (4095, 1024, 10), (3, 33, 16), (33, 100, 130), (256, 512, 384),
                                           (128, 1024, 1024), (4096, 256, 1024), (3072, 64, 3200), (200, 100, 72),
                                           (1000, 36, 1000)])
 def test_linear_three_products(ctx, B, n_in, n_out):
@@ -52,7 +52,8 @@ def test_linear_three_products(ctx, B, n_in, n_out):
     y = _host(ctx.linear_fwd(_dev(x), _dev(w)))
     assert util.relerr(y, _pair(X @ W.T)) < 1e-5
     # square shapes run on the tcgen05 tiles, skinny / tiny ones on the fp32 SIMT tiles
-    assert ctx.last_gemm_engine() == (1 if (B >= 64 and n_out >= 64 and n_in >= 32 and n_in % 4 == 0) else 2)
+    want_engine = 4 if (n_out <= 16 and n_in >= 32) else 1 if (B >= 64 and n_out >= 64 and n_in >= 32 and n_in % 4 == 0) else 2
+    assert ctx.last_gemm_engine() == want_engine
     yr = _host(ctx.linear_fwd(_dev(x), _dev(w), res=_dev(r)))
     assert util.relerr(yr, _pair(X @ W.T + _c(r))) < 1e-5
     dx = _host(ctx.linear_bwd_x(_dev(g), _dev(w)))
