@@ -48,7 +48,15 @@ class GradBucketReducer:
 
 
 class DataParallelTrainer:
-    def __init__(self, builder, builder_kwargs, global_batch, lr, device=0, seed=0, fuse=True):
+    """One rank of a data-parallel training job (or the whole job when there is one rank).
+
+    comm = "nccl": the host facade owns an NCCL communicator and issues the bucket all-reduces
+    itself on a communication stream (capturable in a CUDA graph together with the kernels);
+    comm = "torch": the buckets are handed to torch.distributed through a Python hook (any backend;
+    what the CPU tests exercise with gloo).  "auto" picks "nccl" when the job has several ranks.
+    """
+
+    def __init__(self, builder, builder_kwargs, global_batch, lr, device=0, seed=0, fuse=True, comm="auto"):
         import torch
         import torch.distributed as dist
         from .net import Net
@@ -59,13 +67,21 @@ class DataParallelTrainer:
         self.lo, self.hi = shard_bounds(global_batch, self.world, self.rank)
         self.local_batch = self.hi - self.lo
         self.lr = lr
+        self.graph = False
+        torch.cuda.set_device(device)
+        self.stream = torch.cuda.Stream(device=device)     # a capturable (non-default) stream
         self.net = Net(device=device)
         self.spec = builder(self.net, **builder_kwargs)
         for uid, (re, im) in configs.init_weights(self.spec, seed).items():
             self.net.set_values(uid, re, im)
-        self.net.allocate(self.local_batch, fuse=fuse)
-        self.reducer = GradBucketReducer()
-        if self.reducer.active:
+        self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream)
+        self.comm = ("nccl" if self.world > 1 else "none") if comm == "auto" else comm
+        self.reducer = GradBucketReducer() if self.comm == "torch" else None
+        if self.world > 1 and self.comm == "nccl":
+            box = [self.net.dp_unique_id() if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            self.net.dp_init(box[0], self.rank, self.world)
+        elif self.reducer is not None and self.reducer.active:
             arena = self.net.arena
             base = arena.data_ptr()
 
@@ -82,12 +98,44 @@ class DataParallelTrainer:
         else:
             self.net.upload(x=host_in, labels=host_labels, batch=self.local_batch)
 
+    def _step_eager(self):
+        with self.torch.cuda.stream(self.stream):
+            self.net.forward()
+            self.net.backward()
+            if self.reducer is not None:
+                self.reducer.finish()
+            self.net.update_inputs(self.lr / self.global_batch)
+
+    def capture(self):
+        """Capture forward + backward (+ bucket all-reduces) + update into one CUDA graph.
+
+        The step is a fixed sequence of ~120 launches on static arena addresses; replaying it as a
+        graph removes the per-launch host cost, which dominates once the per-GPU batch is small.
+        Call after at least one eager step (twiddle tables, kernel attributes and the NCCL
+        communicator are set up outside the capture).
+        """
+        if self.comm == "torch" and self.world > 1:
+            raise RuntimeError("graph capture needs comm='nccl' (collectives issued by the host facade)")
+        self.torch.cuda.synchronize()
+        self.net.capture_begin()
+        try:
+            self.net.forward()
+            self.net.backward()
+            self.net.update_inputs(self.lr / self.global_batch)
+        finally:
+            self.net.capture_end()
+        self.torch.cuda.synchronize()
+        self.graph = True
+
     def step_resident(self):
         """forward + backward (+ overlapped gradient all-reduce) + update on the resident batch."""
-        self.net.forward()
-        self.net.backward()
-        self.reducer.finish()
-        self.net.update_inputs(self.lr / self.global_batch)
+        if self.graph:
+            self.net.graph_launch()
+        else:
+            self._step_eager()
+
+    def kernels_per_step(self):
+        return self.net.graph_kernel_count() if self.graph else None
 
     def step(self, host_in, host_labels):
         self.upload(host_in, host_labels)

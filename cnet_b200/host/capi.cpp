@@ -94,4 +94,17 @@ int cnh_grad_arena(cnh_net* n, void** p, size_t* count, int* nb) {
 int cnh_weight_arena(cnh_net* n, void** p, size_t* count) { *p = n->net.weightArena(count); return 0; }
 void* cnh_context(cnh_net* n) { return n->net.context(); }
 
+int cnh_dp_unique_id(char* out128) {
+	std::string err;
+	return CNet::ncclUniqueId(out128, &err) ? 0 : CNB_ERR_CUDA;
+}
+int cnh_dp_init(cnh_net* n, const char* id128, int rank, int nranks) {
+	n->net.setDataParallel(id128, rank, nranks); return status(n);
+}
+int cnh_dp_async_error(cnh_net* n) { return n->net.dataParallelError(); }
+int cnh_capture_begin(cnh_net* n) { n->net.beginCapture(); return status(n); }
+int cnh_capture_end(cnh_net* n) { n->net.endCapture(); return status(n); }
+int cnh_graph_launch(cnh_net* n) { n->net.launchGraph(); return status(n); }
+unsigned long long cnh_graph_kernel_count(cnh_net* n) { return n->net.graphKernelCount(); }
+
 }  // extern "C"

@@ -9,6 +9,8 @@
 #include <cstring>
 #include <iostream>
 
+#include <cuda_runtime.h>
+
 namespace cnet_b200 {
 
 namespace {
@@ -288,6 +290,7 @@ float CrossEntropy::loss(int sample) {
 CNet::CNet() {}
 
 CNet::~CNet() {
+	if (graph_exec_) cudaGraphExecDestroy((cudaGraphExec_t) graph_exec_);
 	for (auto f : func_list_) delete f;
 	if (ctx_) cnb_destroy(ctx_);
 }
@@ -683,19 +686,68 @@ void CNet::backward() {
 		CFunc* f = *it;
 		if (!f->fused_away_ || dynamic_cast<Residual*>(f)) f->backward();
 		if (!ok_) return;
-		while (hook_ && next_bucket < buckets_.size() && buckets_[next_bucket].last_writer == f) {
-			const Bucket& b = buckets_[next_bucket];
-			int rc = hook_(hook_user_, wgrad_base_ + b.begin, b.count, (int) next_bucket, (int) buckets_.size());
-			if (rc != 0) { fail(CNB_ERR_DEVICE, "gradient bucket hook returned " + std::to_string(rc)); return; }
+		while (next_bucket < buckets_.size() && buckets_[next_bucket].last_writer == f) {
+			if (!reduceBucket(next_bucket)) return;
 			++next_bucket;
 		}
 	}
-	while (hook_ && next_bucket < buckets_.size()) {
-		const Bucket& b = buckets_[next_bucket];
-		int rc = hook_(hook_user_, wgrad_base_ + b.begin, b.count, (int) next_bucket, (int) buckets_.size());
-		if (rc != 0) { fail(CNB_ERR_DEVICE, "gradient bucket hook returned " + std::to_string(rc)); return; }
+	while (next_bucket < buckets_.size()) {
+		if (!reduceBucket(next_bucket)) return;
 		++next_bucket;
 	}
+}
+
+bool CNet::reduceBucket(size_t k) {
+	const Bucket& b = buckets_[k];
+	if (nccl_.active()) {
+		if (!nccl_.allReduce(wgrad_base_ + b.begin, b.count, stream_)) { fail(CNB_ERR_CUDA, "all-reduce: " + nccl_.error()); return false; }
+	}
+	if (hook_) {
+		int rc = hook_(hook_user_, wgrad_base_ + b.begin, b.count, (int) k, (int) buckets_.size());
+		if (rc != 0) { fail(CNB_ERR_DEVICE, "gradient bucket hook returned " + std::to_string(rc)); return false; }
+	}
+	return true;
+}
+
+bool CNet::setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nranks) {
+	if (!ctx_) { fail(CNB_ERR_ARG, "setDataParallel: allocateOnGpu first"); return false; }
+	cudaSetDevice(device_);
+	if (!nccl_.init(id, rank, nranks)) { fail(CNB_ERR_CUDA, "setDataParallel: " + nccl_.error()); return false; }
+	return true;
+}
+
+bool CNet::beginCapture() {
+	if (!ctx_ || capturing_) { fail(CNB_ERR_ARG, "beginCapture: not allocated / already capturing"); return false; }
+	if (!stream_) { fail(CNB_ERR_ARG, "beginCapture: the legacy default stream cannot be captured; setStream first"); return false; }
+	cudaError_t e = cudaStreamBeginCapture((cudaStream_t) stream_, cudaStreamCaptureModeThreadLocal);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("cudaStreamBeginCapture: ") + cudaGetErrorString(e)); return false; }
+	capturing_ = true;
+	graph_launches_ = cnb_launch_count();
+	return true;
+}
+
+bool CNet::endCapture() {
+	if (!capturing_) { fail(CNB_ERR_ARG, "endCapture: no capture in progress"); return false; }
+	capturing_ = false;
+	graph_launches_ = cnb_launch_count() - graph_launches_;
+	cudaGraph_t g = nullptr;
+	cudaError_t e = cudaStreamEndCapture((cudaStream_t) stream_, &g);
+	if (e != cudaSuccess || !g) { fail(CNB_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e)); return false; }
+	if (!ok_) { cudaGraphDestroy(g); return false; }       // a layer failed while capturing
+	if (graph_exec_) { cudaGraphExecDestroy((cudaGraphExec_t) graph_exec_); graph_exec_ = nullptr; }
+	cudaGraphExec_t x = nullptr;
+	e = cudaGraphInstantiate(&x, g, 0);
+	cudaGraphDestroy(g);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e)); return false; }
+	graph_exec_ = x;
+	return true;
+}
+
+bool CNet::launchGraph() {
+	if (!graph_exec_) { fail(CNB_ERR_ARG, "launchGraph: capture a step first"); return false; }
+	cudaError_t e = cudaGraphLaunch((cudaGraphExec_t) graph_exec_, (cudaStream_t) stream_);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("cudaGraphLaunch: ") + cudaGetErrorString(e)); return false; }
+	return true;
 }
 
 void CNet::backward(int label) {
@@ -706,6 +758,7 @@ void CNet::backward(int label) {
 
 void CNet::updateInputs(float lr) {
 	if (!ctx_ || !wgrad_count_) return;
+	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
 	int rc = cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_);
 	if (rc != CNB_OK) fail(rc, "updateInputs");
 }

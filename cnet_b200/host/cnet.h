@@ -25,6 +25,7 @@
 #include <vector>
 
 #include "../../include/cnet_b200.h"
+#include "dp_nccl.h"
 
 namespace cnet_b200 {
 
@@ -329,8 +330,11 @@ class CNet {
 	std::vector<Bucket> buckets_;
 	BucketHook hook_ = nullptr;
 	void* hook_user_ = nullptr;
-	void* pinned_ = nullptr;                        // staging for pageable host batches
-	size_t pinned_bytes_ = 0;
+	NcclGroup nccl_;                                // native data parallelism (setDataParallel)
+	void* graph_exec_ = nullptr;                    // cudaGraphExec_t of a captured step
+	bool capturing_ = false;
+	unsigned long long graph_launches_ = 0;         // kernels inside the captured step
+	bool reduceBucket(size_t index);
 
 	void fail(int status, const std::string& where);
 	bool planFusion();
@@ -341,6 +345,18 @@ public:
 	void setStream(void* stream) { stream_ = stream; }
 	void setFusion(bool on) { fuse_ = on; }
 	void setBucketHook(BucketHook hook, void* user) { hook_ = hook; hook_user_ = user; }
+	// Native NCCL data parallelism: every rank calls this with the id made by ncclUniqueId() on one
+	// rank.  backward() then all-reduces each finished gradient bucket on a communication stream and
+	// updateInputs() waits for them; the caller passes lr / global_batch.
+	static bool ncclUniqueId(char out[kNcclUniqueIdBytes], std::string* err) { return NcclGroup::uniqueId(out, err); }
+	bool setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nranks);
+	int dataParallelError() { return nccl_.asyncError(); }
+	// CUDA graph of a step: beginCapture(); forward(); backward(); updateInputs(lr); endCapture();
+	// then launchGraph() replays it (same batch buffers, labels and learning rate).
+	bool beginCapture();
+	bool endCapture();
+	bool launchGraph();
+	unsigned long long graphKernelCount() const { return graph_launches_; }
 	virtual ~CNet();
 
 	int add(CFunc* func);

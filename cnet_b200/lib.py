@@ -87,6 +87,13 @@ SIGNATURES = {
     "cnh_grad_arena": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_sz), C.POINTER(C.c_int)]),
     "cnh_weight_arena": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_sz)]),
     "cnh_context": (_vp, [_vp]),
+    "cnh_dp_unique_id": (C.c_int, [C.c_char_p]),
+    "cnh_dp_init": (C.c_int, [_vp, C.c_char_p, C.c_int, C.c_int]),
+    "cnh_dp_async_error": (C.c_int, [_vp]),
+    "cnh_capture_begin": (C.c_int, [_vp]),
+    "cnh_capture_end": (C.c_int, [_vp]),
+    "cnh_graph_launch": (C.c_int, [_vp]),
+    "cnh_graph_kernel_count": (C.c_ulonglong, [_vp]),
 }
 
 _lib = None

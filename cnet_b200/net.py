@@ -114,6 +114,11 @@ class Net:
     def _set_arena(self, nbytes, ext):
         self.lib.cnh_set_device(self.h, self.device, nbytes, ext)
 
+    def set_stream(self, stream):
+        """Stream (raw cudaStream_t value) every following call launches on."""
+        self.lib.cnh_set_stream(self.h, C.c_void_p(stream))
+        self.stream = stream
+
     def upload(self, x=None, tokens=None, labels=None, batch=None):
         """batchToGpu: host planes [B, n] (numpy or pinned CPU torch tensors) or tokens [B, T]; labels [B]."""
         if tokens is not None:
@@ -146,6 +151,30 @@ class Net:
 
     def sync(self):
         self._check(self.lib.cnh_sync(self.h), "sync")
+
+    # ------------------------------------------------- data parallel, graphs
+    def dp_init(self, unique_id, rank, nranks):
+        """setDataParallel: join the NCCL communicator made from `unique_id` (128 bytes)."""
+        self._check(self.lib.cnh_dp_init(self.h, unique_id, rank, nranks), "setDataParallel")
+
+    @staticmethod
+    def dp_unique_id():
+        buf = C.create_string_buffer(128)
+        if _lib.load().cnh_dp_unique_id(buf) != 0:
+            raise _lib.CnetError("ncclGetUniqueId failed (is libnccl.so.2 loadable?)")
+        return buf.raw
+
+    def capture_begin(self):
+        self._check(self.lib.cnh_capture_begin(self.h), "beginCapture")
+
+    def capture_end(self):
+        self._check(self.lib.cnh_capture_end(self.h), "endCapture")
+
+    def graph_launch(self):
+        self._check(self.lib.cnh_graph_launch(self.h), "launchGraph")
+
+    def graph_kernel_count(self):
+        return self.lib.cnh_graph_kernel_count(self.h)
 
     def context(self):
         return C.c_void_p(self.lib.cnh_context(self.h))

@@ -54,6 +54,22 @@ int cnh_grad_arena(cnh_net* net, void** dev_ptr, size_t* count, int* n_buckets);
 int cnh_weight_arena(cnh_net* net, void** dev_ptr, size_t* count);
 void* cnh_context(cnh_net* net);                                             /* the cnb_ctx* of the net */
 
+/* Data parallelism (no counterpart in the reference, which is single-GPU: gpu/gpu_func.h:38-40; the
+ * intra-GPU analogue is gpu_grad_from_clones, gpu/kernels.cpp:566-598).  One rank makes a 128-byte
+ * NCCL id, every rank (one per GPU) passes it in after cnh_allocate; cnh_backward then sums every
+ * finished gradient bucket over the ranks on a communication stream and cnh_update waits for them.
+ * The caller gives cnh_update lr / global_batch. */
+int cnh_dp_unique_id(char* out128);
+int cnh_dp_init(cnh_net* net, const char* id128, int rank, int nranks);
+int cnh_dp_async_error(cnh_net* net);                                        /* 0 = communicator healthy */
+/* CUDA graph of a step: begin; cnh_forward; cnh_backward; cnh_update; end; then cnh_graph_launch
+ * replays it on the net's stream (replaces the per-launch cudaDeviceSynchronize cadence of
+ * gpu/gpu_func.h:645-681).  Needs a non-default stream (cnh_set_stream). */
+int cnh_capture_begin(cnh_net* net);
+int cnh_capture_end(cnh_net* net);
+int cnh_graph_launch(cnh_net* net);
+unsigned long long cnh_graph_kernel_count(cnh_net* net);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,71 @@
+"""Data-parallel training on 2 GPUs (NCCL) against the single-GPU run of the same global batch:
+the per-step loss curve and the weights after the last update must agree to fp32 reassociation
+noise.  Needs two CUDA devices; skipped otherwise.  NVLS is switched off for the child ranks."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+KW = dict(n=256, blocks=2, m=10)
+GLOBAL_BATCH, STEPS, LR = 64, 6, 0.5
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _train(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+    from cnet_b200 import configs
+    from cnet_b200.dp import DataParallelTrainer
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    if world > 1:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        tr = DataParallelTrainer(configs.build_mixer, KW, global_batch=GLOBAL_BATCH, lr=LR, device=rank, seed=0)
+        losses = []
+        for s in range(STEPS):
+            (xr, xi), labels = configs.make_batch(tr.spec, GLOBAL_BATCH, 0, step=s)
+            if s == 2:
+                tr.capture()            # the rest of the run replays the step as a CUDA graph
+            l = tr.step((tr.shard(xr), tr.shard(xi)), tr.shard(labels))
+            tot = torch.tensor([float(l.sum())], device="cuda")
+            if world > 1:
+                dist.all_reduce(tot)
+            losses.append(float(tot.item()) / GLOBAL_BATCH)
+        tr.net.sync()
+        w = tr.net.get_values(tr.spec.layers["w1"])
+        h = tr.net.get_values(tr.spec.layers["h0"])
+        out[(world, rank)] = (np.array(losses), w[0], w[1], h[0], h[1], tr.net.grad_arena()[2])
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+def test_two_gpu_training_matches_single_gpu():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_train, args=(1, 0, out), nprocs=1, join=True)
+    mp.spawn(_train, args=(2, _free_port(), out), nprocs=2, join=True)
+    one, r0, r1 = out[(1, 0)], out[(2, 0)], out[(2, 1)]
+    assert one[5] >= 1
+    assert np.linalg.norm(r0[0] - one[0]) / np.linalg.norm(one[0]) < 1e-4
+    assert one[0][-1] < one[0][0]
+    for k in range(1, 5):
+        assert np.array_equal(r0[k], r1[k])                     # replicas stay identical
+        assert np.linalg.norm(r0[k] - one[k]) / np.linalg.norm(one[k]) < 1e-4
