@@ -15,20 +15,21 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// One CTA per pair of batch rows; each of the 8 warps takes one eighth of the input length, so a
+// row pair is in flight on 256 threads (B/2 CTAs keep every SM busy even at a batch of a few hundred).
 __global__ void __launch_bounds__(256)
 skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const float* __restrict__ wr,
              const float* __restrict__ wi, float* __restrict__ yr, float* __restrict__ yi, int B, int in, int out) {
-    const int lane = threadIdx.x & 31;
-    const long warp = ((long) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const long nwarps = ((long) gridDim.x * blockDim.x) >> 5;
-    for (long b0 = warp * 2; b0 < B; b0 += nwarps * 2) {
+    __shared__ float red[8][2][2][MAXO];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long b0 = (long) blockIdx.x * 2; b0 < B; b0 += (long) gridDim.x * 2) {
         const bool two = b0 + 1 < B;
         float ar[2][MAXO], ai[2][MAXO];
 #pragma unroll
         for (int o = 0; o < MAXO; ++o) { ar[0][o] = ai[0][o] = ar[1][o] = ai[1][o] = 0.f; }
         const float* x0r = xr + b0 * in; const float* x0i = xi + b0 * in;
         const float* x1r = x0r + (two ? in : 0); const float* x1i = x0i + (two ? in : 0);
-        for (int i = lane; i < in; i += 32) {
+        for (int i = threadIdx.x; i < in; i += 256) {
             float p0r = x0r[i], p0i = x0i[i], p1r = x1r[i], p1i = x1i[i];
 #pragma unroll
             for (int o = 0; o < MAXO; ++o) {
@@ -39,16 +40,22 @@ skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const f
                 }
             }
         }
+        __syncthreads();                                 // `red` of the previous pair has been consumed
 #pragma unroll
         for (int o = 0; o < MAXO; ++o) {
             if (o < out) {
                 float s0r = warp_sum(ar[0][o]), s0i = warp_sum(ai[0][o]);
                 float s1r = warp_sum(ar[1][o]), s1i = warp_sum(ai[1][o]);
-                if (lane == 0) {
-                    yr[b0 * out + o] = s0r; yi[b0 * out + o] = s0i;
-                    if (two) { yr[(b0 + 1) * out + o] = s1r; yi[(b0 + 1) * out + o] = s1i; }
-                }
+                if (lane == 0) { red[warp][0][0][o] = s0r; red[warp][0][1][o] = s0i; red[warp][1][0][o] = s1r; red[warp][1][1][o] = s1i; }
             }
+        }
+        __syncthreads();
+        if (threadIdx.x < 4 * out) {
+            int o = threadIdx.x % out, part = (threadIdx.x / out) & 1, r = threadIdx.x / (2 * out);
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) s += red[w][r][part][o];
+            if (r == 0 || two) (part ? yi : yr)[(b0 + r) * out + o] = s;
         }
     }
 }
@@ -140,8 +147,7 @@ size_t skinny_workspace_bytes(int B, int in, int out, int sm_count) {
 
 int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, const float* wi, float* yr, float* yi,
                int B, int in, int out, cudaStream_t st) {
-    long warps = (B + 1) / 2;
-    long blocks = (warps + 7) / 8;
+    long blocks = (B + 1) / 2;
     long cap = (long) ctx->sm_count * 8;
     skinny_fwd_k<<<(int) std::min(blocks, cap), 256, 0, st>>>(xr, xi, wr, wi, yr, yi, B, in, out);
     CNB_LAUNCH_CHECK("skinny_fwd");

@@ -50,7 +50,7 @@ __device__ __forceinline__ void fft_regs(float (&re)[R], float (&im)[R]) {
 }
 
 template <int R, int SIGN>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (R <= 32 ? 2 : 1))
 fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __restrict__ yr, float* __restrict__ yi,
          const float2* __restrict__ tw, int B, int accumulate) {
     constexpr int N = R * R;
@@ -86,15 +86,48 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
 #pragma unroll
             for (int n2 = 0; n2 < R; ++n2) { re[n2] = sr[t * (R + 1) + n2]; im[n2] = si[t * (R + 1) + n2]; }
             fft_regs<R, SIGN>(re, im);
-            float* qr = yr + row * N + t;
-            float* qi = yi + row * N + t;
+        }
+        __syncthreads();                                 // every row of the tile has been read
+        if (live) {
+            // back through shared memory in natural order X[k1 + R*k2] so that the row leaves (and, when
+            // accumulating, is first read) with contiguous 16-byte accesses
 #pragma unroll
             for (int p = 0; p < R; ++p) {
                 const int k2 = bitrev<R>(p);
-                float vr = re[p] * scale, vi = im[p] * scale;
-                if (accumulate) { vr += qr[k2 * R]; vi += qi[k2 * R]; }
-                qr[k2 * R] = vr;
-                qi[k2 * R] = vi;
+                sr[k2 * (R + 1) + t] = re[p] * scale;
+                si[k2 * (R + 1) + t] = im[p] * scale;
+            }
+        }
+        __syncthreads();
+        if (live) {
+            float* qr = yr + row * N;
+            float* qi = yi + row * N;
+            constexpr int V = N / (4 * R);               // float4 per thread and plane
+            float4 o_r[V], o_i[V];
+            if (accumulate) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    o_r[v] = *reinterpret_cast<const float4*>(qr + 4 * (t + v * R));
+                    o_i[v] = *reinterpret_cast<const float4*>(qi + 4 * (t + v * R));
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const int e = 4 * (t + v * R);           // element index in the row; e = k1 + R*k2
+                float a[4], c[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int idx = e + k;
+                    a[k] = sr[(idx / R) * (R + 1) + (idx % R)];
+                    c[k] = si[(idx / R) * (R + 1) + (idx % R)];
+                }
+                float4 vr = make_float4(a[0], a[1], a[2], a[3]), vi = make_float4(c[0], c[1], c[2], c[3]);
+                if (accumulate) {
+                    vr.x += o_r[v].x; vr.y += o_r[v].y; vr.z += o_r[v].z; vr.w += o_r[v].w;
+                    vi.x += o_i[v].x; vi.y += o_i[v].y; vi.z += o_i[v].z; vi.w += o_i[v].w;
+                }
+                *reinterpret_cast<float4*>(qr + e) = vr;
+                *reinterpret_cast<float4*>(qi + e) = vi;
             }
         }
         __syncthreads();
