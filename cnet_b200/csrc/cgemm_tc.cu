@@ -50,6 +50,7 @@ struct TcParams {
     const float* r_re; const float* r_im;
     int M, N, K, conjB, accumulate;
     int units_per_cta;        // consecutive (tile, k-block) work units per CTA (stream-K)
+    int a_mn, b_mn;           // operand stored [K, rows] (MN-major) instead of [rows, K] (K-major)
     int* status;
 };
 
@@ -108,6 +109,26 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// MN-major operand tile (source stored [K, rows]): slabs of 32 rows-of-the-operand, each slab
+// 16 k-lines of 128 B.  The only layout the tensor core accepts for MN-major TF32 is the 128-byte
+// swizzle with 32-byte atomicity: atoms of 4 k-lines (512 B).  Leading byte offset = distance
+// between slabs (2 KB), stride byte offset = distance between 4-line k atoms (512 B).
+__device__ __forceinline__ uint64_t smem_desc_mn128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((addr >> 4) & 0x3FFF);
+    d |= (uint64_t) (2048 >> 4) << 16;
+    d |= (uint64_t) (512 >> 4) << 32;
+    d |= (uint64_t) 1 << 46;
+    d |= (uint64_t) 1 << 61;                          // layout type: 128-byte swizzle, 32-byte base
+    return d;
+}
+
 // K-major operand tile, 64-byte swizzle: rows of 64 B, 8-row groups 512 B apart.
 __device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
     uint64_t d = 0;
@@ -122,12 +143,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
 // kind::tf32, fp32 accumulate, A and B K-major, M = 128, N = 256
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
 
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate) : "memory");
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -212,8 +234,11 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                 mbar_expect_tx(full_bar(s), STAGE_BYTES);
                 uint32_t dst = smem_base + s * STAGE_BYTES;
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    tma_load_2d(dst + q * PLANE_BYTES, maps[q], full_bar(s), kb * BK, q < 4 ? m0 : n0);
+                for (int q = 0; q < 8; ++q) {
+                    const int r0 = q < 4 ? m0 : n0;
+                    if (q < 4 ? p.a_mn : p.b_mn) tma_load_3d(dst + q * PLANE_BYTES, maps[q], full_bar(s), 0, kb * BK, r0 / 32);
+                    else tma_load_2d(dst + q * PLANE_BYTES, maps[q], full_bar(s), kb * BK, r0);
+                }
             }
         }
     } else if (warp == 1) {
@@ -222,6 +247,8 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             bool ok = true;
             long it = 0;
             int seg = 0;
+            // bits 15 / 16 of the instruction descriptor: operand A / B is MN-major
+            const uint32_t idesc = kInstrDesc | (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
             for (long u = u_begin; u < u_end && ok; ++seg) {
                 int kb0 = (int) (u % k_blocks);
                 int kb1 = (int) min((long) k_blocks, kb0 + (u_end - u));
@@ -238,17 +265,25 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     uint32_t st = smem_base + s * STAGE_BYTES;
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
-                        uint32_t ko = j * 32;        // 8 TF32 = 32 bytes along K inside the swizzled row
-                        uint64_t a_hr = smem_desc_sw64(st + 0 * PLANE_BYTES + ko), a_hi_ = smem_desc_sw64(st + 1 * PLANE_BYTES + ko);
-                        uint64_t a_lr = smem_desc_sw64(st + 2 * PLANE_BYTES + ko), a_li = smem_desc_sw64(st + 3 * PLANE_BYTES + ko);
-                        uint64_t b_h = smem_desc_sw64(st + 4 * PLANE_BYTES + ko), b_l = smem_desc_sw64(st + 6 * PLANE_BYTES + ko);
+                        // one k-step = 8 TF32: 32 bytes along a K-major swizzled row, or one 1 KB atom of k-lines
+                        const uint32_t ka = p.a_mn ? j * 1024 : j * 32, kbo = p.b_mn ? j * 1024 : j * 32;
+                        auto adesc = [&](int plane) {
+                            uint32_t a = st + plane * PLANE_BYTES + ka;
+                            return p.a_mn ? smem_desc_mn128(a) : smem_desc_sw64(a);
+                        };
+                        auto bdesc = [&](int plane) {
+                            uint32_t a = st + plane * PLANE_BYTES + kbo;
+                            return p.b_mn ? smem_desc_mn128(a) : smem_desc_sw64(a);
+                        };
+                        uint64_t a_hr = adesc(0), a_hi_ = adesc(1), a_lr = adesc(2), a_li = adesc(3);
+                        uint64_t b_h = bdesc(4), b_l = bdesc(6);
                         uint32_t first = (kb == kb0 && j == 0) ? 0u : 1u;
-                        umma_tf32(tmem_base, a_lr, b_h, first);      // small terms first
-                        umma_tf32(tmem_base, a_hr, b_l, 1u);
-                        umma_tf32(tmem_base, a_hr, b_h, 1u);
-                        umma_tf32(tmem_base + 256, a_li, b_h, first);
-                        umma_tf32(tmem_base + 256, a_hi_, b_l, 1u);
-                        umma_tf32(tmem_base + 256, a_hi_, b_h, 1u);
+                        umma_tf32(tmem_base, a_lr, b_h, idesc, first);      // small terms first
+                        umma_tf32(tmem_base, a_hr, b_l, idesc, 1u);
+                        umma_tf32(tmem_base, a_hr, b_h, idesc, 1u);
+                        umma_tf32(tmem_base + 256, a_li, b_h, idesc, first);
+                        umma_tf32(tmem_base + 256, a_hi_, b_l, idesc, 1u);
+                        umma_tf32(tmem_base + 256, a_hi_, b_h, idesc, 1u);
                     }
                     umma_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                 }
@@ -452,6 +487,23 @@ int make_map(CUtensorMap* m, const float* base, int rows, int K) {
     return CNB_OK;
 }
 
+// MN-major plane stored [K, rows] (rows contiguous, rows % 32 == 0), seen as [rows/32][K][32]:
+// one box {32, BK, 4} brings four 32-row slabs of 16 k-lines, slab after slab (128-byte swizzle,
+// 32-byte atomicity).
+int make_map_mn(CUtensorMap* m, const float* base, int rows, int K) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {32u, (cuuint64_t) K, (cuuint64_t) (rows / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t) rows * sizeof(float), 32u * sizeof(float)};
+    cuuint32_t box[3] = {32u, (cuuint32_t) BK, 4u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for an MN-major [%d,%d] plane", (int) r, K, rows);
+    return CNB_OK;
+}
+
 }  // namespace
 
 namespace cnb {
@@ -467,11 +519,16 @@ size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
     return 4 * ((size_t) M * K + (size_t) N * K) * sizeof(float) + 4096;
 }
 
-// Operands are split into scratch ([rows,K] hi/lo re/im planes each); a_trans / b_trans say the
-// source is stored [K, rows] and must be transposed on the way.
-int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
-                 const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
-                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st) {
+void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* const dst[4], size_t n, cudaStream_t st) {
+    size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
+    split_k<<<(int) (blocks < cap ? blocks : cap), 256, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], n);
+}
+
+// The GEMM proper on operands that are already split: a[4] / b[4] = hi_re, hi_im, lo_re, lo_im planes,
+// stored [rows, K] (major = 0) or [K, rows] (major = 1, needs rows % 32 == 0).
+int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
+                      const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
+                      int accumulate, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
         CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -479,32 +536,17 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
     }
     if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
         return set_error(CNB_ERR_ARG, "cgemm_tc: misaligned output");
-    float* ws = nullptr;
-    int rc = ensure_scratch(ctx, cgemm_tc_workspace_bytes(M, N, K), &ws);
-    if (rc != CNB_OK) return rc;
-    size_t na = ((size_t) M * K + 63) & ~size_t(63), nb = ((size_t) N * K + 63) & ~size_t(63);
-    float* ap[4] = {ws, ws + na, ws + 2 * na, ws + 3 * na};          // hi_re, hi_im, lo_re, lo_im
-    float* bp[4] = {ws + 4 * na, ws + 4 * na + nb, ws + 4 * na + 2 * nb, ws + 4 * na + 3 * nb};
-    auto split = [&](const float* s0, const float* s1, float** dst, int rows, int trans) -> int {
-        if (trans) {   // source is [K, rows]
-            dim3 grid((rows + 31) / 32, (K + 31) / 32), block(32, 8);
-            split_transpose_k<<<grid, block, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], K, rows);
-        } else {
-            size_t n = (size_t) rows * K;
-            bool al = ((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) == 0;
-            if (!al) return set_error(CNB_ERR_ARG, "cgemm_tc: operand planes must be 16-byte aligned");
-            size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
-            split_k<<<(int) (blocks < cap ? blocks : cap), 256, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], n);
-        }
-        CNB_LAUNCH_CHECK("split");
-        return CNB_OK;
-    };
-    if ((rc = split(a_re, a_im, ap, M, a_trans)) != CNB_OK) return rc;
-    if ((rc = split(b_re, b_im, bp, N, b_trans)) != CNB_OK) return rc;
+    if ((a_mn && M % 32) || (b_mn && N % 32))
+        return set_error(CNB_ERR_ARG, "cgemm_tc: an MN-major operand needs a multiple of 32 rows");
+    if ((!a_mn && K % 4) || (!b_mn && K % 4))
+        return set_error(CNB_ERR_ARG, "cgemm_tc: a K-major operand needs K %% 4 == 0");
+    int rc;
     alignas(64) CUtensorMap maps[8];
     for (int q = 0; q < 4; ++q) {
-        if ((rc = make_map(&maps[q], ap[q], M, K)) != CNB_OK) return rc;
-        if ((rc = make_map(&maps[4 + q], bp[q], N, K)) != CNB_OK) return rc;
+        rc = a_mn ? make_map_mn(&maps[q], a[q], M, K) : make_map(&maps[q], a[q], M, K);
+        if (rc != CNB_OK) return rc;
+        rc = b_mn ? make_map_mn(&maps[4 + q], b[q], N, K) : make_map(&maps[4 + q], b[q], N, K);
+        if (rc != CNB_OK) return rc;
     }
     // stream-K: the (tile, k-block) units are dealt out in equal consecutive runs, one run per CTA,
     // one CTA per SM; a tile whose k-range is shared by several CTAs is summed with atomics
@@ -526,10 +568,51 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
     p.d_re = d_re; p.d_im = d_im; p.r_re = r_re; p.r_im = r_im;
     p.M = M; p.N = N; p.K = K; p.conjB = conjB; p.accumulate = accumulate;
     p.units_per_cta = (int) upc;
+    p.a_mn = a_mn; p.b_mn = b_mn;
     p.status = ctx->d_status;
     cgemm_tc_k<<<(int) ctas, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
                                                            maps[7], p);
     CNB_LAUNCH_CHECK("cgemm_tc");
+    return CNB_OK;
+}
+
+// fp32 operands: split them into scratch first.  a_trans / b_trans say the source is stored
+// [K, rows]; it is then consumed MN-major in place (rows % 32 == 0) or transposed while it is split.
+int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
+                 const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
+                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st) {
+    float* ws = nullptr;
+    int rc = ensure_scratch(ctx, cgemm_tc_workspace_bytes(M, N, K), &ws);
+    if (rc != CNB_OK) return rc;
+    size_t na = ((size_t) M * K + 63) & ~size_t(63), nb = ((size_t) N * K + 63) & ~size_t(63);
+    float* ap[4] = {ws, ws + na, ws + 2 * na, ws + 3 * na};          // hi_re, hi_im, lo_re, lo_im
+    float* bp[4] = {ws + 4 * na, ws + 4 * na + nb, ws + 4 * na + 2 * nb, ws + 4 * na + 3 * nb};
+    int a_mn = 0, b_mn = 0;
+    auto split = [&](const float* s0, const float* s1, float** dst, int rows, int trans, int* mn) -> int {
+        bool al = ((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) == 0;
+        if (trans && !(rows % 32 == 0 && al)) {   // source is [K, rows] with ragged rows: transpose while splitting
+            dim3 grid((rows + 31) / 32, (K + 31) / 32), block(32, 8);
+            split_transpose_k<<<grid, block, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], K, rows);
+        } else {
+            if (!al) return set_error(CNB_ERR_ARG, "cgemm_tc: operand planes must be 16-byte aligned");
+            *mn = trans;
+            split_launch(ctx, s0, s1, dst, (size_t) rows * K, st);
+        }
+        CNB_LAUNCH_CHECK("split");
+        return CNB_OK;
+    };
+    if ((rc = split(a_re, a_im, ap, M, a_trans, &a_mn)) != CNB_OK) return rc;
+    if ((rc = split(b_re, b_im, bp, N, b_trans, &b_mn)) != CNB_OK) return rc;
+    return cgemm_tc_presplit(ctx, ap, a_mn, bp, b_mn, conjB, r_re, r_im, d_re, d_im, M, N, K, accumulate, st);
+}
+
+int split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, cudaStream_t st) {
+    if (((reinterpret_cast<uintptr_t>(re) | reinterpret_cast<uintptr_t>(im) | reinterpret_cast<uintptr_t>(split)) & 15) != 0)
+        return set_error(CNB_ERR_ARG, "split: planes must be 16-byte aligned");
+    size_t np = (n + 63) & ~size_t(63);
+    float* dst[4] = {split, split + np, split + 2 * np, split + 3 * np};
+    split_launch(ctx, re, im, dst, n, st);
+    CNB_LAUNCH_CHECK("split");
     return CNB_OK;
 }
 

@@ -58,6 +58,12 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
                  const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
                  float* d_im, int M, int N, int K, int accumulate, cudaStream_t st);
 size_t cgemm_tc_workspace_bytes(int M, int N, int K);
+// Operands already split into [hi_re, hi_im, lo_re, lo_im] planes; major 0 = [rows, K], 1 = [K, rows].
+int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
+                      const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
+                      int accumulate, cudaStream_t st);
+// split = 4 consecutive planes of pad64(n) floats: hi_re, hi_im, lo_re, lo_im
+int split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, cudaStream_t st);
 void cgemm_tc_release(cnb_ctx* ctx);
 
 // Skinny Linear (out <= 16): HBM-bound fp32 kernels.
