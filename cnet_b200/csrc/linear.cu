@@ -155,6 +155,60 @@ size_t cnb_linear_workspace(int B, int in, int out) {
     return w;
 }
 
+/* ---- operands split once by the caller (hi/lo TF32 planes), reused by several products ---- */
+size_t cnb_split_floats(size_t n) { return 4 * ((n + 63) & ~size_t(63)); }
+
+int cnb_split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, void* stream) {
+    CNB_CHECK_ARG(ctx && re && im && split && n > 0, "cnb_split_planes: bad argument");
+    return cnb::split_planes(ctx, re, im, n, split, cnb::S(stream));
+}
+
+int cnb_linear_split_ok(int B, int in, int out) {
+    return (B >= 64 && in >= 64 && out >= 64 && in % 32 == 0 && out % 32 == 0) ? 1 : 0;
+}
+
+namespace {
+inline void planes_of(const float* split, size_t n, const float* p[4]) {
+    size_t np = (n + 63) & ~size_t(63);
+    for (int q = 0; q < 4; ++q) p[q] = split + q * np;
+}
+}  // namespace
+
+int cnb_linear_fwd_split(cnb_ctx* ctx, const float* x_split, const float* w_split, const float* res_re,
+                         const float* res_im, float* y_re, float* y_im, int B, int in, int out, void* stream) {
+    CNB_CHECK_ARG(ctx && x_split && w_split && y_re && y_im, "cnb_linear_fwd_split: null pointer");
+    CNB_CHECK_ARG(cnb_linear_split_ok(B, in, out), "cnb_linear_fwd_split: B=%d in=%d out=%d not eligible", B, in, out);
+    const float *a[4], *b[4];
+    planes_of(x_split, (size_t) B * in, a);
+    planes_of(w_split, (size_t) out * in, b);
+    cnb::g_last_engine = 1;
+    return cnb::cgemm_tc_presplit(ctx, a, 0, b, 0, 0, res_re, res_im, y_re, y_im, B, out, in, 0, cnb::S(stream));
+}
+
+int cnb_linear_bwd_x_split(cnb_ctx* ctx, const float* g_split, const float* w_split, float* dx_re, float* dx_im,
+                           int B, int in, int out, int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_split && w_split && dx_re && dx_im, "cnb_linear_bwd_x_split: null pointer");
+    CNB_CHECK_ARG(cnb_linear_split_ok(B, in, out), "cnb_linear_bwd_x_split: B=%d in=%d out=%d not eligible", B, in, out);
+    const float *a[4], *b[4];
+    planes_of(g_split, (size_t) B * out, a);
+    planes_of(w_split, (size_t) out * in, b);      // W [out, in] = [K, N]: MN-major B operand
+    cnb::g_last_engine = 1;
+    return cnb::cgemm_tc_presplit(ctx, a, 0, b, 1, 1, nullptr, nullptr, dx_re, dx_im, B, in, out, accumulate,
+                                  cnb::S(stream));
+}
+
+int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_split, float* dw_re, float* dw_im,
+                           int B, int in, int out, int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_split && x_split && dw_re && dw_im, "cnb_linear_bwd_w_split: null pointer");
+    CNB_CHECK_ARG(cnb_linear_split_ok(B, in, out), "cnb_linear_bwd_w_split: B=%d in=%d out=%d not eligible", B, in, out);
+    const float *a[4], *b[4];
+    planes_of(g_split, (size_t) B * out, a);       // G [B, out] = [K, M]: MN-major A operand
+    planes_of(x_split, (size_t) B * in, b);        // X [B, in]  = [K, N]: MN-major B operand
+    cnb::g_last_engine = 1;
+    return cnb::cgemm_tc_presplit(ctx, a, 1, b, 1, 1, nullptr, nullptr, dw_re, dw_im, out, in, B, accumulate,
+                                  cnb::S(stream));
+}
+
 int cnb_set_dft_engine(cnb_ctx* ctx, int force_gemm) {
     CNB_CHECK_ARG(ctx, "cnb_set_dft_engine: null context");
     ctx->force_dft_gemm = force_gemm != 0;

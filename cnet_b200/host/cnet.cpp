@@ -204,6 +204,24 @@ Linear::Linear(InSize in1, InSize in2)
 	: CFunc(InSize(in1.value() + in2.value()), OutSize(in2.value() / in1.value())), in1_len(in1.value()),
 	  in2_len(in2.value()) {}
 
+size_t Linear::extraBytes(int batch) const {
+	if (!cnb_linear_split_ok(batch, in1_len, out_size_)) return 0;
+	return (cnb_split_floats((size_t) batch * in1_len) + cnb_split_floats((size_t) in2_len)) * sizeof(float);
+}
+
+void Linear::bindExtra(char* mem, int batch) {
+	use_split_ = true;
+	x_split_ = reinterpret_cast<float*>(mem);
+	w_split_ = x_split_ + cnb_split_floats((size_t) batch * in1_len);
+}
+
+void Linear::splitWeights() {
+	if (!use_split_) return;
+	const Vars& w = in(1);
+	check(cnb_split_planes(ctx(), w.real_, w.imag_, (size_t) in2_len, w_split_, stream()));
+	w_split_version_ = net_->weights_version_;
+}
+
 void Linear::forward() {
 	const Vars& x = in(0);
 	const Vars& w = in(1);
@@ -211,6 +229,13 @@ void Linear::forward() {
 	if (fused_residual_) {
 		const Vars& r = fused_residual_->previous(residual_operand_)->output();
 		rr = r.real_; ri = r.imag_;
+	}
+	if (use_split_ && cnb_linear_split_ok(batch(), in1_len, out_size_)) {
+		if (w_split_version_ != net_->weights_version_) splitWeights();
+		check(cnb_split_planes(ctx(), x.real_, x.imag_, (size_t) batch() * in1_len, x_split_, stream()));
+		check(cnb_linear_fwd_split(ctx(), x_split_, w_split_, rr, ri, out_.real_, out_.imag_, batch(), in1_len,
+				out_size_, stream()));
+		return;
 	}
 	check(cnb_linear_fwd(ctx(), x.real_, x.imag_, w.real_, w.imag_, rr, ri, out_.real_, out_.imag_, batch(), in1_len,
 			out_size_, stream()));
@@ -220,6 +245,15 @@ void Linear::backward() {
 	CFunc* px = prev_func_[0];
 	CFunc* pw = prev_func_[1];
 	int acc_x = accumulate_into(px), acc_w = accumulate_into(pw);
+	if (use_split_ && cnb_linear_split_ok(batch(), in1_len, out_size_)) {
+		float* gs = net_->g_split_;
+		check(cnb_split_planes(ctx(), out_.dz_star_real_, out_.dz_star_imag_, (size_t) batch() * out_size_, gs, stream()));
+		check(cnb_linear_bwd_w_split(ctx(), gs, x_split_, pw->out_.dz_star_real_, pw->out_.dz_star_imag_, batch(),
+				in1_len, out_size_, acc_w, stream()));
+		check(cnb_linear_bwd_x_split(ctx(), gs, w_split_, px->out_.dz_star_real_, px->out_.dz_star_imag_, batch(),
+				in1_len, out_size_, acc_x, stream()));
+		return;
+	}
 	check(cnb_linear_bwd_w(ctx(), out_.dz_star_real_, out_.dz_star_imag_, px->out_.real_, px->out_.imag_,
 			pw->out_.dz_star_real_, pw->out_.dz_star_imag_, batch(), in1_len, out_size_, acc_w, stream()));
 	check(cnb_linear_bwd_x(ctx(), out_.dz_star_real_, out_.dz_star_imag_, pw->out_.real_, pw->out_.imag_,
@@ -451,7 +485,12 @@ size_t CNet::requiredArenaBytes(int B) const {
 		if (dynamic_cast<FourierTrans*>(f)) dft += (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512;
 		extra += f->extraBytes(B) + 256;
 	}
-	return floats * sizeof(float) + extra + dft + scratchBytes(B) + (16u << 20);
+	size_t gs = 0;
+	for (auto f : func_list_)
+		if (Linear* l = dynamic_cast<Linear*>(f))
+			if (cnb_linear_split_ok(B, l->firstInputLength(), l->outSize()))
+				gs = std::max(gs, cnb_split_floats((size_t) B * l->outSize()) * sizeof(float));
+	return floats * sizeof(float) + extra + dft + gs + scratchBytes(B) + (16u << 20);
 }
 
 bool CNet::allocateOnGpu(int B) {
@@ -582,6 +621,16 @@ bool CNet::allocateOnGpu(int B) {
 			f->bindExtra(static_cast<char*>(p), B);
 		}
 	}
+	{
+		size_t gs = 0;
+		for (auto f : func_list_)
+			if (Linear* l = dynamic_cast<Linear*>(f))
+				if (l->use_split_) gs = std::max(gs, cnb_split_floats((size_t) B * l->outSize()) * sizeof(float));
+		if (gs) {
+			if ((rc = cnb_alloc(ctx_, gs, &p)) != CNB_OK) { fail(rc, "gradient split planes"); return false; }
+			g_split_ = static_cast<float*>(p);
+		}
+	}
 	// 3. upload the host copies of the weights
 	for (auto f : inputs_) {
 		if (f == main_in_ && !dynamic_cast<CEmbedding*>(f)) continue;
@@ -608,6 +657,7 @@ bool CNet::setInputValues(int uid, const float* re, const float* im, int len) {
 	if (rc == CNB_OK) rc = cnb_h2d(ctx_, v.imag_, im, (size_t) len * sizeof(float), stream_);
 	if (rc == CNB_OK) rc = cnb_sync(ctx_, stream_);
 	if (rc != CNB_OK) { fail(rc, "setInputValues"); return false; }
+	++weights_version_;
 	return true;
 }
 
@@ -760,7 +810,11 @@ void CNet::updateInputs(float lr) {
 	if (!ctx_ || !wgrad_count_) return;
 	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
 	int rc = cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_);
-	if (rc != CNB_OK) fail(rc, "updateInputs");
+	if (rc != CNB_OK) { fail(rc, "updateInputs"); return; }
+	// the new weights are split here, once, for the next forward and dX* products
+	++weights_version_;
+	for (auto f : func_list_)
+		if (Linear* l = dynamic_cast<Linear*>(f)) l->splitWeights();
 }
 
 bool CNet::gpuForward(InputFunc* inp, OutputFunc* outp, InputBatch& b) {

@@ -246,6 +246,15 @@ class Linear : public CFunc {                       // impl/linear.h:11-156
 	int in1_len, in2_len;
 	CFunc* fused_residual_ = nullptr;               // Residual add done in the GEMM epilogue
 	int residual_operand_ = 0;                      // which Residual input is the other addend
+	// hi/lo TF32 split planes kept by the layer: x is split in forward() and reused by dW*, W is
+	// split when the weights change and reused by forward and dX*
+	float* x_split_ = nullptr;
+	float* w_split_ = nullptr;
+	bool use_split_ = false;
+	unsigned long long w_split_version_ = ~0ull;
+	size_t extraBytes(int batch) const override;
+	void bindExtra(char* mem, int batch) override;
+	void splitWeights();
 public:
 	Linear(Uid uid, InSize in1, InSize in2);
 	Linear(InSize in1, InSize in2);
@@ -306,6 +315,7 @@ typedef int (*BucketHook)(void* user, float* grads, size_t count, int bucket, in
 
 class CNet {
 	friend class CFunc;
+	friend class Linear;
 	std::vector<CFunc*> func_list_;                 // owned, insertion order
 	std::map<int, CFunc*> map_;
 	std::vector<CFunc*> inputs_, outputs_;
@@ -330,6 +340,8 @@ class CNet {
 	std::vector<Bucket> buckets_;
 	BucketHook hook_ = nullptr;
 	void* hook_user_ = nullptr;
+	unsigned long long weights_version_ = 0;        // bumped whenever weight values change
+	float* g_split_ = nullptr;                      // shared split planes of a Linear's output gradient
 	NcclGroup nccl_;                                // native data parallelism (setDataParallel)
 	void* graph_exec_ = nullptr;                    // cudaGraphExec_t of a captured step
 	bool capturing_ = false;

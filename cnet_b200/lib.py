@@ -37,6 +37,12 @@ SIGNATURES = {
     "cnb_linear_fwd": (C.c_int, [_vp] + [_P] * 8 + [C.c_int] * 3 + [_vp]),
     "cnb_linear_bwd_x": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] * 4 + [_vp]),
     "cnb_linear_bwd_w": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] * 4 + [_vp]),
+    "cnb_split_floats": (_sz, [_sz]),
+    "cnb_split_planes": (C.c_int, [_vp, _P, _P, _sz, _P, _vp]),
+    "cnb_linear_split_ok": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "cnb_linear_fwd_split": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] * 3 + [_vp]),
+    "cnb_linear_bwd_x_split": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 4 + [_vp]),
+    "cnb_linear_bwd_w_split": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 4 + [_vp]),
     "cnb_last_gemm_engine": (C.c_int, []),
     "cnb_linear_workspace": (_sz, [C.c_int, C.c_int, C.c_int]),
     "cnb_reserve_scratch": (C.c_int, [_vp, _sz]),

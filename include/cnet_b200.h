@@ -99,6 +99,22 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im,
  * gpu/reduce.cpp:594-598 and gpu/reducegrad.cpp:309-322. */
 size_t cnb_linear_workspace(int B, int in, int out);
 int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes);
+/* The same three products on operands the caller has split once (hi/lo TF32 planes): a tensor
+ * used by several products (X by forward and dW*, G by dX* and dW*, W by forward and dX*) is then
+ * read by the tensor-core GEMM in place, row-major for one product and as the transposed operand
+ * for the other.  `split` buffers hold cnb_split_floats(n) floats: hi_re, hi_im, lo_re, lo_im.
+ * Eligible when cnb_linear_split_ok (all dims >= 64, in and out multiples of 32).  Same reference
+ * call sites as cnb_linear_fwd / _bwd_x / _bwd_w above. */
+size_t cnb_split_floats(size_t n);
+int cnb_split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, void* stream);
+int cnb_linear_split_ok(int B, int in, int out);
+int cnb_linear_fwd_split(cnb_ctx* ctx, const float* x_split, const float* w_split,
+                         const float* res_re, const float* res_im,
+                         float* y_re, float* y_im, int B, int in, int out, void* stream);
+int cnb_linear_bwd_x_split(cnb_ctx* ctx, const float* g_split, const float* w_split,
+                           float* dx_re, float* dx_im, int B, int in, int out, int accumulate, void* stream);
+int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_split,
+                           float* dw_re, float* dw_im, int B, int in, int out, int accumulate, void* stream);
 /* Which GEMM engine the last cnb_linear_* call on this thread used:
  * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (ragged shapes),
  * 4 = skinny fp32 kernels (out <= 16, HBM-bound). */

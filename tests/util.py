@@ -15,6 +15,8 @@ CASES = {
     "mixer_64x2": (configs.build_mixer, dict(n=64, blocks=2, m=10), 5, "normal", 1),
     "embed_lm_small": (configs.build_embed_lm, dict(tokens=4, vocab=32, dim=8, hidden=16), 6, None, 2),
     "linear_48x40": (configs.build_linear, dict(n_in=48, n_out=40), 7, "fanin", 1),
+    # large enough for the tensor-core GEMM with cached operand splits (all dims >= 64), two updates
+    "mixer_64x1_b64": (configs.build_mixer, dict(n=64, blocks=1, m=10), 64, "normal", 2),
 }
 LR = 0.01
 
