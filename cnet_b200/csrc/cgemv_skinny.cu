@@ -15,109 +15,158 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// One CTA per pair of batch rows; each of the 8 warps takes one eighth of the input length, so a
-// row pair is in flight on 256 threads (B/2 CTAs keep every SM busy even at a batch of a few hundred).
+// Forward: W (out x in, both planes) is staged once per CTA in shared memory; every warp then walks
+// batch rows two at a time: each lane owns a strided slice of the input, accumulates the `out`
+// products against shared-memory W, and the warp reduces them with shuffles.  X is read once.
 __global__ void __launch_bounds__(256)
 skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const float* __restrict__ wr,
              const float* __restrict__ wi, float* __restrict__ yr, float* __restrict__ yi, int B, int in, int out) {
-    __shared__ float red[8][2][2][MAXO];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (long b0 = (long) blockIdx.x * 2; b0 < B; b0 += (long) gridDim.x * 2) {
+    extern __shared__ float sw[];                        // [out][in] re, then [out][in] im
+    float* swr = sw;
+    float* swi = sw + (size_t) out * in;
+    for (int e = threadIdx.x; e < out * in; e += blockDim.x) { swr[e] = wr[e]; swi[e] = wi[e]; }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const long warp = ((long) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long nwarps = ((long) gridDim.x * blockDim.x) >> 5;
+    for (long b0 = warp * 2; b0 < B; b0 += nwarps * 2) {
         const bool two = b0 + 1 < B;
         float ar[2][MAXO], ai[2][MAXO];
 #pragma unroll
         for (int o = 0; o < MAXO; ++o) { ar[0][o] = ai[0][o] = ar[1][o] = ai[1][o] = 0.f; }
         const float* x0r = xr + b0 * in; const float* x0i = xi + b0 * in;
         const float* x1r = x0r + (two ? in : 0); const float* x1i = x0i + (two ? in : 0);
-        for (int i = threadIdx.x; i < in; i += 256) {
+        for (int i = lane; i < in; i += 32) {
             float p0r = x0r[i], p0i = x0i[i], p1r = x1r[i], p1i = x1i[i];
 #pragma unroll
             for (int o = 0; o < MAXO; ++o) {
                 if (o < out) {
-                    float cr = wr[(size_t) o * in + i], ci = wi[(size_t) o * in + i];
+                    float cr = swr[o * in + i], ci = swi[o * in + i];
                     ar[0][o] += p0r * cr - p0i * ci; ai[0][o] += p0r * ci + p0i * cr;
                     ar[1][o] += p1r * cr - p1i * ci; ai[1][o] += p1r * ci + p1i * cr;
                 }
             }
         }
-        __syncthreads();                                 // `red` of the previous pair has been consumed
 #pragma unroll
         for (int o = 0; o < MAXO; ++o) {
             if (o < out) {
                 float s0r = warp_sum(ar[0][o]), s0i = warp_sum(ai[0][o]);
                 float s1r = warp_sum(ar[1][o]), s1i = warp_sum(ai[1][o]);
-                if (lane == 0) { red[warp][0][0][o] = s0r; red[warp][0][1][o] = s0i; red[warp][1][0][o] = s1r; red[warp][1][1][o] = s1i; }
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x < 4 * out) {
-            int o = threadIdx.x % out, part = (threadIdx.x / out) & 1, r = threadIdx.x / (2 * out);
-            float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < 8; ++w) s += red[w][r][part][o];
-            if (r == 0 || two) (part ? yi : yr)[(b0 + r) * out + o] = s;
-        }
-    }
-}
-
-__global__ void __launch_bounds__(256)
-skinny_bwd_x_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ wr,
-               const float* __restrict__ wi, float* __restrict__ dr, float* __restrict__ di, int B, int in, int out,
-               int accumulate) {
-    size_t total = (size_t) B * in;
-    for (size_t e = (size_t) blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t) gridDim.x * blockDim.x) {
-        size_t b = e / in;
-        int i = (int) (e % in);
-        float sr = 0.f, si = 0.f;
-#pragma unroll
-        for (int o = 0; o < MAXO; ++o) {
-            if (o < out) {
-                float a = gr[b * out + o], c = gi[b * out + o];
-                float wre = wr[(size_t) o * in + i], wim = wi[(size_t) o * in + i];
-                sr += a * wre + c * wim;          // (a + ic)(wre - i wim)
-                si += c * wre - a * wim;
-            }
-        }
-        if (accumulate) { sr += dr[e]; si += di[e]; }
-        dr[e] = sr; di[e] = si;
-    }
-}
-
-// stage 1: partial[c][o][i] = sum over the rows of chunk c of G[b,o] conj(X[b,i]); block = 32 columns x 8 row lanes
-__global__ void __launch_bounds__(256)
-skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ xr,
-                      const float* __restrict__ xi, float* __restrict__ pr, float* __restrict__ pi, int B, int in,
-                      int out, int rows_per_chunk) {
-    __shared__ float sr[8][33], si[8][33];
-    const int col = blockIdx.x * 32 + threadIdx.x;
-    const int r0 = blockIdx.y * rows_per_chunk, r1 = min(B, r0 + rows_per_chunk);
-    float ar[MAXO], ai[MAXO];
-#pragma unroll
-    for (int o = 0; o < MAXO; ++o) ar[o] = ai[o] = 0.f;
-    if (col < in) {
-        for (int b = r0 + threadIdx.y; b < r1; b += 8) {
-            float x = xr[(size_t) b * in + col], y = xi[(size_t) b * in + col];
-#pragma unroll
-            for (int o = 0; o < MAXO; ++o) {
-                if (o < out) {
-                    float a = gr[(size_t) b * out + o], c = gi[(size_t) b * out + o];
-                    ar[o] += a * x + c * y;       // (a + ic)(x - iy)
-                    ai[o] += c * x - a * y;
+                if (lane == 0) {
+                    yr[b0 * out + o] = s0r; yi[b0 * out + o] = s0i;
+                    if (two) { yr[(b0 + 1) * out + o] = s1r; yi[(b0 + 1) * out + o] = s1i; }
                 }
             }
         }
     }
-    for (int o = 0; o < out; ++o) {
-        __syncthreads();
-        sr[threadIdx.y][threadIdx.x] = ar[o];
-        si[threadIdx.y][threadIdx.x] = ai[o];
-        __syncthreads();
-        if (threadIdx.y == 0 && col < in) {
-            float a = 0.f, c = 0.f;
+}
+
+// dX*: W columns for 4 consecutive inputs are read as float4; G[b, :] is broadcast.
+template <int W>
+__global__ void __launch_bounds__(256)
+skinny_bwd_x_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ wr,
+               const float* __restrict__ wi, float* __restrict__ dr, float* __restrict__ di, int B, int in, int out,
+               int accumulate) {
+    const int per_row = in / W;
+    size_t total = (size_t) B * per_row;
+    for (size_t e = (size_t) blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t) gridDim.x * blockDim.x) {
+        size_t b = e / per_row;
+        int i = (int) (e % per_row) * W;
+        float sr[W], si[W];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) { a += sr[k][threadIdx.x]; c += si[k][threadIdx.x]; }
-            size_t off = ((size_t) blockIdx.y * out + o) * in + col;
-            pr[off] = a; pi[off] = c;
+        for (int k = 0; k < W; ++k) sr[k] = si[k] = 0.f;
+#pragma unroll
+        for (int o = 0; o < MAXO; ++o) {
+            if (o < out) {
+                float a = gr[b * out + o], c = gi[b * out + o];
+                float wre[W], wim[W];
+                if constexpr (W == 4) {
+                    float4 t = *reinterpret_cast<const float4*>(wr + (size_t) o * in + i);
+                    float4 u = *reinterpret_cast<const float4*>(wi + (size_t) o * in + i);
+                    wre[0] = t.x; wre[1] = t.y; wre[2] = t.z; wre[3] = t.w;
+                    wim[0] = u.x; wim[1] = u.y; wim[2] = u.z; wim[3] = u.w;
+                } else { wre[0] = wr[(size_t) o * in + i]; wim[0] = wi[(size_t) o * in + i]; }
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    sr[k] += a * wre[k] + c * wim[k];      // (a + ic)(wre - i wim)
+                    si[k] += c * wre[k] - a * wim[k];
+                }
+            }
+        }
+        size_t off = b * in + i;
+        if constexpr (W == 4) {
+            float4 vr = make_float4(sr[0], sr[1], sr[2], sr[3]), vi = make_float4(si[0], si[1], si[2], si[3]);
+            if (accumulate) {
+                float4 pr = *reinterpret_cast<const float4*>(dr + off), pi = *reinterpret_cast<const float4*>(di + off);
+                vr.x += pr.x; vr.y += pr.y; vr.z += pr.z; vr.w += pr.w;
+                vi.x += pi.x; vi.y += pi.y; vi.z += pi.z; vi.w += pi.w;
+            }
+            *reinterpret_cast<float4*>(dr + off) = vr;
+            *reinterpret_cast<float4*>(di + off) = vi;
+        } else {
+            if (accumulate) { sr[0] += dr[off]; si[0] += di[off]; }
+            dr[off] = sr[0]; di[off] = si[0];
+        }
+    }
+}
+
+// stage 1: partial[c][o][i] = sum over the rows of chunk c of G[b,o] conj(X[b,i]);
+// block = 32 column groups of W columns x 8 row lanes (W = 4: 16-byte reads of X)
+template <int W>
+__global__ void __launch_bounds__(256)
+skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ xr,
+                      const float* __restrict__ xi, float* __restrict__ pr, float* __restrict__ pi, int B, int in,
+                      int out, int rows_per_chunk) {
+    __shared__ float sr[8][32 * W + 1], si[8][32 * W + 1];
+    const int col = (blockIdx.x * 32 + threadIdx.x) * W;
+    const int r0 = blockIdx.y * rows_per_chunk, r1 = min(B, r0 + rows_per_chunk);
+    float ar[MAXO][W], ai[MAXO][W];
+#pragma unroll
+    for (int o = 0; o < MAXO; ++o)
+#pragma unroll
+        for (int k = 0; k < W; ++k) ar[o][k] = ai[o][k] = 0.f;
+    if (col < in) {
+        for (int b = r0 + threadIdx.y; b < r1; b += 8) {
+            float x[W], y[W];
+            if constexpr (W == 4) {
+                float4 t = *reinterpret_cast<const float4*>(xr + (size_t) b * in + col);
+                float4 u = *reinterpret_cast<const float4*>(xi + (size_t) b * in + col);
+                x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w; y[0] = u.x; y[1] = u.y; y[2] = u.z; y[3] = u.w;
+            } else { x[0] = xr[(size_t) b * in + col]; y[0] = xi[(size_t) b * in + col]; }
+#pragma unroll
+            for (int o = 0; o < MAXO; ++o) {
+                if (o < out) {
+                    float a = gr[(size_t) b * out + o], c = gi[(size_t) b * out + o];
+#pragma unroll
+                    for (int k = 0; k < W; ++k) {
+                        ar[o][k] += a * x[k] + c * y[k];       // (a + ic)(x - iy)
+                        ai[o][k] += c * x[k] - a * y[k];
+                    }
+                }
+            }
+        }
+    }
+    const int t = threadIdx.y * 32 + threadIdx.x;
+#pragma unroll
+    for (int o = 0; o < MAXO; ++o) {
+        if (o < out) {
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < W; ++k) {
+                sr[threadIdx.y][threadIdx.x * W + k] = ar[o][k];
+                si[threadIdx.y][threadIdx.x * W + k] = ai[o][k];
+            }
+            __syncthreads();
+            if (t < 32 * W) {
+                int c = blockIdx.x * 32 * W + t;
+                if (c < in) {
+                    float a = 0.f, d = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { a += sr[k][t]; d += si[k][t]; }
+                    size_t off = ((size_t) blockIdx.y * out + o) * in + c;
+                    pr[off] = a; pi[off] = d;
+                }
+            }
         }
     }
 }
@@ -136,36 +185,49 @@ __global__ void skinny_bwd_w_stage2_k(const float* __restrict__ pr, const float*
 
 namespace cnb {
 
-bool skinny_ok(int B, int in, int out) { return out <= MAXO && in >= 32 && B >= 1; }
+bool skinny_ok(int B, int in, int out) {
+    // the forward stages W in shared memory: out * in complex values must fit
+    return out <= MAXO && in >= 32 && B >= 1 && (size_t) out * in * 8 <= 200 * 1024;
+}
 
 size_t skinny_workspace_bytes(int B, int in, int out, int sm_count) {
-    int col_blocks = (in + 31) / 32;
-    int chunks = (sm_count * 4 + col_blocks - 1) / col_blocks;
-    chunks = std::max(1, std::min(chunks, std::min((B + 7) / 8, 128)));
+    (void) sm_count;
+    int chunks = std::max(1, std::min((B + 7) / 8, 128));      // upper bound of the launch's choice
     return (size_t) chunks * out * in * 2 * sizeof(float);
 }
 
 int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, const float* wi, float* yr, float* yi,
                int B, int in, int out, cudaStream_t st) {
-    long blocks = (B + 1) / 2;
-    long cap = (long) ctx->sm_count * 8;
-    skinny_fwd_k<<<(int) std::min(blocks, cap), 256, 0, st>>>(xr, xi, wr, wi, yr, yi, B, in, out);
+    size_t smem = (size_t) out * in * 2 * sizeof(float);
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        CNB_CUDA(cudaFuncSetAttribute(skinny_fwd_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        smem_set = smem;
+    }
+    long blocks = ((B + 1) / 2 + 7) / 8;                 // 8 warps per CTA, 2 rows per warp and pass
+    long cap = (long) ctx->sm_count * (smem > 100 * 1024 ? 1 : 2);
+    skinny_fwd_k<<<(int) std::max<long>(1, std::min(blocks, cap)), 256, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out);
     CNB_LAUNCH_CHECK("skinny_fwd");
     return CNB_OK;
 }
 
 int skinny_bwd_x(cnb_ctx* ctx, const float* gr, const float* gi, const float* wr, const float* wi, float* dr, float* di,
                  int B, int in, int out, int accumulate, cudaStream_t st) {
-    size_t total = (size_t) B * in;
+    bool vec = (in % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(wi) |
+                                  reinterpret_cast<uintptr_t>(dr) | reinterpret_cast<uintptr_t>(di)) & 15) == 0;
+    size_t total = (size_t) B * (vec ? in / 4 : in);
     size_t blocks = (total + 255) / 256, cap = (size_t) ctx->sm_count * 16;
-    skinny_bwd_x_k<<<(int) std::min(blocks, cap), 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate);
+    if (vec) skinny_bwd_x_k<4><<<(int) std::min(blocks, cap), 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate);
+    else skinny_bwd_x_k<1><<<(int) std::min(blocks, cap), 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate);
     CNB_LAUNCH_CHECK("skinny_bwd_x");
     return CNB_OK;
 }
 
 int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr, const float* xi, float* dr, float* di,
                  int B, int in, int out, int accumulate, cudaStream_t st) {
-    int col_blocks = (in + 31) / 32;
+    bool vec = (in % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(xi)) & 15) == 0;
+    int w = vec ? 4 : 1;
+    int col_blocks = (in + 32 * w - 1) / (32 * w);
     int chunks = (ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
     chunks = std::max(1, std::min(chunks, std::min((B + 7) / 8, 128)));
     int rows = (B + chunks - 1) / chunks;
@@ -176,7 +238,8 @@ int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr
     if (rc != CNB_OK) return rc;
     float* pr = ws;
     float* pi = ws + (size_t) chunks * n;
-    skinny_bwd_w_stage1_k<<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
+    if (vec) skinny_bwd_w_stage1_k<4><<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
+    else skinny_bwd_w_stage1_k<1><<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage1");
     skinny_bwd_w_stage2_k<<<(int) ((n + 255) / 256), 256, 0, st>>>(pr, pi, dr, di, chunks, n, accumulate);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage2");

@@ -99,51 +99,69 @@ __global__ void hadamard_bwd_elem_k(const float* __restrict__ gr, const float* _
 // Column reduction stage 1: partial[c][n] = sum over the rows of chunk c of t[b,n] o conj(u[b,n]).
 // MODE 0: t = g (plain Hadamard).  MODE 1: t = CGelu backward of g at a (fused pair); then
 // du (+)= t o conj(h) is written in the same pass.
-// Block = (32 columns) x (8 row lanes); a warp reads 128 contiguous bytes of each plane per row.
-template <int MODE>
-__global__ void colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
-                                   const float* __restrict__ ar, const float* __restrict__ ai,
-                                   const float* __restrict__ ur, const float* __restrict__ ui,
-                                   const float* __restrict__ hr, const float* __restrict__ hi,
-                                   float* __restrict__ dur, float* __restrict__ dui, int accumulate_u,
-                                   float* __restrict__ pr, float* __restrict__ pi,
-                                   int B, int N, int rows_per_chunk) {
-    __shared__ float sr[8][33], si[8][33];
-    int col = blockIdx.x * 32 + threadIdx.x;
-    int r0 = blockIdx.y * rows_per_chunk;
-    int r1 = min(B, r0 + rows_per_chunk);
-    float accr = 0.f, acci = 0.f;
+// Block = 32 column groups of W columns x 8 row lanes; with W = 4 every access is 16 bytes and a
+// warp touches 512 contiguous bytes of each plane per row.
+template <int MODE, int W>
+__global__ void __launch_bounds__(256)
+colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
+                   const float* __restrict__ ar, const float* __restrict__ ai,
+                   const float* __restrict__ ur, const float* __restrict__ ui,
+                   const float* __restrict__ hr, const float* __restrict__ hi,
+                   float* __restrict__ dur, float* __restrict__ dui, int accumulate_u,
+                   float* __restrict__ pr, float* __restrict__ pi,
+                   int B, int N, int rows_per_chunk) {
+    __shared__ float sr[8][32 * W + 1], si[8][32 * W + 1];
+    const int col = (blockIdx.x * 32 + threadIdx.x) * W;
+    const int r0 = blockIdx.y * rows_per_chunk;
+    const int r1 = min(B, r0 + rows_per_chunk);
+    float accr[W], acci[W];
+#pragma unroll
+    for (int k = 0; k < W; ++k) accr[k] = acci[k] = 0.f;
     if (col < N) {
-        float hre = 0.f, him = 0.f;
-        if (MODE == 1) { hre = hr[col]; him = hi[col]; }
+        Pack<W> hre, him;
+        if (MODE == 1) { hre = ld<W>(hr, col); him = ld<W>(hi, col); }
         for (int b = r0 + threadIdx.y; b < r1; b += 8) {
             size_t i = (size_t) b * N + col;
-            float tr = gr[i], ti = gi[i];
+            Pack<W> tr = ld<W>(gr, i), ti = ld<W>(gi, i), xr = ld<W>(ur, i), xi = ld<W>(ui, i);
             if (MODE == 1) {
-                float dx = 0.5f * dgelu_f(ar[i]), dy = 0.5f * dgelu_f(ai[i]);
-                float p = dx + dy, m = dx - dy;
-                // dz* = conj(g*) (dx-dy) + g* (dx+dy)
-                float nr = tr * m + tr * p, ni = -ti * m + ti * p;
-                tr = nr; ti = ni;
-                if (dur) {
-                    float vr = tr * hre + ti * him, vi = ti * hre - tr * him;   // t o conj(h)
-                    if (accumulate_u) { vr += dur[i]; vi += dui[i]; }
-                    dur[i] = vr; dui[i] = vi;
+                Pack<W> zr = ld<W>(ar, i), zi = ld<W>(ai, i), vr, vi;
+                if (dur && accumulate_u) { vr = ld<W>(dur, i); vi = ld<W>(dui, i); }
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    float dx = 0.5f * dgelu_f(zr.v[k]), dy = 0.5f * dgelu_f(zi.v[k]);
+                    float p = dx + dy, m = dx - dy;
+                    // dz* = conj(g*) (dx-dy) + g* (dx+dy)
+                    float nr = tr.v[k] * m + tr.v[k] * p, ni = -ti.v[k] * m + ti.v[k] * p;
+                    tr.v[k] = nr; ti.v[k] = ni;
+                    float wr = nr * hre.v[k] + ni * him.v[k], wi = ni * hre.v[k] - nr * him.v[k];   // t o conj(h)
+                    if (dur && accumulate_u) { vr.v[k] += wr; vi.v[k] += wi; } else { vr.v[k] = wr; vi.v[k] = wi; }
                 }
+                if (dur) { st<W>(dur, i, vr); st<W>(dui, i, vi); }
             }
-            float xr = ur[i], xi = ui[i];
-            accr += tr * xr + ti * xi;        // t o conj(u)
-            acci += ti * xr - tr * xi;
+#pragma unroll
+            for (int k = 0; k < W; ++k) {
+                accr[k] += tr.v[k] * xr.v[k] + ti.v[k] * xi.v[k];        // t o conj(u)
+                acci[k] += ti.v[k] * xr.v[k] - tr.v[k] * xi.v[k];
+            }
         }
     }
-    sr[threadIdx.y][threadIdx.x] = accr;
-    si[threadIdx.y][threadIdx.x] = acci;
-    __syncthreads();
-    if (threadIdx.y == 0 && col < N) {
 #pragma unroll
-        for (int k = 1; k < 8; ++k) { accr += sr[k][threadIdx.x]; acci += si[k][threadIdx.x]; }
-        pr[(size_t) blockIdx.y * N + col] = accr;
-        pi[(size_t) blockIdx.y * N + col] = acci;
+    for (int k = 0; k < W; ++k) {
+        sr[threadIdx.y][threadIdx.x * W + k] = accr[k];
+        si[threadIdx.y][threadIdx.x * W + k] = acci[k];
+    }
+    __syncthreads();
+    // 32 * W columns of this block, summed over the 8 row lanes by the first 32 * W threads
+    const int t = threadIdx.y * 32 + threadIdx.x;
+    if (t < 32 * W) {
+        int c = blockIdx.x * 32 * W + t;
+        if (c < N) {
+            float a = 0.f, d = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { a += sr[k][t]; d += si[k][t]; }
+            pr[(size_t) blockIdx.y * N + c] = a;
+            pi[(size_t) blockIdx.y * N + c] = d;
+        }
     }
 }
 
@@ -193,11 +211,14 @@ __global__ void gelu_bwd_k(const float* __restrict__ gr, const float* __restrict
     }
 }
 
+// sp != NULL: also emit the hi/lo TF32 split planes of y (4 planes of `np` floats) that the
+// tensor-core GEMM of the consuming Linear reads, saving that layer's separate split pass.
 template <int W>
 __global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* __restrict__ ui,
                                     const float* __restrict__ hr, const float* __restrict__ hi,
                                     float* __restrict__ ar, float* __restrict__ ai,
-                                    float* __restrict__ yr, float* __restrict__ yi, size_t total, int N) {
+                                    float* __restrict__ yr, float* __restrict__ yi, size_t total, int N,
+                                    float* __restrict__ sp, size_t np) {
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         size_t j = i % N;
@@ -211,6 +232,15 @@ __global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* _
 #pragma unroll
         for (int k = 0; k < W; ++k) { r.v[k] = gelu_f(r.v[k]); s.v[k] = gelu_f(s.v[k]); }
         st<W>(yr, i, r); st<W>(yi, i, s);
+        if (sp) {
+            Pack<W> rh, rl, sh, sl;
+#pragma unroll
+            for (int k = 0; k < W; ++k) {
+                rh.v[k] = __uint_as_float(__float_as_uint(r.v[k]) & 0xFFFFE000u); rl.v[k] = r.v[k] - rh.v[k];
+                sh.v[k] = __uint_as_float(__float_as_uint(s.v[k]) & 0xFFFFE000u); sl.v[k] = s.v[k] - sh.v[k];
+            }
+            st<W>(sp, i, rh); st<W>(sp + np, i, sh); st<W>(sp + 2 * np, i, rl); st<W>(sp + 3 * np, i, sl);
+        }
     }
 }
 
@@ -269,7 +299,11 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
                      const float* ur, const float* ui, const float* hr, const float* hi,
                      float* dur, float* dui, int acc_u, float* dvr, float* dvi, int acc_v,
                      int B, int N, cudaStream_t stm) {
-    int col_blocks = (N + 31) / 32;
+    bool vec = (N % 4 == 0) && aligned16(gr) && aligned16(gi) && aligned16(ur) && aligned16(ui) &&
+               (mode == 0 || (aligned16(ar) && aligned16(ai) && aligned16(hr) && aligned16(hi))) &&
+               (!dur || (aligned16(dur) && aligned16(dui)));
+    int w = vec ? 4 : 1;
+    int col_blocks = (N + 32 * w - 1) / (32 * w);
     int chunks = (ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
     int max_chunks = (B + 7) / 8;
     if (chunks > max_chunks) chunks = max_chunks;
@@ -283,10 +317,10 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
     float* pr = part;
     float* pi = part + (size_t) chunks * N;
     dim3 grid(col_blocks, chunks), block(32, 8);
-    if (mode == 0)
-        colreduce_stage1_k<0><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows);
-    else
-        colreduce_stage1_k<1><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows);
+#define CNB_COLREDUCE(MODE, W) colreduce_stage1_k<MODE, W><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows)
+    if (mode == 0) { if (vec) CNB_COLREDUCE(0, 4); else CNB_COLREDUCE(0, 1); }
+    else { if (vec) CNB_COLREDUCE(1, 4); else CNB_COLREDUCE(1, 1); }
+#undef CNB_COLREDUCE
     CNB_LAUNCH_CHECK("colreduce_stage1");
     colreduce_stage2_k<<<(N + 255) / 256, 256, 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
     CNB_LAUNCH_CHECK("colreduce_stage2");
@@ -373,17 +407,24 @@ int cnb_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float
     return CNB_OK;
 }
 
-int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im, const float* h_re,
-                          const float* h_im, float* a_re, float* a_im, float* y_re, float* y_im, int B, int N,
-                          void* stream) {
+int cnb_hadamard_gelu_fwd_split(cnb_ctx* ctx, const float* u_re, const float* u_im, const float* h_re,
+                                const float* h_im, float* a_re, float* a_im, float* y_re, float* y_im,
+                                float* y_split, int B, int N, void* stream) {
     CNB_CHECK_ARG(ctx && u_re && u_im && h_re && h_im && a_re && a_im && y_re && y_im,
                   "cnb_hadamard_gelu_fwd: null pointer");
     CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_gelu_fwd: B=%d N=%d", B, N);
     cudaStream_t stm = cnb::S(stream);
     size_t total = (size_t) B * N;
-    bool vec = (N % 4 == 0) && all_aligned(u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im);
-    DISPATCH_W(vec, hadamard_gelu_fwd_k, total, u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im, total, N);
+    size_t np = (total + 63) & ~size_t(63);
+    bool vec = (N % 4 == 0) && all_aligned(u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im, y_split);
+    DISPATCH_W(vec, hadamard_gelu_fwd_k, total, u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im, total, N, y_split, np);
     return CNB_OK;
+}
+
+int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im, const float* h_re,
+                          const float* h_im, float* a_re, float* a_im, float* y_re, float* y_im, int B, int N,
+                          void* stream) {
+    return cnb_hadamard_gelu_fwd_split(ctx, u_re, u_im, h_re, h_im, a_re, a_im, y_re, y_im, nullptr, B, N, stream);
 }
 
 int cnb_hadamard_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* a_re,
@@ -512,8 +553,8 @@ extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, con
     float* pr = sc.ptr;
     float* pi = sc.ptr + (size_t) kStaticMaxChunks * kStaticMaxN;
     dim3 grid(col_blocks, chunks), block(32, 8);
-    colreduce_stage1_k<0><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
-                                                   nullptr, nullptr, 0, pr, pi, B, N, rows);
+    colreduce_stage1_k<0, 1><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
+                                                      nullptr, nullptr, 0, pr, pi, B, N, rows);
     CNB_LAUNCH_CHECK("colreduce_stage1");
     colreduce_stage2_k<<<(N + 255) / 256, 256, 0, stm>>>(pr, pi, dv_re, dv_im, accumulate_v, chunks, N);
     CNB_LAUNCH_CHECK("colreduce_stage2");

@@ -49,6 +49,12 @@ __device__ __forceinline__ void fft_regs(float (&re)[R], float (&im)[R]) {
     }
 }
 
+// Barrier among the R threads that share a row: they sit in one warp when R <= 32, so warps run
+// their load / transform / store phases independently and overlap each other's memory latency.
+template <int R> __device__ __forceinline__ void row_sync() {
+    if constexpr (R <= 32) __syncwarp(); else __syncthreads();
+}
+
 template <int R, int SIGN>
 __global__ void __launch_bounds__(256, (R <= 32 ? 2 : 1))
 fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __restrict__ yr, float* __restrict__ yi,
@@ -81,13 +87,13 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                 si[k1 * (R + 1) + t] = vi;
             }
         }
-        __syncthreads();
+        row_sync<R>();
         if (live) {
 #pragma unroll
             for (int n2 = 0; n2 < R; ++n2) { re[n2] = sr[t * (R + 1) + n2]; im[n2] = si[t * (R + 1) + n2]; }
             fft_regs<R, SIGN>(re, im);
         }
-        __syncthreads();                                 // every row of the tile has been read
+        row_sync<R>();                                   // every row of the tile has been read
         if (live) {
             // back through shared memory in natural order X[k1 + R*k2] so that the row leaves (and, when
             // accumulating, is first read) with contiguous 16-byte accesses
@@ -98,7 +104,7 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                 si[k2 * (R + 1) + t] = im[p] * scale;
             }
         }
-        __syncthreads();
+        row_sync<R>();
         if (live) {
             float* qr = yr + row * N;
             float* qi = yi + row * N;
@@ -130,7 +136,7 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                 *reinterpret_cast<float4*>(qi + e) = vi;
             }
         }
-        __syncthreads();
+        row_sync<R>();
     }
 }
 

@@ -158,8 +158,18 @@ void Hadamard::forward() {
 	const Vars& v = in(1);
 	if (fused_gelu_) {
 		Vars& y = fused_gelu_->out_;
-		check(cnb_hadamard_gelu_fwd(ctx(), u.real_, u.imag_, v.real_, v.imag_, out_.real_, out_.imag_, y.real_,
-				y.imag_, batch(), out_size_, stream()));
+		// a Linear that is the only consumer of the GELU output gets its operand split planes from here
+		float* ysplit = nullptr;
+		if (fused_gelu_->no_outputs() == 1) {
+			Linear* l = dynamic_cast<Linear*>(fused_gelu_->next(0));
+			if (l && l->use_split_ && l->previous(0) == fused_gelu_ &&
+					cnb_linear_split_ok(batch(), l->firstInputLength(), l->outSize())) {
+				ysplit = l->x_split_;
+				l->x_presplit_ = true;
+			}
+		}
+		check(cnb_hadamard_gelu_fwd_split(ctx(), u.real_, u.imag_, v.real_, v.imag_, out_.real_, out_.imag_, y.real_,
+				y.imag_, ysplit, batch(), out_size_, stream()));
 		return;
 	}
 	check(cnb_hadamard_fwd(ctx(), u.real_, u.imag_, v.real_, v.imag_, prev_func_[1]->batched_ ? 1 : 0, out_.real_,
@@ -232,7 +242,9 @@ void Linear::forward() {
 	}
 	if (use_split_ && cnb_linear_split_ok(batch(), in1_len, out_size_)) {
 		if (w_split_version_ != net_->weights_version_) splitWeights();
-		check(cnb_split_planes(ctx(), x.real_, x.imag_, (size_t) batch() * in1_len, x_split_, stream()));
+		if (!x_presplit_)
+			check(cnb_split_planes(ctx(), x.real_, x.imag_, (size_t) batch() * in1_len, x_split_, stream()));
+		x_presplit_ = false;
 		check(cnb_linear_fwd_split(ctx(), x_split_, w_split_, rr, ri, out_.real_, out_.imag_, batch(), in1_len,
 				out_size_, stream()));
 		return;

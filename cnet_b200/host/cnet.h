@@ -243,6 +243,7 @@ public:
 
 class Linear : public CFunc {                       // impl/linear.h:11-156
 	friend class CNet;
+	friend class Hadamard;
 	int in1_len, in2_len;
 	CFunc* fused_residual_ = nullptr;               // Residual add done in the GEMM epilogue
 	int residual_operand_ = 0;                      // which Residual input is the other addend
@@ -251,6 +252,7 @@ class Linear : public CFunc {                       // impl/linear.h:11-156
 	float* x_split_ = nullptr;
 	float* w_split_ = nullptr;
 	bool use_split_ = false;
+	bool x_presplit_ = false;                       // the producer of x writes x_split_ itself
 	unsigned long long w_split_version_ = ~0ull;
 	size_t extraBytes(int batch) const override;
 	void bindExtra(char* mem, int batch) override;

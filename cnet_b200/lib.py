@@ -55,6 +55,7 @@ SIGNATURES = {
     "cnb_gelu_fwd": (C.c_int, [_vp] + [_P] * 4 + [_sz, _vp]),
     "cnb_gelu_bwd": (C.c_int, [_vp] + [_P] * 6 + [_sz, C.c_int, _vp]),
     "cnb_hadamard_gelu_fwd": (C.c_int, [_vp] + [_P] * 8 + [C.c_int] * 2 + [_vp]),
+    "cnb_hadamard_gelu_fwd_split": (C.c_int, [_vp] + [_P] * 9 + [C.c_int] * 2 + [_vp]),
     "cnb_hadamard_gelu_bwd": (C.c_int, [_vp] + [_P] * 10 + [C.c_int] + [_P] * 2 + [C.c_int] * 3 + [_vp]),
     "cnb_residual_fwd": (C.c_int, [_vp] + [_P] * 6 + [_sz, _vp]),
     "cnb_axpy": (C.c_int, [_vp] + [_P] * 4 + [_sz, C.c_int, _vp]),

@@ -183,6 +183,12 @@ int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im,
                           const float* h_re, const float* h_im,
                           float* a_re, float* a_im, float* y_re, float* y_im,
                           int B, int N, void* stream);
+/* Same, and when y_split != NULL also writes the hi/lo TF32 split planes of y
+ * (cnb_split_floats(B*N) floats) that cnb_linear_fwd_split / _bwd_w_split consume. */
+int cnb_hadamard_gelu_fwd_split(cnb_ctx* ctx, const float* u_re, const float* u_im,
+                                const float* h_re, const float* h_im,
+                                float* a_re, float* a_im, float* y_re, float* y_im,
+                                float* y_split, int B, int N, void* stream);
 /* Fused backward of the pair: t = gelu_bwd(g*, a); du* (+)= t o conj(h); dh* (+)= sum_b t o conj(u). */
 int cnb_hadamard_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                           const float* a_re, const float* a_im,
