@@ -554,10 +554,13 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     int k_blocks = (K + BK - 1) / BK;
     long total = (long) tiles * k_blocks;
     long min_units = 8;                                  // do not split below 8 k-blocks per CTA
-    long ctas = std::min<long>(ctx->sm_count, std::max<long>(1, total / min_units));
-    if (tiles >= ctx->sm_count * 4) ctas = tiles;         // many tiles: whole tiles, no atomics
+    // leaving a few SMs free (gemm_cta_limit) lets a concurrent collective's kernels run beside the GEMM
+    const int sms = ctx->gemm_cta_limit > 0 ? std::min(ctx->gemm_cta_limit, ctx->sm_count) : ctx->sm_count;
+    const bool whole_tiles = tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0;
+    long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
+    if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
     long upc = (total + ctas - 1) / ctas;
-    if (tiles >= ctx->sm_count * 4) upc = k_blocks;
+    if (whole_tiles) upc = k_blocks;
     ctas = (total + upc - 1) / upc;
     bool splits_tiles = (upc % k_blocks) != 0;
     if (splits_tiles && !accumulate) {

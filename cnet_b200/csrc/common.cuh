@@ -25,6 +25,7 @@ struct cnb_ctx {
     float* scratch = nullptr;         // column-reduction partials and GEMM operand staging
     size_t scratch_bytes = 0;
     std::map<int, cnb_twiddle> twiddles;
+    int gemm_cta_limit = 0;           // > 0: the tensor-core GEMM uses at most this many CTAs (SMs)
     bool force_dft_gemm = false;      // FourierTrans as a GEMM even where the FFT kernel applies
 };
 

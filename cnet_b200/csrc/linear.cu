@@ -209,6 +209,12 @@ int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_sp
                                   cnb::S(stream));
 }
 
+int cnb_set_gemm_sm_limit(cnb_ctx* ctx, int max_ctas) {
+    CNB_CHECK_ARG(ctx && max_ctas >= 0, "cnb_set_gemm_sm_limit: bad argument");
+    ctx->gemm_cta_limit = max_ctas;
+    return CNB_OK;
+}
+
 int cnb_set_dft_engine(cnb_ctx* ctx, int force_gemm) {
     CNB_CHECK_ARG(ctx, "cnb_set_dft_engine: null context");
     ctx->force_dft_gemm = force_gemm != 0;

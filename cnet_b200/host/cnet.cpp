@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <iostream>
 
@@ -572,7 +573,9 @@ bool CNet::allocateOnGpu(int B) {
 		cnb_memset0(ctx_, wgrad_base_, total * sizeof(float), stream_);
 	}
 	size_t off = 0;
-	const size_t bucket_floats = 1u << 20;
+	// fewer, larger buckets amortise the per-collective latency; the last one is exposed after backward
+	size_t bucket_floats = 9000000;
+	if (const char* e = getenv("CNB_BUCKET_FLOATS")) bucket_floats = (size_t) atoll(e);
 	size_t bucket_begin = 0, bucket_first = 0;
 	for (size_t k = 0; k < weights.size(); ++k) {
 		CFunc* f = weights[k];
@@ -743,6 +746,7 @@ void CNet::backward() {
 	if (!ctx_) { fail(CNB_ERR_ARG, "backward: allocateOnGpu first (there is no CPU path)"); return; }
 	for (auto f : func_list_) f->grad_written_ = false;
 	main_out_->prev_func_[0]->grad_written_ = true;        // seeded by CrossEntropy::forward
+	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, dp_gemm_ctas_);
 	size_t next_bucket = 0;
 	for (auto it = func_list_.rbegin(); it != func_list_.rend(); ++it) {
 		CFunc* f = *it;
@@ -775,6 +779,15 @@ bool CNet::setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nran
 	if (!ctx_) { fail(CNB_ERR_ARG, "setDataParallel: allocateOnGpu first"); return false; }
 	cudaSetDevice(device_);
 	if (!nccl_.init(id, rank, nranks)) { fail(CNB_ERR_CUDA, "setDataParallel: " + nccl_.error()); return false; }
+	if (nccl_.active()) {
+		// the GEMM is one CTA per SM and fills shared memory; keep a few SMs for NCCL's kernels so the
+		// bucket all-reduces really overlap the backward pass (CNB_DP_RESERVED_SMS overrides, 0 = none)
+		int reserve = 12;
+		if (const char* e = getenv("CNB_DP_RESERVED_SMS")) reserve = atoi(e);
+		int sms = 0;
+		cnb_device_info(device_, &sms, nullptr, nullptr, nullptr);
+		if (reserve > 0 && sms > reserve) dp_gemm_ctas_ = sms - reserve;   // applied during backward()
+	}
 	return true;
 }
 
@@ -820,6 +833,7 @@ void CNet::backward(int label) {
 
 void CNet::updateInputs(float lr) {
 	if (!ctx_ || !wgrad_count_) return;
+	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, 0);
 	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
 	int rc = cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_);
 	if (rc != CNB_OK) { fail(rc, "updateInputs"); return; }

@@ -342,6 +342,7 @@ class CNet {
 	std::vector<Bucket> buckets_;
 	BucketHook hook_ = nullptr;
 	void* hook_user_ = nullptr;
+	int dp_gemm_ctas_ = 0;                          // GEMM grid cap while all-reduces are in flight
 	unsigned long long weights_version_ = 0;        // bumped whenever weight values change
 	float* g_split_ = nullptr;                      // shared split planes of a Linear's output gradient
 	NcclGroup nccl_;                                // native data parallelism (setDataParallel)

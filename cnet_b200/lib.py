@@ -43,6 +43,7 @@ SIGNATURES = {
     "cnb_linear_fwd_split": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] * 3 + [_vp]),
     "cnb_linear_bwd_x_split": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 4 + [_vp]),
     "cnb_linear_bwd_w_split": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 4 + [_vp]),
+    "cnb_set_gemm_sm_limit": (C.c_int, [_vp, C.c_int]),
     "cnb_last_gemm_engine": (C.c_int, []),
     "cnb_linear_workspace": (_sz, [C.c_int, C.c_int, C.c_int]),
     "cnb_reserve_scratch": (C.c_int, [_vp, _sz]),

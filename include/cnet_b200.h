@@ -115,6 +115,10 @@ int cnb_linear_bwd_x_split(cnb_ctx* ctx, const float* g_split, const float* w_sp
                            float* dx_re, float* dx_im, int B, int in, int out, int accumulate, void* stream);
 int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_split,
                            float* dw_re, float* dw_im, int B, int in, int out, int accumulate, void* stream);
+/* The tensor-core GEMM is persistent (one CTA per SM, all shared memory).  max_ctas > 0 caps its
+ * grid so that the remaining SMs stay free for kernels that must run beside it (the gradient
+ * all-reduce of a data-parallel job); 0 restores the full grid.  No reference counterpart. */
+int cnb_set_gemm_sm_limit(cnb_ctx* ctx, int max_ctas);
 /* Which GEMM engine the last cnb_linear_* call on this thread used:
  * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (ragged shapes),
  * 4 = skinny fp32 kernels (out <= 16, HBM-bound). */
