@@ -32,6 +32,8 @@ from cnet_b200 import configs  # noqa: E402
 WORKLOADS = {
     # name: (builder, kwargs, global batch, input kind)
     "mixer_dp4096": (configs.build_mixer, dict(n=1024, blocks=8, m=10), 4096, "normal"),
+    # config 2: standalone complex Linear 4096 -> 4096 at batch 4096: forward + dX* + dW* (no net around it)
+    "linear_4096": (None, dict(n_in=4096, n_out=4096), 4096, "fanin"),
     "mixer_b512": (configs.build_mixer, dict(n=1024, blocks=8, m=10), 512, "normal"),
     "classifier_b64": (configs.build_classifier, dict(n=784, m=10), 64, "image"),
     "embed_lm_b1024": (configs.build_embed_lm, dict(tokens=64, vocab=8192, dim=256, hidden=2048), 1024, None),
@@ -108,6 +110,8 @@ def run_reference(args):
         return
     from oracle import ref
     builder, kw, gbatch, kind = WORKLOADS[args.workload]
+    if builder is None:
+        builder = configs.build_linear
     if not ref.available():
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libcnet_ref.so is not built"}))
         return
@@ -177,6 +181,177 @@ def cpu_baseline(workload, seconds=15.0):
     return {"value": k / dt, "unit": "samples/s", "cores": ref.max_threads(), "kind": "reference",
             "sample": "%d of %d samples of the workload through the unmodified reference CPU path "
                       "(oracle/_ref), %.1f s" % (k, gbatch, dt)}
+
+
+# DRAM traffic of one launch of the dominant kernel from the ncu capture summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum), keyed by (M, N, K); None where not captured.
+NCU_TRAFFIC_BYTES = {}
+
+
+def _time_launches(torch, fn, reps=20):
+    """Average device time of fn() in ms: CUDA events on the launching stream, L2 flushed in between."""
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        fn()
+    tot = 0.0
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    return tot / reps
+
+
+def _roofline(args, kw, B, gbatch, step_ms, device):
+    """The dominant kernel of the step (the complex GEMM of the Linear layers, or the skinny head kernel
+    when the net has no square Linear) at this rank's shape, plus the HBM-bound kernels of one block."""
+    import torch
+    from cnet_b200.ops import Context
+    peaks = _peaks()
+    ctx = Context(device=device, arena_bytes=2 << 30)
+    n = kw.get("n", 1024)
+    if args.workload.startswith("embed"):
+        n_in, n_out = kw["tokens"] * kw["dim"], kw["hidden"]
+    elif args.workload.startswith("classifier"):
+        n_in, n_out = kw["n"], kw["m"]
+    else:
+        n_in, n_out = n, n
+    x = tuple(torch.randn(B, n_in, device="cuda") for _ in range(2))
+    w = tuple(torch.randn(n_out, n_in, device="cuda") * n_in ** -0.5 for _ in range(2))
+    hbm = []
+    if ctx.lib.cnb_linear_split_ok(B, n_in, n_out):
+        xs, ws = ctx.split(x), ctx.split(w)
+        y = ctx._new(B, n_out)
+        dur = _time_launches(torch, lambda: ctx.linear_fwd_split(xs, ws, B, n_in, n_out, out=y))
+        flops = 8.0 * B * n_in * n_out
+        achieved = flops / (dur * 1e-3) / 1e12
+        peak = peaks["bf16"] / 6.0       # dense TF32 = bf16 / 2; 3xTF32 = three MMAs per real product
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)), "kernel": "cgemm_tc_k (tcgen05 3xTF32)",
+                "shape": [B, n_out, n_in], "ms_per_launch": dur,
+                "peak_note": "bf16 burst %.1f TFLOP/s / 6 (TF32 = bf16/2, 3 MMAs per product), of %s"
+                             % (peaks["bf16"], peaks["source"])}
+    else:
+        y = None
+        dur = _time_launches(torch, lambda: ctx.linear_fwd(x, w))
+        nbytes = 8.0 * B * n_in + 8.0 * n_in * n_out + 8.0 * B * n_out
+        achieved = nbytes / (dur * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm"], "traffic": None, "kernel": "skinny_fwd_k (fp32)",
+                "shape": [B, n_out, n_in], "ms_per_launch": dur, "peak_note": "copy bandwidth, of " + peaks["source"]}
+    roof["step_gemm_tflops"] = _gemm_flops(kw, gbatch, args.workload) / (step_ms * 1e-3) / 1e12
+    # HBM-bound kernels at the same activation shape: algorithmic bytes / time, against the measured copy bandwidth
+    if not args.workload.startswith("embed"):
+        N = n_in
+        u, g = x, tuple(torch.randn(B, N, device="cuda") for _ in range(2))
+        h = tuple(torch.randn(N, device="cuda") for _ in range(2))
+        a, yy = ctx.hadamard_gelu_fwd(u, h)
+        cases = [("hadamard_gelu_fwd_k", lambda: ctx.hadamard_gelu_fwd(u, h), 24.0 * B * N),
+                 ("colreduce_stage1_k<1> (gelu'+hadamard bwd + dh* partials)", lambda: ctx.hadamard_gelu_bwd(g, a, u, h), 32.0 * B * N),
+                 ("fft_rr_k / dft fwd", lambda: ctx.dft_fwd(u), 16.0 * B * N)]
+        n_w = 2 * n_in * n_out * max(1, kw.get("blocks", 1))       # the whole weight arena of the net
+        wflat = torch.randn(n_w, device="cuda")
+        gflat = torch.randn(n_w, device="cuda")
+        cases.append(("sgd_k", lambda: ctx.sgd_update(wflat, gflat, 1e-3), 16.0 * wflat.numel()))
+        for name, fn, nbytes in cases:
+            d = _time_launches(torch, fn, reps=10)
+            gbs = nbytes / (d * 1e-3) / 1e9
+            hbm.append({"kernel": name, "GB/s": round(gbs, 1), "frac": round(gbs / peaks["hbm"], 3), "ms": round(d, 4)})
+    roof["hbm_kernels"] = hbm
+    ctx.close()
+    return roof
+
+
+def run_linear(args):
+    """Config 2: one complex Linear layer, forward plus both backward products, through the C-ABI
+    operators (operands split once per step, three tensor-core GEMMs).  Single GPU."""
+    import torch
+    from cnet_b200 import lib as cl
+    from cnet_b200.ops import Context
+    _, kw, B, _ = WORKLOADS[args.workload]
+    n_in, n_out = kw["n_in"], kw["n_out"]
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        raise SystemExit("linear_4096 is a single-GPU workload")
+    torch.cuda.set_device(0)
+    lib = cl.load()
+    ctx = Context(device=0, arena_bytes=1 << 30)
+    r = np.random.Generator(np.random.Philox(key=[0, 77]))
+    s = n_in ** -0.5
+    host = [torch.from_numpy((r.standard_normal((B, n_in)) * s).astype(np.float32)).pin_memory() for _ in range(2)]
+    host += [torch.from_numpy(r.standard_normal((B, n_out)).astype(np.float32)).pin_memory() for _ in range(2)]
+    w = tuple(torch.from_numpy((r.standard_normal((n_out, n_in)) * s).astype(np.float32)).cuda() for _ in range(2))
+    x = tuple(torch.empty(B, n_in, device="cuda") for _ in range(2))
+    g = tuple(torch.empty(B, n_out, device="cuda") for _ in range(2))
+    y, dx, dw = ctx._new(B, n_out), ctx._new(B, n_in), ctx._new(n_out, n_in)
+    host_y = torch.empty(B, dtype=torch.float32).pin_memory()
+
+    def upload():
+        for d, h in zip(x + g, host):
+            d.copy_(h, non_blocking=True)
+
+    def step():
+        xs, ws, gs = ctx.split(x), ctx.split(w), ctx.split(g)
+        ctx.linear_fwd_split(xs, ws, B, n_in, n_out, out=y)
+        ctx.linear_bwd_x_split(gs, ws, B, n_in, n_out, out=dx)
+        ctx.linear_bwd_w_split(gs, xs, B, n_in, n_out, out=dw)
+
+    def e2e_step():
+        upload()
+        step()
+        host_y.copy_(y[0][:, 0], non_blocking=False)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    upload()
+    for _ in range(max(3, args.warmup)):
+        step()
+    clocks = _Clocks(0)
+    l0 = lib.cnb_launch_count()
+    ms = timed(step, args.steps)
+    launches = lib.cnb_launch_count() - l0
+    clk = clocks.stop()
+    e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    # parity spot check against float64 on a sample of outputs
+    xs = (x[0][:8].double() + 1j * x[1][:8].double())
+    want = xs @ (w[0].double() + 1j * w[1].double()).T
+    err = float(((y[0][:8].double() + 1j * y[1][:8].double()) - want).norm() / want.norm())
+    peaks = _peaks()
+    per_step = ms / args.steps
+    tflops = 3 * 8.0 * B * n_in * n_out / (per_step * 1e-3) / 1e12
+    xs_, ws_ = ctx.split(x), ctx.split(w)
+    dur = _time_launches(torch, lambda: ctx.linear_fwd_split(xs_, ws_, B, n_in, n_out, out=y))
+    achieved = 8.0 * B * n_in * n_out / (dur * 1e-3) / 1e12
+    peak = peaks["bf16"] / 6.0
+    line = {
+        "metric": "train samples/sec (fwd+bwd+update)", "value": B / (per_step * 1e-3), "unit": "samples/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": B, **kw, "parallelism": "dp1",
+                   "note": "forward + dX* + dW* of one layer, no update (config 2 measures the three products)",
+                   "l2": "operands and outputs (> 1 GB per step) exceed the 126 MB L2"},
+        "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
+                "h2d_bytes_per_step": sum(h.numel() * 4 for h in host), "d2h_bytes_per_step": B * 4},
+        "gpu_launches": int(launches), "clocks": clk,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)), "kernel": "cgemm_tc_k (tcgen05 3xTF32)",
+                     "shape": [B, n_out, n_in], "ms_per_launch": dur, "step_gemm_tflops": tflops,
+                     "peak_note": "bf16 burst %.1f TFLOP/s / 6, of %s" % (peaks["bf16"], peaks["source"])},
+        "forward_relerr_vs_f64": err, "cpu_baseline": None,
+    }
+    print(json.dumps(line))
+    ctx.close()
 
 
 def run_ours(args):
@@ -260,46 +435,7 @@ def run_ours(args):
     ms_e2e = timed(e2e_step, args.steps)
     loss_mean = float(host_loss.mean())
 
-    # dominant kernel: the complex GEMM of the Linear layers, timed alone on this rank's shape
-    roof = None
-    if rank == 0:
-        peaks = _peaks()
-        ctx = Context(device=local, arena_bytes=1 << 30)
-        n = kw.get("n", 1024)
-        if args.workload.startswith("embed"):
-            n_in, n_out = kw["tokens"] * kw["dim"], kw["hidden"]
-        elif args.workload.startswith("classifier"):
-            n_in, n_out = kw["n"], kw["m"]
-        else:
-            n_in, n_out = n, n
-        x = tuple(torch.randn(B, n_in, device="cuda") for _ in range(2))
-        w = tuple(torch.randn(n_out, n_in, device="cuda") * n_in ** -0.5 for _ in range(2))
-        for _ in range(3):
-            ctx.linear_fwd(x, w)
-        reps = 10
-        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
-        tot = 0.0
-        for _ in range(reps):
-            flush.zero_()                               # L2 flush between timed launches
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            ctx.linear_fwd(x, w)
-            e1.record()
-            torch.cuda.synchronize()
-            tot += e0.elapsed_time(e1)
-        engine = ctx.last_gemm_engine()
-        dur_ms = tot / reps
-        flops = 8.0 * B * n_in * n_out
-        achieved = flops / (dur_ms * 1e-3) / 1e12
-        # 3xTF32: three TF32 MMAs per real product; dense TF32 runs at half the bf16 rate
-        peak = peaks["bf16"] / 6.0 if engine == 1 else peaks["bf16"] / 6.0
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": None, "kernel": "cgemm_tc_3xtf32" if engine == 1 else "cgemm_simt_fp32",
-                "shape": [B, n_out, n_in], "ms_per_launch": dur_ms,
-                "peak_note": "measured bf16 burst %.1f TFLOP/s / 6 (TF32 = bf16/2, three MMAs per product), %s"
-                             % (peaks["bf16"], peaks["source"]),
-                "step_gemm_tflops": _gemm_flops(kw, gbatch, args.workload) / (ms / args.steps * 1e-3) / 1e12}
-        ctx.close()
+    roof = _roofline(args, kw, B, gbatch, ms / args.steps, local) if rank == 0 else None
 
     if rank == 0:
         per_step = ms / args.steps
@@ -333,6 +469,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif WORKLOADS[args.workload][0] is None:
+        run_linear(args)
     else:
         run_ours(args)
 

@@ -70,6 +70,32 @@ class Context:
                                              B, n_in, n_out, acc, self._stream()), "linear_bwd_w")
         return dw
 
+    # operands split once (hi/lo TF32 planes) and reused by several products
+    def split(self, x):
+        n = x[0].numel()
+        out = self.torch.empty(self.lib.cnb_split_floats(n), dtype=self.torch.float32, device="cuda")
+        _lib.check(self.lib.cnb_split_planes(self.h, _p(x[0]), _p(x[1]), n, _p(out), self._stream()), "split_planes")
+        return out
+
+    def linear_fwd_split(self, x_split, w_split, B, n_in, n_out, res=None, out=None):
+        y = out if out is not None else self._new(B, n_out)
+        _lib.check(self.lib.cnb_linear_fwd_split(self.h, _p(x_split), _p(w_split), _p(res[0]) if res else None,
+                                                 _p(res[1]) if res else None, _p(y[0]), _p(y[1]), B, n_in, n_out,
+                                                 self._stream()), "linear_fwd_split")
+        return y
+
+    def linear_bwd_x_split(self, g_split, w_split, B, n_in, n_out, out=None, accumulate=False):
+        dx = out if out is not None else self._new(B, n_in)
+        _lib.check(self.lib.cnb_linear_bwd_x_split(self.h, _p(g_split), _p(w_split), _p(dx[0]), _p(dx[1]), B, n_in,
+                                                   n_out, int(accumulate), self._stream()), "linear_bwd_x_split")
+        return dx
+
+    def linear_bwd_w_split(self, g_split, x_split, B, n_in, n_out, out=None, accumulate=False):
+        dw = out if out is not None else self._new(n_out, n_in)
+        _lib.check(self.lib.cnb_linear_bwd_w_split(self.h, _p(g_split), _p(x_split), _p(dw[0]), _p(dw[1]), B, n_in,
+                                                   n_out, int(accumulate), self._stream()), "linear_bwd_w_split")
+        return dw
+
     def last_gemm_engine(self):
         return self.lib.cnb_last_gemm_engine()
 
