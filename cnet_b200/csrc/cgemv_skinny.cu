@@ -171,14 +171,23 @@ skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi
     }
 }
 
+// stage 2: 32 outputs x 8 chunk lanes per block, fixed summation order
 __global__ void skinny_bwd_w_stage2_k(const float* __restrict__ pr, const float* __restrict__ pi, float* __restrict__ dr,
                                       float* __restrict__ di, int chunks, size_t n, int accumulate) {
-    size_t e = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= n) return;
+    __shared__ float sr[8][33], si[8][33];
+    size_t e = (size_t) blockIdx.x * 32 + threadIdx.x;
     float a = 0.f, c = 0.f;
-    for (int k = 0; k < chunks; ++k) { a += pr[(size_t) k * n + e]; c += pi[(size_t) k * n + e]; }
-    if (accumulate) { a += dr[e]; c += di[e]; }
-    dr[e] = a; di[e] = c;
+    if (e < n)
+        for (int k = threadIdx.y; k < chunks; k += 8) { a += pr[(size_t) k * n + e]; c += pi[(size_t) k * n + e]; }
+    sr[threadIdx.y][threadIdx.x] = a;
+    si[threadIdx.y][threadIdx.x] = c;
+    __syncthreads();
+    if (threadIdx.y == 0 && e < n) {
+#pragma unroll
+        for (int k = 1; k < 8; ++k) { a += sr[k][threadIdx.x]; c += si[k][threadIdx.x]; }
+        if (accumulate) { a += dr[e]; c += di[e]; }
+        dr[e] = a; di[e] = c;
+    }
 }
 
 }  // namespace
@@ -241,7 +250,7 @@ int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr
     if (vec) skinny_bwd_w_stage1_k<4><<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
     else skinny_bwd_w_stage1_k<1><<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage1");
-    skinny_bwd_w_stage2_k<<<(int) ((n + 255) / 256), 256, 0, st>>>(pr, pi, dr, di, chunks, n, accumulate);
+    skinny_bwd_w_stage2_k<<<(int) ((n + 31) / 32), dim3(32, 8), 0, st>>>(pr, pi, dr, di, chunks, n, accumulate);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage2");
     return CNB_OK;
 }

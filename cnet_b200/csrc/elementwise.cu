@@ -165,16 +165,26 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
     }
 }
 
-// Stage 2: dv[n] (+)= sum_c partial[c][n] in a fixed order (deterministic).
+// Stage 2: dv[n] (+)= sum_c partial[c][n], always in the same order (deterministic).
+// Block = 32 columns x 8 chunk lanes: the chunk loop is 8 times shorter than one thread per column
+// and the partial rows are read 128 contiguous bytes at a time.
 __global__ void colreduce_stage2_k(const float* __restrict__ pr, const float* __restrict__ pi,
                                    float* __restrict__ dr, float* __restrict__ di, int accumulate,
                                    int chunks, int N) {
-    int col = blockIdx.x * blockDim.x + threadIdx.x;
-    if (col >= N) return;
+    __shared__ float sr[8][33], si[8][33];
+    int col = blockIdx.x * 32 + threadIdx.x;
     float a = 0.f, b = 0.f;
-    for (int c = 0; c < chunks; ++c) { a += pr[(size_t) c * N + col]; b += pi[(size_t) c * N + col]; }
-    if (accumulate) { a += dr[col]; b += di[col]; }
-    dr[col] = a; di[col] = b;
+    if (col < N)
+        for (int c = threadIdx.y; c < chunks; c += 8) { a += pr[(size_t) c * N + col]; b += pi[(size_t) c * N + col]; }
+    sr[threadIdx.y][threadIdx.x] = a;
+    si[threadIdx.y][threadIdx.x] = b;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < N) {
+#pragma unroll
+        for (int k = 1; k < 8; ++k) { a += sr[k][threadIdx.x]; b += si[k][threadIdx.x]; }
+        if (accumulate) { a += dr[col]; b += di[col]; }
+        dr[col] = a; di[col] = b;
+    }
 }
 
 // --------------------------------------------------------------------- CGelu
@@ -322,7 +332,7 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
     else { if (vec) CNB_COLREDUCE(1, 4); else CNB_COLREDUCE(1, 1); }
 #undef CNB_COLREDUCE
     CNB_LAUNCH_CHECK("colreduce_stage1");
-    colreduce_stage2_k<<<(N + 255) / 256, 256, 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
+    colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
     CNB_LAUNCH_CHECK("colreduce_stage2");
     return CNB_OK;
 }
@@ -556,7 +566,7 @@ extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, con
     colreduce_stage1_k<0, 1><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
                                                       nullptr, nullptr, 0, pr, pi, B, N, rows);
     CNB_LAUNCH_CHECK("colreduce_stage1");
-    colreduce_stage2_k<<<(N + 255) / 256, 256, 0, stm>>>(pr, pi, dv_re, dv_im, accumulate_v, chunks, N);
+    colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dv_re, dv_im, accumulate_v, chunks, N);
     CNB_LAUNCH_CHECK("colreduce_stage2");
     return CNB_OK;
 }

@@ -137,6 +137,23 @@ class DataParallelTrainer:
     def kernels_per_step(self):
         return self.net.graph_kernel_count() if self.graph else None
 
+    def prefetch(self, host_in, host_labels):
+        """Start the H2D copy of this rank's shard of the NEXT batch (overlaps the running step)."""
+        if self.spec.tokens:
+            self.net.prefetch(tokens=host_in[0], labels=host_labels, batch=self.local_batch)
+        else:
+            self.net.prefetch(x=host_in, labels=host_labels, batch=self.local_batch)
+
+    def step_pipelined(self, next_in, next_labels, loss_out):
+        """One step on the batch staged by the previous call, while `next_*` is copied in for the next one;
+        the step's per-sample losses land in `loss_out` (pinned) asynchronously: call net.wait_losses()."""
+        self.net.commit()
+        if next_in is not None:
+            self.prefetch(next_in, next_labels)
+        self.step_resident()
+        self.net.wait_losses()          # the previous step's losses: the host stays one step ahead at most
+        self.net.read_losses_async(loss_out, self.local_batch)
+
     def step(self, host_in, host_labels):
         self.upload(host_in, host_labels)
         self.step_resident()

@@ -77,6 +77,12 @@ int cnh_allocate(cnh_net* n, int batch) { n->net.allocateOnGpu(batch); return st
 int cnh_upload(cnh_net* n, const float* re, const float* im, const int32_t* tokens, const int32_t* labels, int batch) {
 	n->net.batchToGpu(re, im, tokens, labels, batch); return status(n);
 }
+int cnh_prefetch(cnh_net* n, const float* re, const float* im, const int32_t* tokens, const int32_t* labels, int batch) {
+	n->net.prefetchBatch(re, im, tokens, labels, batch); return status(n);
+}
+int cnh_commit(cnh_net* n) { n->net.commitBatch(); return status(n); }
+int cnh_read_losses_async(cnh_net* n, float* host_out, int cnt) { n->net.readLossesAsync(host_out, cnt); return status(n); }
+int cnh_wait_losses(cnh_net* n) { n->net.waitLosses(); return status(n); }
 int cnh_forward(cnh_net* n) { n->net.forward(); return status(n); }
 int cnh_backward(cnh_net* n) { n->net.backward(); return status(n); }
 int cnh_backward_label(cnh_net* n, int label) { n->net.backward(label); return status(n); }
@@ -93,6 +99,12 @@ int cnh_grad_arena(cnh_net* n, void** p, size_t* count, int* nb) {
 }
 int cnh_weight_arena(cnh_net* n, void** p, size_t* count) { *p = n->net.weightArena(count); return 0; }
 void* cnh_context(cnh_net* n) { return n->net.context(); }
+int cnh_save(cnh_net* n, const char* path) { n->net.save(path); return status(n); }
+int cnh_restore(cnh_net* n, const char* path) { n->net.restore(path); return status(n); }
+int cnh_num_funcs(cnh_net* n) { return n->net.noFunctions(); }
+int cnh_uid_at(cnh_net* n, int i) { return (i >= 0 && i < n->net.noFunctions()) ? n->net.uidAt(i) : CNB_ERR_ARG; }
+int cnh_type_of(cnh_net* n, int uid) { CFunc* f = n->net[uid]; return f ? f->getType() : CNB_ERR_ARG; }
+int cnh_in_size(cnh_net* n, int uid) { CFunc* f = n->net[uid]; return f ? f->inSize() : CNB_ERR_ARG; }
 
 int cnh_dp_unique_id(char* out128) {
 	std::string err;

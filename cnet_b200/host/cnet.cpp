@@ -338,6 +338,12 @@ CNet::CNet() {}
 
 CNet::~CNet() {
 	if (graph_exec_) cudaGraphExecDestroy((cudaGraphExec_t) graph_exec_);
+	if (copy_stream_) {
+		cudaStreamSynchronize((cudaStream_t) copy_stream_);
+		cudaEventDestroy((cudaEvent_t) ev_h2d_); cudaEventDestroy((cudaEvent_t) ev_commit_);
+		cudaEventDestroy((cudaEvent_t) ev_step_); cudaEventDestroy((cudaEvent_t) ev_d2h_);
+		cudaStreamDestroy((cudaStream_t) copy_stream_);
+	}
 	for (auto f : func_list_) delete f;
 	if (ctx_) cnb_destroy(ctx_);
 }
@@ -503,7 +509,14 @@ size_t CNet::requiredArenaBytes(int B) const {
 		if (Linear* l = dynamic_cast<Linear*>(f))
 			if (cnb_linear_split_ok(B, l->firstInputLength(), l->outSize()))
 				gs = std::max(gs, cnb_split_floats((size_t) B * l->outSize()) * sizeof(float));
-	return floats * sizeof(float) + extra + dft + gs + scratchBytes(B) + (16u << 20);
+	size_t staging = 0;                                // input pipeline: one staged batch + labels
+	if (!func_list_.empty()) {
+		CFunc* f0 = func_list_.front();
+		if (CEmbedding* em = dynamic_cast<CEmbedding*>(f0)) staging = (size_t) B * em->noOutTokens() * 4;
+		else staging = 2 * (size_t) B * f0->out_size_ * 4;
+		staging += (size_t) B * 4 + 1024;
+	}
+	return floats * sizeof(float) + extra + dft + gs + staging + scratchBytes(B) + (16u << 20);
 }
 
 bool CNet::allocateOnGpu(int B) {
@@ -678,8 +691,14 @@ bool CNet::setInputValues(int uid, const float* re, const float* im, int len) {
 
 bool CNet::getInputValues(int uid, float* re, float* im, int len) {
 	auto it = map_.find(uid);
-	if (it == map_.end() || !it->second->is_input_ || !ctx_) { fail(CNB_ERR_ARG, "getInputValues: bad uid / not allocated"); return false; }
+	if (it == map_.end() || !it->second->is_input_) { fail(CNB_ERR_ARG, "getInputValues: uid is not an input"); return false; }
 	CFunc* f = it->second;
+	if (!ctx_) {                                 // not on the device yet: the host copies
+		if ((size_t) len != f->host_re_.size()) { fail(CNB_ERR_ARG, "getInputValues: length / no values set"); return false; }
+		std::copy(f->host_re_.begin(), f->host_re_.end(), re);
+		std::copy(f->host_im_.begin(), f->host_im_.end(), im);
+		return true;
+	}
 	CEmbedding* e = dynamic_cast<CEmbedding*>(f);
 	const Vars& v = e ? e->table_ : f->out_;
 	if ((size_t) len != v.count()) { fail(CNB_ERR_ARG, "getInputValues: length"); return false; }
@@ -730,6 +749,89 @@ bool CNet::batchToGpu(const float* re, const float* im, const int* tokens, const
 	}
 	if (rc == CNB_OK && labels) rc = cnb_h2d(ctx_, main_out_->labels_, labels, (size_t) B * sizeof(int32_t), stream_);
 	if (rc != CNB_OK) { fail(rc, "batchToGpu"); return false; }
+	return true;
+}
+
+bool CNet::pipelineInit() {
+	if (copy_stream_) return true;
+	cudaStream_t st;
+	cudaEvent_t e[4];
+	if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) { fail(CNB_ERR_CUDA, "pipeline: stream"); return false; }
+	for (int i = 0; i < 4; ++i)
+		if (cudaEventCreateWithFlags(&e[i], cudaEventDisableTiming) != cudaSuccess) { fail(CNB_ERR_CUDA, "pipeline: event"); return false; }
+	copy_stream_ = st; ev_h2d_ = e[0]; ev_commit_ = e[1]; ev_step_ = e[2]; ev_d2h_ = e[3];
+	size_t in_bytes = 0;
+	if (CEmbedding* em = dynamic_cast<CEmbedding*>(main_in_)) in_bytes = (size_t) batch_ * em->noOutTokens() * sizeof(int32_t);
+	else in_bytes = 2 * (size_t) batch_ * main_in_->out_size_ * sizeof(float);
+	void* p = nullptr;
+	int rc = cnb_alloc(ctx_, in_bytes, &p);
+	if (rc != CNB_OK) { fail(rc, "pipeline staging"); return false; }
+	stage_in_ = static_cast<char*>(p);
+	if ((rc = cnb_alloc(ctx_, (size_t) batch_ * sizeof(int32_t), &p)) != CNB_OK) { fail(rc, "pipeline staging"); return false; }
+	stage_labels_ = static_cast<int32_t*>(p);
+	return true;
+}
+
+bool CNet::prefetchBatch(const float* re, const float* im, const int* tokens, const int* labels, int B) {
+	if (!ctx_) { fail(CNB_ERR_ARG, "prefetchBatch: allocateOnGpu first"); return false; }
+	if (B <= 0 || B > batch_) { fail(CNB_ERR_ARG, "prefetchBatch: batch " + std::to_string(B) + " exceeds the allocated " + std::to_string(batch_)); return false; }
+	if (!pipelineInit()) return false;
+	cudaStream_t cs = (cudaStream_t) copy_stream_;
+	cudaError_t e = cudaStreamWaitEvent(cs, (cudaEvent_t) ev_commit_, 0);      // staging of the previous batch consumed
+	if (CEmbedding* em = dynamic_cast<CEmbedding*>(main_in_)) {
+		if (!tokens) { fail(CNB_ERR_ARG, "prefetchBatch: token ids expected"); return false; }
+		if (e == cudaSuccess) e = cudaMemcpyAsync(stage_in_, tokens, (size_t) B * em->noOutTokens() * sizeof(int32_t), cudaMemcpyHostToDevice, cs);
+	} else {
+		if (!re || !im) { fail(CNB_ERR_ARG, "prefetchBatch: re/im planes expected"); return false; }
+		size_t bytes = (size_t) B * main_in_->out_size_ * sizeof(float);
+		if (e == cudaSuccess) e = cudaMemcpyAsync(stage_in_, re, bytes, cudaMemcpyHostToDevice, cs);
+		if (e == cudaSuccess) e = cudaMemcpyAsync(stage_in_ + bytes, im, bytes, cudaMemcpyHostToDevice, cs);
+	}
+	if (e == cudaSuccess && labels) e = cudaMemcpyAsync(stage_labels_, labels, (size_t) B * sizeof(int32_t), cudaMemcpyHostToDevice, cs);
+	if (e == cudaSuccess) e = cudaEventRecord((cudaEvent_t) ev_h2d_, cs);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("prefetchBatch: ") + cudaGetErrorString(e)); return false; }
+	staged_batch_ = B;
+	return true;
+}
+
+bool CNet::commitBatch() {
+	if (!copy_stream_ || staged_batch_ <= 0) { fail(CNB_ERR_ARG, "commitBatch: no staged batch"); return false; }
+	cudaStream_t ms = (cudaStream_t) stream_;
+	int B = staged_batch_;
+	cudaError_t e = cudaStreamWaitEvent(ms, (cudaEvent_t) ev_h2d_, 0);
+	if (e == cudaSuccess && d2h_pending_) e = cudaStreamWaitEvent(ms, (cudaEvent_t) ev_d2h_, 0);   // losses of the last step are out
+	if (CEmbedding* em = dynamic_cast<CEmbedding*>(main_in_)) {
+		if (e == cudaSuccess) e = cudaMemcpyAsync(em->tokens_, stage_in_, (size_t) B * em->noOutTokens() * sizeof(int32_t), cudaMemcpyDeviceToDevice, ms);
+	} else {
+		size_t bytes = (size_t) B * main_in_->out_size_ * sizeof(float);
+		if (e == cudaSuccess) e = cudaMemcpyAsync(main_in_->out_.real_, stage_in_, bytes, cudaMemcpyDeviceToDevice, ms);
+		if (e == cudaSuccess) e = cudaMemcpyAsync(main_in_->out_.imag_, stage_in_ + bytes, bytes, cudaMemcpyDeviceToDevice, ms);
+	}
+	if (e == cudaSuccess) e = cudaMemcpyAsync(main_out_->labels_, stage_labels_, (size_t) B * sizeof(int32_t), cudaMemcpyDeviceToDevice, ms);
+	if (e == cudaSuccess) e = cudaEventRecord((cudaEvent_t) ev_commit_, ms);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("commitBatch: ") + cudaGetErrorString(e)); return false; }
+	cur_batch_ = B;
+	staged_batch_ = 0;
+	return true;
+}
+
+bool CNet::readLossesAsync(float* host_out, int n) {
+	if (!ctx_ || n <= 0 || n > cur_batch_) { fail(CNB_ERR_ARG, "readLossesAsync: bad count"); return false; }
+	if (!pipelineInit()) return false;
+	cudaStream_t cs = (cudaStream_t) copy_stream_;
+	cudaError_t e = cudaEventRecord((cudaEvent_t) ev_step_, (cudaStream_t) stream_);
+	if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, (cudaEvent_t) ev_step_, 0);
+	if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, main_out_->loss_, (size_t) n * sizeof(float), cudaMemcpyDeviceToHost, cs);
+	if (e == cudaSuccess) e = cudaEventRecord((cudaEvent_t) ev_d2h_, cs);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("readLossesAsync: ") + cudaGetErrorString(e)); return false; }
+	d2h_pending_ = true;
+	return true;
+}
+
+bool CNet::waitLosses() {
+	if (!d2h_pending_) return true;
+	cudaError_t e = cudaEventSynchronize((cudaEvent_t) ev_d2h_);
+	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("waitLosses: ") + cudaGetErrorString(e)); return false; }
 	return true;
 }
 

@@ -350,6 +350,17 @@ class CNet {
 	bool capturing_ = false;
 	unsigned long long graph_launches_ = 0;         // kernels inside the captured step
 	bool reduceBucket(size_t index);
+	// double-buffered input pipeline (prefetchBatch / commitBatch / readLossesAsync)
+	void* copy_stream_ = nullptr;                   // cudaStream_t for host <-> device copies
+	void* ev_h2d_ = nullptr;                        // staged batch has arrived
+	void* ev_commit_ = nullptr;                     // staging buffer has been consumed
+	void* ev_step_ = nullptr;                       // losses of the step are final
+	void* ev_d2h_ = nullptr;                        // losses have reached the host
+	char* stage_in_ = nullptr;                      // device staging: [re | im] planes or token ids
+	int32_t* stage_labels_ = nullptr;
+	int staged_batch_ = 0;
+	bool d2h_pending_ = false;
+	bool pipelineInit();
 
 	void fail(int status, const std::string& where);
 	bool planFusion();
@@ -400,6 +411,16 @@ public:
 
 	// batch upload (batchToGpu, gpu/gpu_func.h:368-427): ONE copy per plane
 	bool batchToGpu(const float* re, const float* im, const int* tokens, const int* labels, int batch);
+	// Input pipeline (the reference uploads 2*B small copies synchronously before every forward,
+	// gpu/gpu_func.h:368-427).  prefetchBatch() starts the host-to-device copy of the NEXT batch into a
+	// staging buffer on a copy stream while the current step runs; commitBatch() makes the compute
+	// stream wait for it and moves it into the input tensors (device-to-device); readLossesAsync()
+	// brings the per-sample losses back on the copy stream and waitLosses() blocks until they arrived.
+	// Host buffers should be pinned, or the copies are not asynchronous.
+	bool prefetchBatch(const float* re, const float* im, const int* tokens, const int* labels, int batch);
+	bool commitBatch();
+	bool readLossesAsync(float* host_out, int n);
+	bool waitLosses();
 	// the step
 	void forward();                                 // all layers, insertion order (impl/cnet.h:366-377)
 	void backward();                                // reverse order with the uploaded labels
@@ -412,6 +433,15 @@ public:
 	float getLoss(OutputFunc* outp, Batch* batch);  // mean loss, per-sample losses into the batch
 	bool getLosses(float* out, int n);
 	bool sync();
+
+	// Checkpoints in the reference's ModelSaver byte format (impl/model_saver.h; CNet::save / restore,
+	// gpu/gpu_func.h:1103-1111).  restore() needs an empty net; allocateOnGpu afterwards.
+	bool save(const std::string& file);
+	bool restore(const std::string& file);
+	std::string saveToString();
+	bool restoreFromString(const std::string& data);
+	int noFunctions() const { return (int) func_list_.size(); }
+	int uidAt(int i) const { return func_list_.at(i)->uid(); }
 
 	bool readOutput(int uid, int what, float* re, float* im);   // 0 values, 1 dL/dz*: for tests
 	bool ok() const { return ok_; }

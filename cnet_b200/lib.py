@@ -85,6 +85,10 @@ SIGNATURES = {
     "cnh_required_arena": (_sz, [_vp, C.c_int]),
     "cnh_allocate": (C.c_int, [_vp, C.c_int]),
     "cnh_upload": (C.c_int, [_vp, _P, _P, _P, _P, C.c_int]),
+    "cnh_prefetch": (C.c_int, [_vp, _P, _P, _P, _P, C.c_int]),
+    "cnh_commit": (C.c_int, [_vp]),
+    "cnh_read_losses_async": (C.c_int, [_vp, _P, C.c_int]),
+    "cnh_wait_losses": (C.c_int, [_vp]),
     "cnh_forward": (C.c_int, [_vp]),
     "cnh_backward": (C.c_int, [_vp]),
     "cnh_backward_label": (C.c_int, [_vp, C.c_int]),
@@ -95,6 +99,12 @@ SIGNATURES = {
     "cnh_grad_arena": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_sz), C.POINTER(C.c_int)]),
     "cnh_weight_arena": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_sz)]),
     "cnh_context": (_vp, [_vp]),
+    "cnh_save": (C.c_int, [_vp, C.c_char_p]),
+    "cnh_restore": (C.c_int, [_vp, C.c_char_p]),
+    "cnh_num_funcs": (C.c_int, [_vp]),
+    "cnh_uid_at": (C.c_int, [_vp, C.c_int]),
+    "cnh_type_of": (C.c_int, [_vp, C.c_int]),
+    "cnh_in_size": (C.c_int, [_vp, C.c_int]),
     "cnh_dp_unique_id": (C.c_int, [C.c_char_p]),
     "cnh_dp_init": (C.c_int, [_vp, C.c_char_p, C.c_int, C.c_int]),
     "cnh_dp_async_error": (C.c_int, [_vp]),

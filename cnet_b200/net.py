@@ -88,6 +88,31 @@ class Net:
     def get_wgrad(self, uid):
         return self._pair(self.lib.cnh_get_wgrad, uid, "get_wgrad")
 
+    # ------------------------------------------------------------ checkpoints
+    def save(self, path):
+        """CNet::save: the reference's ModelSaver byte format (weights are read back from the device first)."""
+        self._check(self.lib.cnh_save(self.h, str(path).encode()), "save")
+
+    @classmethod
+    def restore(cls, path, device=0):
+        """CNet::restore into a fresh net; returns it (not yet allocated on the GPU)."""
+        net = cls(device=device)
+        net._check(net.lib.cnh_restore(net.h, str(path).encode()), "restore")
+        for i in range(net.lib.cnh_num_funcs(net.h)):
+            uid = net.lib.cnh_uid_at(net.h, i)
+            t = net.lib.cnh_type_of(net.h, uid)
+            in_len = net.lib.cnh_in_size(net.h, uid) if t == EMBEDDING else net.lib.cnh_out_size(net.h, uid)
+            net._specs[uid] = (t, in_len)
+            if i == 0:
+                net.main_is_tokens = t == EMBEDDING
+        return net
+
+    def uids(self):
+        return [self.lib.cnh_uid_at(self.h, i) for i in range(self.lib.cnh_num_funcs(self.h))]
+
+    def type_of(self, uid):
+        return self.lib.cnh_type_of(self.h, uid)
+
     # ----------------------------------------------------------------- device
     def allocate(self, batch, fuse=True, stream=None):
         """allocateOnGpu(batch): plan the batched tensors in one arena and upload the weights."""
@@ -129,6 +154,28 @@ class Net:
             rc = self.lib.cnh_upload(self.h, _addr(x[0]), _addr(x[1]), None, _addr(labels), B)
         self._check(rc, "batchToGpu")
         self.cur_batch = B
+
+    def prefetch(self, x=None, tokens=None, labels=None, batch=None):
+        """Start copying the NEXT batch (pinned host buffers) to a device staging area on the copy stream."""
+        if tokens is not None:
+            B = batch or tokens.shape[0]
+            rc = self.lib.cnh_prefetch(self.h, None, None, _addr(tokens), _addr(labels), B)
+        else:
+            B = batch or x[0].shape[0]
+            rc = self.lib.cnh_prefetch(self.h, _addr(x[0]), _addr(x[1]), None, _addr(labels), B)
+        self._check(rc, "prefetchBatch")
+        self._staged = B
+
+    def commit(self):
+        """Make the staged batch the current one (compute stream waits for its copy)."""
+        self._check(self.lib.cnh_commit(self.h), "commitBatch")
+        self.cur_batch = self._staged
+
+    def read_losses_async(self, pinned_out, n):
+        self._check(self.lib.cnh_read_losses_async(self.h, _addr(pinned_out), n), "readLossesAsync")
+
+    def wait_losses(self):
+        self._check(self.lib.cnh_wait_losses(self.h), "waitLosses")
 
     def forward(self):
         self._check(self.lib.cnh_forward(self.h), "forward")

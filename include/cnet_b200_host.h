@@ -43,6 +43,14 @@ int cnh_allocate(cnh_net* net, int batch);                                   /* 
 /* batchToGpu (gpu/gpu_func.h:368-427): planes [B, n] or tokens [B, T]; labels [B] */
 int cnh_upload(cnh_net* net, const float* re, const float* im, const int32_t* tokens,
                const int32_t* labels, int batch);
+/* Double-buffered input pipeline (replaces the synchronous per-sample copies of batchToGpu): start the
+ * H2D copy of the NEXT batch from pinned host memory on a copy stream; commit = compute stream waits
+ * for it and moves it into the input tensors; losses come back asynchronously. */
+int cnh_prefetch(cnh_net* net, const float* re, const float* im, const int32_t* tokens,
+                 const int32_t* labels, int batch);
+int cnh_commit(cnh_net* net);
+int cnh_read_losses_async(cnh_net* net, float* pinned_host_out, int n);
+int cnh_wait_losses(cnh_net* net);
 int cnh_forward(cnh_net* net);                                               /* GpuForward, :645-657 */
 int cnh_backward(cnh_net* net);                                              /* gpuBackward, :1096-1101 */
 int cnh_backward_label(cnh_net* net, int label);                             /* CNet::backward(label) */
@@ -52,6 +60,15 @@ int cnh_sync(cnh_net* net);
 int cnh_read_output(cnh_net* net, int uid, int what, float* re, float* im); /* testDataFromGpu, :840-862 */
 int cnh_grad_arena(cnh_net* net, void** dev_ptr, size_t* count, int* n_buckets);
 int cnh_weight_arena(cnh_net* net, void** dev_ptr, size_t* count);
+/* CNet::save / CNet::restore (gpu/gpu_func.h:1103-1111) in the reference's ModelSaver byte format
+ * (impl/model_saver.h:27, 530-795): files written here load in the reference and vice versa.
+ * cnh_restore needs an empty net; the graph can then be inspected and allocated. */
+int cnh_save(cnh_net* net, const char* path);
+int cnh_restore(cnh_net* net, const char* path);
+int cnh_num_funcs(cnh_net* net);
+int cnh_uid_at(cnh_net* net, int index);
+int cnh_type_of(cnh_net* net, int uid);
+int cnh_in_size(cnh_net* net, int uid);
 void* cnh_context(cnh_net* net);                                             /* the cnb_ctx* of the net */
 
 /* Data parallelism (no counterpart in the reference, which is single-GPU: gpu/gpu_func.h:38-40; the

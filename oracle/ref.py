@@ -36,6 +36,13 @@ def lib():
         _lib.ref_out_size.argtypes = [C.c_void_p, C.c_int]
         _lib.ref_update.argtypes = [C.c_void_p, C.c_float, C.c_int]
         _lib.ref_set_threads.argtypes = [C.c_int]
+        _lib.ref_save.argtypes = [C.c_void_p, C.c_char_p]
+        _lib.ref_restore.argtypes = [C.c_char_p]
+        _lib.ref_restore.restype = C.c_void_p
+        for n in ("ref_num_funcs",):
+            getattr(_lib, n).argtypes = [C.c_void_p]
+        for n in ("ref_uid_at", "ref_type_of", "ref_in_len"):
+            getattr(_lib, n).argtypes = [C.c_void_p, C.c_int]
     return _lib
 
 
@@ -57,7 +64,8 @@ def max_threads():
 
 class RefNet:
     def __init__(self):
-        self.h = C.c_void_p(lib().ref_create())
+        lib()
+        self.h = C.c_void_p(_lib.ref_create())
         self.in_len = {}
         self.B = 0
 
@@ -65,6 +73,29 @@ class RefNet:
         if getattr(self, "h", None):
             lib().ref_destroy(self.h)
             self.h = None
+
+    def save(self, path):
+        """ModelSaver::Save of the reference (impl/model_saver.h:799-821)."""
+        assert lib().ref_save(self.h, str(path).encode()) == 0
+
+    @classmethod
+    def restore(cls, path):
+        """ModelSaver::Restore of the reference into a fresh ComplexNet."""
+        self = cls.__new__(cls)
+        self.h = C.c_void_p(lib().ref_restore(str(path).encode()))
+        assert self.h, "reference could not restore " + str(path)
+        self.B = 0
+        self.in_len = {}
+        for i in range(lib().ref_num_funcs(self.h)):
+            uid = lib().ref_uid_at(self.h, i)
+            self.in_len[uid] = lib().ref_in_len(self.h, uid)
+        return self
+
+    def uids(self):
+        return [lib().ref_uid_at(self.h, i) for i in range(lib().ref_num_funcs(self.h))]
+
+    def type_of(self, uid):
+        return lib().ref_type_of(self.h, uid)
 
     def add(self, type_, a=0, b=0, c=0, prev=()):
         p = np.asarray(list(prev), np.int32)

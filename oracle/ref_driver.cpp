@@ -15,6 +15,7 @@
 //   for b in batch: setInput; forward; loss; backward(label_b)
 //   update(lr, batch)          -> w -= (lr/batch) * sum_b dz*_w
 #include "impl/cnet.h"
+#include "impl/model_saver.h"
 
 #include <chrono>
 #include <map>
@@ -195,6 +196,26 @@ int ref_out_size(void* h, int uid) {
 	CFunc* f = fn(static_cast<RefNet*>(h), uid);
 	return f ? f->outSize() : -1;
 }
+
+// Checkpoints through the reference's own ModelSaver (impl/model_saver.h:799-821, 908-967).
+int ref_save(void* h, const char* path) {
+	ModelSaver saver;
+	return saver.Save(static_cast<RefNet*>(h)->net, path) ? 0 : -1;
+}
+
+void* ref_restore(const char* path) {
+	FILELog::ReportingLevel() = lError;
+	RefNet* r = new RefNet();
+	ModelSaver saver;
+	if (!saver.Restore(r->net, path)) { delete r; return NULL; }
+	for (auto f : r->net.functionList()) r->uids.push_back(f->uid());
+	return r;
+}
+
+int ref_num_funcs(void* h) { return (int) static_cast<RefNet*>(h)->uids.size(); }
+int ref_uid_at(void* h, int i) { return static_cast<RefNet*>(h)->uids[i]; }
+int ref_type_of(void* h, int uid) { return ComplexNet::getType(fn(static_cast<RefNet*>(h), uid)); }
+int ref_in_len(void* h, int uid) { return fn(static_cast<RefNet*>(h), uid)->input().length_; }
 
 int ref_update(void* h, float lr, int batch_size) {
 	static_cast<RefNet*>(h)->net.update(lr, batch_size);

@@ -27,3 +27,10 @@ if __name__ == "__main__":
         np.savez_compressed(path, **{k: np.asarray(v, np.float32) if not k.startswith("loss") else v
                                      for k, v in out.items()})
         print(name, len(out), "arrays", os.path.getsize(path) // 1024, "KiB")
+    # a checkpoint written by the reference's own ModelSaver (impl/model_saver.h:799-821)
+    from cnet_b200 import configs
+    net = ref.RefNet()
+    spec = configs.build_embed_lm(net, tokens=4, vocab=32, dim=8, hidden=16)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    net.save(os.path.join(util.GOLDEN_DIR, "embed_lm_small.cnet"))

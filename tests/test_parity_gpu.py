@@ -128,3 +128,60 @@ def test_graph_replay_matches_eager_steps():
         runs.append((np.array(losses), tr.net.get_values(tr.spec.layers["w0"])))
     assert util.relerr(runs[1][0], runs[0][0]) < 1e-5
     assert util.relerr(runs[1][1], runs[0][1]) < 1e-5
+
+
+def test_input_pipeline_matches_plain_uploads():
+    """prefetch / commit / async loss read-back give the same training run as synchronous uploads."""
+    import torch
+    from cnet_b200.dp import DataParallelTrainer
+    kw = dict(n=128, blocks=1, m=10)
+    B, steps = 64, 5
+    batches = []
+    runs = []
+    for pipelined in (False, True):
+        tr = DataParallelTrainer(configs.build_mixer, kw, global_batch=B, lr=0.5, device=0, seed=0)
+        if not batches:
+            for s in range(steps):
+                (xr, xi), labels = configs.make_batch(tr.spec, B, 0, step=s)
+                batches.append(((torch.from_numpy(xr).pin_memory(), torch.from_numpy(xi).pin_memory()),
+                                torch.from_numpy(labels).pin_memory()))
+        losses = []
+        if pipelined:
+            outs = [torch.empty(B).pin_memory() for _ in range(steps)]
+            tr.prefetch(*batches[0])
+            for s in range(steps):
+                nxt = batches[s + 1] if s + 1 < steps else (None, None)
+                tr.step_pipelined(nxt[0], nxt[1], outs[s])
+            tr.net.wait_losses()
+            losses = [float(o.mean()) for o in outs]
+        else:
+            for s in range(steps):
+                losses.append(float(tr.step(*batches[s]).mean()))
+        torch.cuda.synchronize()
+        runs.append((np.array(losses), tr.net.get_values(tr.spec.layers["w0"])))
+    assert util.relerr(runs[1][0], runs[0][0]) < 1e-6
+    assert util.relerr(runs[1][1], runs[0][1]) < 1e-6
+
+
+def test_restored_checkpoint_trains_on_the_device(tmp_path):
+    """A checkpoint written by the reference loads, runs on the GPU like the restatement, and the weights
+    saved after an update are the device's."""
+    import os
+    path = os.path.join(util.GOLDEN_DIR, "embed_lm_small.cnet")
+    dev = Net.restore(path)
+    ora = cnet_oracle.OracleNet()
+    spec = configs.build_embed_lm(ora, tokens=4, vocab=32, dim=8, hidden=16)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        ora.set_values(uid, re, im)
+    dev.allocate(6)
+    tok, labels = configs.make_batch(spec, 6, 0)
+    ld = dev.run_batch(spec.main, tokens=tok, labels=labels)
+    lo = ora.run_batch(spec.main, tokens=tok, labels=labels)
+    assert util.relerr(ld, lo) < 1e-4
+    dev.update(0.01, 6)
+    ora.update(0.01, 6)
+    out = tmp_path / "trained.cnet"
+    dev.save(out)
+    again = Net.restore(out)
+    for name in ("emb", "w1", "w2"):
+        assert util.relerr(again.get_values(spec.layers[name]), ora.get_values(spec.layers[name])) < 1e-4
