@@ -14,7 +14,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 # layer type ids: the reference's own (impl/cnet.h:31-44)
-HADAMARD, EMBEDDING, LINEAR, FOURIER, CROSSENT, RESIDUAL, SOFTMAX, INPUT, CRELU, GELU = range(1, 11)
+HADAMARD, EMBEDDING, LINEAR, FOURIER, CROSSENT, RESIDUAL, SOFTMAX, INPUT, CRELU, GELU, L2OUT, TRIFOURIER = range(1, 13)
 
 
 @dataclass
@@ -97,6 +97,18 @@ def build_embed_lm(net, tokens=64, vocab=8192, dim=256, hidden=2048):
                    [(emb, vocab * dim, 0.02), (w1, d * hidden, d ** -0.5), (w2, hidden * vocab, hidden ** -0.5)],
                    tokens=True, vocab=vocab,
                    layers=dict(emb=emb, w1=w1, l1=l1, gelu=g, w2=w2, l2=l2, sm=sm, ce=ce))
+
+
+def build_relu_tri(net, n=24, m=6):
+    """The layers no benchmark config uses: CInput -> TriangFourier -> CRelu -> Linear(n->m) -> L2Out."""
+    x = net.add(INPUT, n)
+    tf = net.add(TRIFOURIER, n, prev=[x])
+    r = net.add(CRELU, n, prev=[tf])
+    w = net.add(INPUT, n * m)
+    lin = net.add(LINEAR, n, n * m, prev=[r, w])
+    out = net.add(L2OUT, m, prev=[lin])
+    return NetSpec("relu_tri", x, out, n, m, [(w, n * m, n ** -0.5)],
+                   layers=dict(x=x, tf=tf, relu=r, w=w, lin=lin, ce=out))
 
 
 def _rng(seed, stream):

@@ -3,6 +3,7 @@
 // All kernels stream each plane once with 16-byte accesses where the row length allows
 // it (W = 4), else scalar (W = 1); grids are sized in multiples of the SM count.
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 
 #include "common.cuh"
@@ -254,6 +255,44 @@ __global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* _
     }
 }
 
+// --------------------------------------------------------------------- CRelu
+// y = z where re > 0 and im > 0, else 0; the backward passes g* through the same gate.
+template <int W>
+__global__ void crelu_k(const float* __restrict__ zr, const float* __restrict__ zi,
+                        const float* __restrict__ sr, const float* __restrict__ si,
+                        float* __restrict__ dr, float* __restrict__ di, int accumulate, size_t total) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        Pack<W> a = ld<W>(zr, i), b = ld<W>(zi, i), x = ld<W>(sr, i), y = ld<W>(si, i), r, s;
+        if (accumulate) { r = ld<W>(dr, i); s = ld<W>(di, i); }
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            bool on = a.v[k] > 0.f && b.v[k] > 0.f;
+            float vr = on ? x.v[k] : 0.f, vi = on ? y.v[k] : 0.f;
+            r.v[k] = accumulate ? r.v[k] + vr : vr;
+            s.v[k] = accumulate ? s.v[k] + vi : vi;
+        }
+        st<W>(dr, i, r); st<W>(di, i, s);
+    }
+}
+
+// momentum-only "Adam" of the reference: m = beta m + (1-beta) g; w -= lr m / (1 - beta^(t+1)); g = 0
+template <int W>
+__global__ void adam_k(float* __restrict__ w, float* __restrict__ m, float* __restrict__ g, size_t total, float lr_hat,
+                       float beta) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * W;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
+        Pack<W> a = ld<W>(w, i), b = ld<W>(m, i), c = ld<W>(g, i);
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            b.v[k] = b.v[k] * beta + (1.f - beta) * c.v[k];
+            a.v[k] -= lr_hat * b.v[k];
+            c.v[k] = 0.f;
+        }
+        st<W>(w, i, a); st<W>(m, i, b); st<W>(g, i, c);
+    }
+}
+
 // ------------------------------------------------- Residual, pass-through, SGD
 template <int W>
 __global__ void add2_k(const float* __restrict__ ur, const float* __restrict__ ui,
@@ -469,6 +508,35 @@ int cnb_axpy(cnb_ctx* ctx, const float* src_re, const float* src_im, float* dst_
     }
     bool vec = (n % 4 == 0) && all_aligned(src_re, src_im, dst_re, dst_im);
     DISPATCH_W(vec, add2_k, n, src_re, src_im, dst_re, dst_im, dst_re, dst_im, n);
+    return CNB_OK;
+}
+
+int cnb_crelu_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float* y_re, float* y_im, size_t n,
+                  void* stream) {
+    CNB_CHECK_ARG(ctx && z_re && z_im && y_re && y_im && n > 0, "cnb_crelu_fwd: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    bool vec = (n % 4 == 0) && all_aligned(z_re, z_im, y_re, y_im);
+    DISPATCH_W(vec, crelu_k, n, z_re, z_im, z_re, z_im, y_re, y_im, 0, n);
+    return CNB_OK;
+}
+
+int cnb_crelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const float* z_re, const float* z_im,
+                  float* dz_re, float* dz_im, size_t n, int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && z_re && z_im && dz_re && dz_im && n > 0, "cnb_crelu_bwd: bad argument");
+    cudaStream_t stm = cnb::S(stream);
+    bool vec = (n % 4 == 0) && all_aligned(g_re, g_im, z_re, z_im, dz_re, dz_im);
+    DISPATCH_W(vec, crelu_k, n, z_re, z_im, g_re, g_im, dz_re, dz_im, accumulate, n);
+    return CNB_OK;
+}
+
+int cnb_adam_update(cnb_ctx* ctx, float* w, float* m, float* g, size_t n, float lr, float beta, int t,
+                    void* stream) {
+    CNB_CHECK_ARG(ctx && w && m && g && n > 0 && t >= 0, "cnb_adam_update: bad argument");
+    CNB_CHECK_ARG(beta >= 0.f && beta < 1.f, "cnb_adam_update: beta=%f", beta);
+    cudaStream_t stm = cnb::S(stream);
+    float lr_hat = (float) ((double) lr / (1.0 - pow((double) beta, t + 1)));
+    bool vec = (n % 4 == 0) && all_aligned(w, m, g);
+    DISPATCH_W(vec, adam_k, n, w, m, g, n, lr_hat, beta);
     return CNB_OK;
 }
 

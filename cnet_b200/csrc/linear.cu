@@ -23,8 +23,18 @@ __global__ void twiddle_k(float* __restrict__ fr, float* __restrict__ fi, int N)
     }
 }
 
-int get_twiddle(cnb_ctx* ctx, int N, cudaStream_t st, cnb_twiddle* out) {
-    auto it = ctx->twiddles.find(N);
+// TriangFourier: the same matrix with the entries above the diagonal (q > p) zeroed
+__global__ void tri_mask_k(float* __restrict__ fr, float* __restrict__ fi, int N) {
+    size_t total = (size_t) N * N;
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t) gridDim.x * blockDim.x)
+        if ((int) (i % N) > (int) (i / N)) { fr[i] = 0.f; fi[i] = 0.f; }
+}
+
+const int kTriKey = 1 << 28;    // twiddle-cache key offset of the triangular matrices
+
+int get_twiddle(cnb_ctx* ctx, int key, cudaStream_t st, cnb_twiddle* out) {
+    const int N = key & (kTriKey - 1);
+    auto it = ctx->twiddles.find(key);
     if (it != ctx->twiddles.end()) { *out = it->second; return CNB_OK; }
     cnb_twiddle t;
     void* p = nullptr;
@@ -36,7 +46,11 @@ int get_twiddle(cnb_ctx* ctx, int N, cudaStream_t st, cnb_twiddle* out) {
     t.im = static_cast<float*>(p);
     twiddle_k<<<ctx->sm_count * 4, 256, 0, st>>>(t.re, t.im, N);
     CNB_LAUNCH_CHECK("twiddle");
-    ctx->twiddles[N] = t;
+    if (key & kTriKey) {
+        tri_mask_k<<<ctx->sm_count * 4, 256, 0, st>>>(t.re, t.im, N);
+        CNB_LAUNCH_CHECK("tri_mask");
+    }
+    ctx->twiddles[key] = t;
     *out = t;
     return CNB_OK;
 }
@@ -207,6 +221,26 @@ int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_sp
     cnb::g_last_engine = 1;
     return cnb::cgemm_tc_presplit(ctx, a, 1, b, 1, 1, nullptr, nullptr, dw_re, dw_im, out, in, B, accumulate,
                                   cnb::S(stream));
+}
+
+int cnb_tdft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, float* y_re, float* y_im, int B, int N,
+                 void* stream) {
+    CNB_CHECK_ARG(ctx && x_re && x_im && y_re && y_im, "cnb_tdft_fwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0 && N <= 16384, "cnb_tdft_fwd: B=%d N=%d (N <= 16384)", B, N);
+    cnb_twiddle t;
+    int rc = get_twiddle(ctx, N | kTriKey, cnb::S(stream), &t);
+    if (rc != CNB_OK) return rc;
+    return cnb_linear_fwd(ctx, x_re, x_im, t.re, t.im, nullptr, nullptr, y_re, y_im, B, N, N, stream);
+}
+
+int cnb_tdft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re, float* dx_im, int B, int N,
+                 int accumulate, void* stream) {
+    CNB_CHECK_ARG(ctx && g_re && g_im && dx_re && dx_im, "cnb_tdft_bwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && N > 0 && N <= 16384, "cnb_tdft_bwd: B=%d N=%d (N <= 16384)", B, N);
+    cnb_twiddle t;
+    int rc = get_twiddle(ctx, N | kTriKey, cnb::S(stream), &t);
+    if (rc != CNB_OK) return rc;
+    return cnb_linear_bwd_x(ctx, g_re, g_im, t.re, t.im, dx_re, dx_im, B, N, N, accumulate, stream);
 }
 
 int cnb_set_gemm_sm_limit(cnb_ctx* ctx, int max_ctas) {

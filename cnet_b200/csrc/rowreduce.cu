@@ -90,6 +90,21 @@ __global__ void crossent_k(const float* __restrict__ zr, const float* __restrict
     }
 }
 
+// L2Out: loss[b] = sum |z|^2; seed dz* = z
+__global__ void l2out_k(const float* __restrict__ zr, const float* __restrict__ zi, float* __restrict__ loss,
+                        float* __restrict__ dr, float* __restrict__ di, int N) {
+    __shared__ float sm[32];
+    size_t base = (size_t) blockIdx.x * N;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float a = zr[base + i], b = zi[base + i];
+        s += a * a + b * b;
+        if (dr) { dr[base + i] = a; di[base + i] = b; }
+    }
+    s = block_sum(s, sm);
+    if (threadIdx.x == 0) loss[blockIdx.x] = s;
+}
+
 inline int threads_for(int n) {
     int t = 32;
     while (t < n / 4 && t < 512) t <<= 1;
@@ -128,6 +143,16 @@ int cnb_crossent_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im, con
     CNB_CHECK_ARG(B > 0 && M > 0, "cnb_crossent_fwd_bwd: B=%d M=%d", B, M);
     crossent_k<<<B, threads_for(M), 0, cnb::S(stream)>>>(z_re, z_im, labels, loss, dz_re, dz_im, M);
     CNB_LAUNCH_CHECK("crossent");
+    return CNB_OK;
+}
+
+int cnb_l2out_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float* loss, float* dz_re, float* dz_im,
+                      int B, int N, void* stream) {
+    CNB_CHECK_ARG(ctx && z_re && z_im && loss, "cnb_l2out_fwd_bwd: null pointer");
+    CNB_CHECK_ARG((dz_re == nullptr) == (dz_im == nullptr), "cnb_l2out_fwd_bwd: dz planes must be a pair");
+    CNB_CHECK_ARG(B > 0 && N > 0, "cnb_l2out_fwd_bwd: B=%d N=%d", B, N);
+    l2out_k<<<B, threads_for(N), 0, cnb::S(stream)>>>(z_re, z_im, loss, dz_re, dz_im, N);
+    CNB_LAUNCH_CHECK("l2out");
     return CNB_OK;
 }
 

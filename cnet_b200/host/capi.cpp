@@ -51,6 +51,9 @@ int cnh_add(cnh_net* n, int type, int a, int b, int c, const int* prev, int npre
 	case isResidual:     f = new Residual(InSize(a)); break;
 	case isSoftMax:      f = new SoftMax(InSize(a)); break;
 	case isCrossEntropy: f = new CrossEntropy(InSize(a)); break;
+	case isL2Out:        f = new L2Out(InSize(a)); break;
+	case isCrelu:        f = new CRelu(InSize(a)); break;
+	case isTrianFourier: f = new TriangFourier(InSize(a)); break;
 	default: return CNB_ERR_UNSUPPORTED;
 	}
 	int uid = n->net.add(f, std::vector<int>(prev, prev + nprev));
@@ -87,6 +90,8 @@ int cnh_forward(cnh_net* n) { n->net.forward(); return status(n); }
 int cnh_backward(cnh_net* n) { n->net.backward(); return status(n); }
 int cnh_backward_label(cnh_net* n, int label) { n->net.backward(label); return status(n); }
 int cnh_update(cnh_net* n, float lr) { n->net.updateInputs(lr); return status(n); }
+int cnh_adam_update(cnh_net* n, float lr, float beta, int t) { n->net.adamUpdate(lr, beta, t); return status(n); }
+int cnh_infer(cnh_net* n) { n->net.infer(); return status(n); }
 int cnh_get_losses(cnh_net* n, float* out, int cnt) { n->net.getLosses(out, cnt); return status(n); }
 int cnh_sync(cnh_net* n) { n->net.sync(); return status(n); }
 int cnh_read_output(cnh_net* n, int uid, int what, float* re, float* im) {

@@ -261,6 +261,25 @@ void Linear::backward() {
 	if (use_split_ && cnb_linear_split_ok(batch(), in1_len, out_size_)) {
 		float* gs = net_->g_split_;
 		check(cnb_split_planes(ctx(), out_.dz_star_real_, out_.dz_star_imag_, (size_t) batch() * out_size_, gs, stream()));
+		// Small problems give each of the 148 persistent CTAs only a few k-blocks, so prologue and
+		// epilogue dominate: run the two independent products side by side on half the SMs each.
+		const bool side_by_side = net_->side_stream_ != nullptr &&
+				(size_t) batch() * in1_len * out_size_ <= (size_t) 1536 * 1024 * 1024;
+		if (side_by_side) {
+			cudaStream_t ms = (cudaStream_t) stream(), ss = (cudaStream_t) net_->side_stream_;
+			int limit = net_->dp_gemm_ctas_ > 0 ? net_->dp_gemm_ctas_ : net_->sm_count_;
+			cudaEventRecord((cudaEvent_t) net_->ev_side_fork_, ms);
+			cudaStreamWaitEvent(ss, (cudaEvent_t) net_->ev_side_fork_, 0);
+			cnb_set_gemm_sm_limit(ctx(), limit / 2);
+			check(cnb_linear_bwd_w_split(ctx(), gs, x_split_, pw->out_.dz_star_real_, pw->out_.dz_star_imag_, batch(),
+					in1_len, out_size_, acc_w, ss));
+			check(cnb_linear_bwd_x_split(ctx(), gs, w_split_, px->out_.dz_star_real_, px->out_.dz_star_imag_, batch(),
+					in1_len, out_size_, acc_x, ms));
+			cnb_set_gemm_sm_limit(ctx(), net_->dp_gemm_ctas_ > 0 ? net_->dp_gemm_ctas_ : 0);
+			cudaEventRecord((cudaEvent_t) net_->ev_side_join_, ss);
+			cudaStreamWaitEvent(ms, (cudaEvent_t) net_->ev_side_join_, 0);
+			return;
+		}
 		check(cnb_linear_bwd_w_split(ctx(), gs, x_split_, pw->out_.dz_star_real_, pw->out_.dz_star_imag_, batch(),
 				in1_len, out_size_, acc_w, stream()));
 		check(cnb_linear_bwd_x_split(ctx(), gs, w_split_, px->out_.dz_star_real_, px->out_.dz_star_imag_, batch(),
@@ -307,30 +326,63 @@ void SoftMax::backward() {
 			p->out_.dz_star_real_, p->out_.dz_star_imag_, batch(), in_size_, acc, stream()));
 }
 
-// ------------------------------------------------------------- CrossEntropy
-void CrossEntropy::bindExtra(char* mem, int batch) {
+// ------------------------------------------------------------------- losses
+void LossFunc::bindExtra(char* mem, int batch) {
 	loss_ = reinterpret_cast<float*>(mem);
 	labels_ = reinterpret_cast<int32_t*>(mem + (((size_t) batch * 4 + 255) & ~size_t(255)));
 }
 
-void CrossEntropy::forward() {
-	CFunc* p = prev_func_[0];
-	check(cnb_crossent_fwd_bwd(ctx(), p->out_.real_, p->out_.imag_, labels_, loss_, p->out_.dz_star_real_,
-			p->out_.dz_star_imag_, batch(), in_size_, stream()));
-}
-
-void CrossEntropy::backward(int label) {
+void LossFunc::backward(int label) {
 	std::vector<int32_t> l(batch(), label);
 	check(cnb_h2d(ctx(), labels_, l.data(), l.size() * sizeof(int32_t), stream()));
 	check(cnb_sync(ctx(), stream()));
 	forward();
 }
 
-float CrossEntropy::loss(int sample) {
+float LossFunc::loss(int sample) {
 	float v = 0.f;
 	if (sample < 0 || sample >= batch()) return NAN;
 	check(cnb_d2h(ctx(), &v, loss_ + sample, sizeof(float), stream()));
 	return v;
+}
+
+void CrossEntropy::forward() {
+	CFunc* p = prev_func_[0];
+	bool seed = !net_->infer_only_;
+	check(cnb_crossent_fwd_bwd(ctx(), p->out_.real_, p->out_.imag_, labels_, loss_, seed ? p->out_.dz_star_real_ : nullptr,
+			seed ? p->out_.dz_star_imag_ : nullptr, batch(), in_size_, stream()));
+}
+
+void L2Out::forward() {
+	CFunc* p = prev_func_[0];
+	bool seed = !net_->infer_only_;
+	check(cnb_l2out_fwd_bwd(ctx(), p->out_.real_, p->out_.imag_, loss_, seed ? p->out_.dz_star_real_ : nullptr,
+			seed ? p->out_.dz_star_imag_ : nullptr, batch(), in_size_, stream()));
+}
+
+// -------------------------------------------------------- CRelu, TriangFourier
+void CRelu::forward() {
+	const Vars& z = in(0);
+	check(cnb_crelu_fwd(ctx(), z.real_, z.imag_, out_.real_, out_.imag_, (size_t) batch() * out_size_, stream()));
+}
+
+void CRelu::backward() {
+	CFunc* p = prev_func_[0];
+	int acc = accumulate_into(p);
+	check(cnb_crelu_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, p->out_.real_, p->out_.imag_,
+			p->out_.dz_star_real_, p->out_.dz_star_imag_, (size_t) batch() * out_size_, acc, stream()));
+}
+
+void TriangFourier::forward() {
+	const Vars& x = in(0);
+	check(cnb_tdft_fwd(ctx(), x.real_, x.imag_, out_.real_, out_.imag_, batch(), in_size_, stream()));
+}
+
+void TriangFourier::backward() {
+	CFunc* p = prev_func_[0];
+	int acc = accumulate_into(p);
+	check(cnb_tdft_bwd(ctx(), out_.dz_star_real_, out_.dz_star_imag_, p->out_.dz_star_real_, p->out_.dz_star_imag_,
+			batch(), in_size_, acc, stream()));
 }
 
 // --------------------------------------------------------------------- CNet
@@ -338,6 +390,11 @@ CNet::CNet() {}
 
 CNet::~CNet() {
 	if (graph_exec_) cudaGraphExecDestroy((cudaGraphExec_t) graph_exec_);
+	if (side_stream_) {
+		cudaStreamSynchronize((cudaStream_t) side_stream_);
+		cudaEventDestroy((cudaEvent_t) ev_side_fork_); cudaEventDestroy((cudaEvent_t) ev_side_join_);
+		cudaStreamDestroy((cudaStream_t) side_stream_);
+	}
 	if (copy_stream_) {
 		cudaStreamSynchronize((cudaStream_t) copy_stream_);
 		cudaEventDestroy((cudaEvent_t) ev_h2d_); cudaEventDestroy((cudaEvent_t) ev_commit_);
@@ -369,6 +426,9 @@ int CNet::getType(CFunc* f) {
 	if (dynamic_cast<Residual*>(f)) return isResidual;
 	if (dynamic_cast<SoftMax*>(f)) return isSoftMax;
 	if (dynamic_cast<CrossEntropy*>(f)) return isCrossEntropy;
+	if (dynamic_cast<L2Out*>(f)) return isL2Out;
+	if (dynamic_cast<CRelu*>(f)) return isCrelu;
+	if (dynamic_cast<TriangFourier*>(f)) return isTrianFourier;
 	if (dynamic_cast<CGelu*>(f)) return isGelu;
 	return 0x7fffffff;
 }
@@ -487,7 +547,7 @@ size_t CNet::scratchBytes(int B) const {
 	for (auto f : func_list_) {
 		if (Linear* l = dynamic_cast<Linear*>(f))
 			scratch = std::max(scratch, cnb_linear_workspace(B, l->firstInputLength(), l->outSize()));
-		if (dynamic_cast<FourierTrans*>(f))
+		if (dynamic_cast<FourierTrans*>(f) || dynamic_cast<TriangFourier*>(f))
 			scratch = std::max(scratch, cnb_linear_workspace(B, f->in_size_, f->in_size_));
 		if (f->type_ == isHadamard) scratch = std::max(scratch, (size_t) 128 * f->out_size_ * 2 * sizeof(float));
 	}
@@ -501,7 +561,7 @@ size_t CNet::requiredArenaBytes(int B) const {
 		if (weight) floats += 4 * pad64(f->out_size_);
 		else floats += 4 * pad64((size_t) B * f->out_size_);
 		if (CEmbedding* e = dynamic_cast<CEmbedding*>(f)) floats += 4 * pad64((size_t) e->inSize());
-		if (dynamic_cast<FourierTrans*>(f)) dft += (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512;
+		if (dynamic_cast<FourierTrans*>(f) || dynamic_cast<TriangFourier*>(f)) dft += (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512;
 		extra += f->extraBytes(B) + 256;
 	}
 	size_t gs = 0;
@@ -516,15 +576,21 @@ size_t CNet::requiredArenaBytes(int B) const {
 		else staging = 2 * (size_t) B * f0->out_size_ * 4;
 		staging += (size_t) B * 4 + 1024;
 	}
-	return floats * sizeof(float) + extra + dft + gs + staging + scratchBytes(B) + (16u << 20);
+	size_t momentum = 0;                               // Adam momentum planes (allocated on first adamUpdate)
+	for (auto f : func_list_) {
+		bool weight = dynamic_cast<CInput*>(f) && f != func_list_.front();
+		if (weight) momentum += 2 * pad64(f->out_size_) * sizeof(float);
+		if (CEmbedding* e = dynamic_cast<CEmbedding*>(f)) momentum += 2 * pad64((size_t) e->inSize()) * sizeof(float);
+	}
+	return floats * sizeof(float) + extra + dft + gs + staging + momentum + scratchBytes(B) + (16u << 20);
 }
 
 bool CNet::allocateOnGpu(int B) {
 	if (ctx_) { fail(CNB_ERR_ARG, "allocateOnGpu: already allocated"); return false; }
 	if (B <= 0 || func_list_.empty()) { fail(CNB_ERR_ARG, "allocateOnGpu: empty net or batch"); return false; }
 	main_in_ = findFirstInput();
-	main_out_ = dynamic_cast<CrossEntropy*>(findFirstOutput());
-	if (!main_in_ || !main_out_) { fail(CNB_ERR_ARG, "allocateOnGpu: net needs an InputFunc and a CrossEntropy output"); return false; }
+	main_out_ = dynamic_cast<LossFunc*>(findFirstOutput());
+	if (!main_in_ || !main_out_) { fail(CNB_ERR_ARG, "allocateOnGpu: net needs an InputFunc and a loss output (CrossEntropy or L2Out)"); return false; }
 	dynamic_cast<InputFunc*>(main_in_)->setIsMainInput(true);
 	main_out_->setIsMainOutput(true);
 	init_exec_graph();
@@ -564,6 +630,16 @@ bool CNet::allocateOnGpu(int B) {
 			: cnb_create(device_, arena_bytes_, &ctx_);
 	if (rc != CNB_OK) { fail(rc, "allocateOnGpu"); ctx_ = nullptr; return false; }
 	batch_ = cur_batch_ = B;
+	cnb_device_info(device_, &sm_count_, nullptr, nullptr, nullptr);
+	if (stream_ && !side_stream_) {             // a second stream only makes sense beside a real (non-default) stream
+		cudaStream_t st;
+		cudaEvent_t e0, e1;
+		if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess &&
+				cudaEventCreateWithFlags(&e0, cudaEventDisableTiming) == cudaSuccess &&
+				cudaEventCreateWithFlags(&e1, cudaEventDisableTiming) == cudaSuccess) {
+			side_stream_ = st; ev_side_fork_ = e0; ev_side_join_ = e1;
+		}
+	}
 	if ((rc = cnb_reserve_scratch(ctx_, scratchBytes(B))) != CNB_OK) { fail(rc, "scratch"); return false; }
 
 	// 1. weights: one block of value planes and one block of dz* planes with the same layout,
@@ -943,6 +1019,30 @@ void CNet::updateInputs(float lr) {
 	++weights_version_;
 	for (auto f : func_list_)
 		if (Linear* l = dynamic_cast<Linear*>(f)) l->splitWeights();
+}
+
+void CNet::adamUpdate(float lr, float beta, int t) {
+	if (!ctx_ || !wgrad_count_) return;
+	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, 0);
+	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
+	if (!momentum_base_) {
+		void* p = nullptr;
+		int rc = cnb_alloc(ctx_, wgrad_count_ * sizeof(float), &p);
+		if (rc != CNB_OK) { fail(rc, "adamUpdate: momentum planes (size the arena for them)"); return; }
+		momentum_base_ = static_cast<float*>(p);
+		cnb_memset0(ctx_, momentum_base_, wgrad_count_ * sizeof(float), stream_);
+	}
+	int rc = cnb_adam_update(ctx_, weight_base_, momentum_base_, wgrad_base_, wgrad_count_, lr, beta, t, stream_);
+	if (rc != CNB_OK) { fail(rc, "adamUpdate"); return; }
+	++weights_version_;
+	for (auto f : func_list_)
+		if (Linear* l = dynamic_cast<Linear*>(f)) l->splitWeights();
+}
+
+void CNet::infer() {
+	infer_only_ = true;
+	forward();
+	infer_only_ = false;
 }
 
 bool CNet::gpuForward(InputFunc* inp, OutputFunc* outp, InputBatch& b) {

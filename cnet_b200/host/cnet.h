@@ -31,7 +31,8 @@ namespace cnet_b200 {
 
 // type ids: the reference's own (impl/cnet.h:31-44)
 const int isHadamard = 1, isEmbedding = 2, isLinear = 3, isFourier = 4, isCrossEntropy = 5,
-          isResidual = 6, isSoftMax = 7, isInput = 8, isCrelu = 9, isGelu = 10;
+          isResidual = 6, isSoftMax = 7, isInput = 8, isCrelu = 9, isGelu = 10, isL2Out = 11,
+          isTrianFourier = 12;
 const int NO_TOKEN = -1;   // impl/batch.h:11
 
 // strong ints of the kept constructor signatures (impl/sizes.h:8-56)
@@ -291,24 +292,63 @@ public:
 	void backward() override;
 };
 
-class CrossEntropy : public CFunc, public OutputFunc {   // impl/crossent.h:9-185
+// A loss layer: device buffers for the labels and the per-sample losses of the batch.  forward()
+// computes the loss AND seeds dL/dz* of its input in the same pass.
+class LossFunc : public CFunc, public OutputFunc {
 	friend class CNet;
+protected:
 	float* loss_ = nullptr;                         // device [batch]
 	int32_t* labels_ = nullptr;                     // device [batch]
 	size_t extraBytes(int batch) const override { return 2 * (((size_t) batch * 4 + 255) & ~size_t(255)); }
 	void bindExtra(char* mem, int batch) override;
 public:
-	CrossEntropy(Uid uid, InSize n) : CFunc(uid, n, OutSize(1)) { is_output_ = true; }
-	explicit CrossEntropy(InSize n) : CFunc(n, OutSize(1)) { is_output_ = true; }
-	CFunc* clone(Uid uid) override { return new CrossEntropy(uid, InSize(in_size_)); }
-	std::string getName() override { return "CrossEntropy_" + std::to_string(uid_); }
-	int outputLength() override { return in_size_; }
+	LossFunc(Uid uid, InSize n) : CFunc(uid, n, OutSize(1)) { is_output_ = true; }
+	explicit LossFunc(InSize n) : CFunc(n, OutSize(1)) { is_output_ = true; }
 	float loss(int sample) override;
 	float* deviceLosses() const { return loss_; }
 	int32_t* deviceLabels() const { return labels_; }
-	void forward() override;            // loss AND the backward seed in one pass over the logits
 	void backward() override {}
 	void backward(int label) override;  // batch of one sample: reseeds with `label`
+};
+
+class CrossEntropy : public LossFunc {              // impl/crossent.h:9-185
+public:
+	CrossEntropy(Uid uid, InSize n) : LossFunc(uid, n) {}
+	explicit CrossEntropy(InSize n) : LossFunc(n) {}
+	CFunc* clone(Uid uid) override { return new CrossEntropy(uid, InSize(in_size_)); }
+	std::string getName() override { return "CrossEntropy_" + std::to_string(uid_); }
+	int outputLength() override { return in_size_; }
+	void forward() override;
+};
+
+class L2Out : public LossFunc {                     // impl/l2out.h:10-79: loss = sum |z|^2, dz* = z
+public:
+	L2Out(Uid uid, InSize n) : LossFunc(uid, n) {}
+	explicit L2Out(InSize n) : LossFunc(n) {}
+	CFunc* clone(Uid uid) override { return new L2Out(uid, InSize(in_size_)); }
+	std::string getName() override { return "L2Out_" + std::to_string(uid_); }
+	int outputLength() override { return 1; }
+	void forward() override;
+};
+
+class CRelu : public CFunc {                        // impl/relu.h:12-96
+public:
+	CRelu(Uid uid, InSize n) : CFunc(uid, n, OutSize(n.value())) {}
+	explicit CRelu(InSize n) : CFunc(n, OutSize(n.value())) {}
+	CFunc* clone(Uid uid) override { return new CRelu(uid, InSize(in_size_)); }
+	std::string getName() override { return "CRelu_" + std::to_string(uid_); }
+	void forward() override;
+	void backward() override;
+};
+
+class TriangFourier : public CFunc {                // impl/ft.h:115-222: lower-triangular DFT
+public:
+	TriangFourier(Uid uid, InSize n) : CFunc(uid, n, OutSize(n.value())) {}
+	explicit TriangFourier(InSize n) : CFunc(n, OutSize(n.value())) {}
+	CFunc* clone(Uid uid) override { return new TriangFourier(uid, InSize(in_size_)); }
+	std::string getName() override { return "TriangFourier_" + std::to_string(uid_); }
+	void forward() override;
+	void backward() override;
 };
 
 // Called after every gradient bucket (a contiguous range of the weight-gradient arena, in
@@ -318,6 +358,8 @@ typedef int (*BucketHook)(void* user, float* grads, size_t count, int bucket, in
 class CNet {
 	friend class CFunc;
 	friend class Linear;
+	friend class CrossEntropy;
+	friend class L2Out;
 	std::vector<CFunc*> func_list_;                 // owned, insertion order
 	std::map<int, CFunc*> map_;
 	std::vector<CFunc*> inputs_, outputs_;
@@ -334,10 +376,12 @@ class CNet {
 	bool ok_ = true;
 	std::string error_;
 	CFunc* main_in_ = nullptr;
-	CrossEntropy* main_out_ = nullptr;
+	LossFunc* main_out_ = nullptr;
 	float* wgrad_base_ = nullptr;                   // contiguous dz* planes of every weight, backward order
 	size_t wgrad_count_ = 0;
 	float* weight_base_ = nullptr;                  // contiguous value planes, same order
+	float* momentum_base_ = nullptr;                // Adam momentum, same layout (allocated on first adamUpdate)
+	bool infer_only_ = false;
 	struct Bucket { size_t begin, count; CFunc* last_writer; };
 	std::vector<Bucket> buckets_;
 	BucketHook hook_ = nullptr;
@@ -345,6 +389,10 @@ class CNet {
 	int dp_gemm_ctas_ = 0;                          // GEMM grid cap while all-reduces are in flight
 	unsigned long long weights_version_ = 0;        // bumped whenever weight values change
 	float* g_split_ = nullptr;                      // shared split planes of a Linear's output gradient
+	void* side_stream_ = nullptr;                   // second compute stream: dW* runs beside dX* at small batches
+	void* ev_side_fork_ = nullptr;
+	void* ev_side_join_ = nullptr;
+	int sm_count_ = 0;
 	NcclGroup nccl_;                                // native data parallelism (setDataParallel)
 	void* graph_exec_ = nullptr;                    // cudaGraphExec_t of a captured step
 	bool capturing_ = false;
@@ -430,6 +478,10 @@ public:
 	bool gpuForward(InputFunc* inp, OutputFunc* outp, EmbeddingBatch& batch);
 	bool gpuBackward();
 	void gpuUpdateInputs(float l_rate) { updateInputs(l_rate); }
+	// The reference's momentum-only Adam (CNet::adamUpdate, gpu/gpu_func.h:503-510): t counts updates
+	// from 0; the caller passes l_rate / batch.  The momentum planes are allocated on first use.
+	void adamUpdate(float l_rate, float beta, int t);
+	void infer();                                   // forward without seeding gradients (impl/cnet.h:379-389)
 	float getLoss(OutputFunc* outp, Batch* batch);  // mean loss, per-sample losses into the batch
 	bool getLosses(float* out, int n);
 	bool sync();

@@ -125,6 +125,9 @@ bool CNet::restoreFromString(const std::string& data) {
 		case isResidual:     f = new Residual(Uid(uid), InSize(out_len)); break;
 		case isSoftMax:      f = new SoftMax(Uid(uid), InSize(in_len)); break;
 		case isCrossEntropy: f = new CrossEntropy(Uid(uid), InSize(in_len)); break;
+		case isL2Out:        f = new L2Out(Uid(uid), InSize(in_len)); break;
+		case isCrelu:        f = new CRelu(Uid(uid), InSize(out_len)); break;
+		case isTrianFourier: f = new TriangFourier(Uid(uid), InSize(in_len)); break;
 		case isGelu:         f = new CGelu(Uid(uid), InSize(out_len)); break;
 		default:
 			fail(CNB_ERR_UNSUPPORTED, "restore: layer type " + std::to_string(type) + " is outside this library's path");

@@ -49,6 +49,12 @@ SIGNATURES = {
     "cnb_reserve_scratch": (C.c_int, [_vp, _sz]),
     "cnb_dft_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 2 + [_vp]),
     "cnb_dft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
+    "cnb_tdft_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 2 + [_vp]),
+    "cnb_tdft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
+    "cnb_crelu_fwd": (C.c_int, [_vp] + [_P] * 4 + [_sz, _vp]),
+    "cnb_crelu_bwd": (C.c_int, [_vp] + [_P] * 6 + [_sz, C.c_int, _vp]),
+    "cnb_l2out_fwd_bwd": (C.c_int, [_vp] + [_P] * 5 + [C.c_int] * 2 + [_vp]),
+    "cnb_adam_update": (C.c_int, [_vp, _P, _P, _P, _sz, C.c_float, C.c_float, C.c_int, _vp]),
     "cnb_set_dft_engine": (C.c_int, [_vp, C.c_int]),
     "cnb_hadamard_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] + [_P] * 2 + [C.c_int] * 2 + [_vp]),
     "cnb_hadamard_bwd": (C.c_int, [_vp] + [_P] * 6 + [C.c_int] + [_P] * 2 + [C.c_int] + [_P] * 2 + [C.c_int] * 3 + [_vp]),
@@ -93,6 +99,8 @@ SIGNATURES = {
     "cnh_backward": (C.c_int, [_vp]),
     "cnh_backward_label": (C.c_int, [_vp, C.c_int]),
     "cnh_update": (C.c_int, [_vp, C.c_float]),
+    "cnh_adam_update": (C.c_int, [_vp, C.c_float, C.c_float, C.c_int]),
+    "cnh_infer": (C.c_int, [_vp]),
     "cnh_get_losses": (C.c_int, [_vp, _P, C.c_int]),
     "cnh_sync": (C.c_int, [_vp]),
     "cnh_read_output": (C.c_int, [_vp, C.c_int, C.c_int, _P, _P]),

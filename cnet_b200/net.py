@@ -187,6 +187,13 @@ class Net:
         """gpuUpdateInputs(l_rate): w -= l_rate * dz*_w, gradients zeroed."""
         self._check(self.lib.cnh_update(self.h, lr), "updateInputs")
 
+    def adam_update(self, lr, beta, t):
+        """CNet::adamUpdate: momentum-only Adam of the reference; pass lr / batch."""
+        self._check(self.lib.cnh_adam_update(self.h, lr, beta, t), "adamUpdate")
+
+    def infer(self):
+        self._check(self.lib.cnh_infer(self.h), "infer")
+
     def losses(self, n=None):
         n = n or self.cur_batch
         out = np.empty(n, np.float32)
@@ -271,4 +278,9 @@ class Net:
     def update(self, lr, batch_size):
         """ComplexNet::update(lr, batch): w -= (lr / batch) * dz*_w."""
         self.update_inputs(lr / batch_size)
+        self.sync()
+
+    def adam(self, lr, batch_size, beta, t):
+        """ComplexNet::adamUpdate(lr, batch, beta, t)."""
+        self.adam_update(lr / batch_size, beta, t)
         self.sync()

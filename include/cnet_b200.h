@@ -135,6 +135,14 @@ int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
  * CPU: impl/ft.h:57-80. */
 int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                 float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
+/* TriangFourier: Y[b,p] = N^-1/2 sum_{q <= p} X[b,q] e^{-2 pi i pq/N} and its backward
+ * dX*[b,q] (+)= N^-1/2 sum_{p >= q} G*[b,p] e^{+2 pi i pq/N}: the complex GEMM against the
+ * lower-triangular twiddle matrix.  Replaces TrianFourierGpu::gpu_T_fft_forward / _backward
+ * (gpu/reduce.h:101-107, gpu/reduce.cpp:37-46, gpu/reducegrad.cpp:49-56).  CPU: impl/ft.h:139-188. */
+int cnb_tdft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
+                 float* y_re, float* y_im, int B, int N, void* stream);
+int cnb_tdft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                 float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
 /* N = 256, 1024, 4096 run as a shared-memory FFT (one read + one write of the tensor); any other
  * N, or every N after cnb_set_dft_engine(ctx, 1), as a complex GEMM against the twiddle matrix.
  * cnb_last_gemm_engine() reports 3 after an FFT-kernel call. */
@@ -181,6 +189,14 @@ int cnb_gelu_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im,
 int cnb_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                  const float* z_re, const float* z_im,
                  float* dz_re, float* dz_im, size_t n, int accumulate, void* stream);
+/* CRelu: y = z where re > 0 and im > 0, else 0; backward dz* (+)= g* through the same gate.
+ * Replaces ReluGpu::gpu_relu_forward / _backward (gpu/kernels.h:284-289, gpu/kernels.cpp:18-87).
+ * CPU: impl/relu.h:31-62. */
+int cnb_crelu_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im,
+                  float* y_re, float* y_im, size_t n, void* stream);
+int cnb_crelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
+                  const float* z_re, const float* z_im,
+                  float* dz_re, float* dz_im, size_t n, int accumulate, void* stream);
 /* Fused Hadamard(shared h) -> CGelu: a = u o h (kept for the backward), y = gelu(a).
  * Same reference kernels as the two above, one pass over HBM. */
 int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im,
@@ -231,6 +247,12 @@ int cnb_crossent_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im,
                          const int32_t* labels, float* loss,
                          float* dz_re, float* dz_im, int B, int M, void* stream);
 
+/* L2Out: loss[b] = sum_k |z_k|^2 and the backward seed dz* = z (dz_* may be NULL).  Replaces
+ * L2Gpu::gpu_norm_forward / gpu_norm_backward (gpu/reduce.h:175-181, gpu/reduce.cpp:232-251,
+ * 424-467).  CPU: impl/l2out.h:31-57 through CFunc::out_backward (impl/cfunc.h:327-339). */
+int cnb_l2out_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float* loss,
+                      float* dz_re, float* dz_im, int B, int N, void* stream);
+
 /* ------------------------------------------------------------------ embedding
  * out[b, t*D + d] = table[tok[b,t], d]; tok < 0 (NO_TOKEN, impl/batch.h:11) gives zeros.
  * Replaces EmbeddingGpu::gpu_embedding_forward (gpu/kernels.h:183, gpu/kernels.cpp:362-403).
@@ -251,6 +273,12 @@ int cnb_embed_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
  * CPU: impl/cfunc.h:147-152 + impl/cnet.h:413-421. */
 int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
                    void* stream);
+
+/* The reference's momentum-only "Adam": m = beta m + (1 - beta) g; w -= lr m / (1 - beta^(t+1));
+ * g = 0.  Replaces gpu_update_adam_input (gpu/kernels.h:77, gpu/kernels.cpp:494-525).
+ * CPU: impl/cfunc.h:273-287 + impl/cnet.h:423-431. */
+int cnb_adam_update(cnb_ctx* ctx, float* w, float* m, float* g, size_t n, float lr, float beta, int t,
+                    void* stream);
 
 /* Number of kernels this library has launched in this process (diagnostics / benches). */
 unsigned long long cnb_launch_count(void);

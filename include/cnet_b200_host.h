@@ -28,7 +28,7 @@ void cnh_clear_error(cnh_net* net);
 /* CNet::add(CFunc*, {uids}) (gpu/gpu_func.h:1013-1019).  type = the reference's type id
  * (impl/cnet.h:31-44); (a,b,c): CInput(a) | CEmbedding(dim a, tokens b, vocab c) |
  * FourierTrans(a) | Hadamard(a,a) | CGelu(a) | Linear(in1 a, in2 b) | Residual(a) |
- * SoftMax(a) | CrossEntropy(a). */
+ * SoftMax(a) | CrossEntropy(a) | CRelu(a) | L2Out(a) | TriangFourier(a). */
 int cnh_add(cnh_net* net, int type, int a, int b, int c, const int* prev, int nprev);
 int cnh_out_size(cnh_net* net, int uid);
 int cnh_init_inputs(cnh_net* net, uint64_t seed);                            /* CNet::init_inputs(seed) */
@@ -55,6 +55,8 @@ int cnh_forward(cnh_net* net);                                               /* 
 int cnh_backward(cnh_net* net);                                              /* gpuBackward, :1096-1101 */
 int cnh_backward_label(cnh_net* net, int label);                             /* CNet::backward(label) */
 int cnh_update(cnh_net* net, float lr);                                      /* gpuUpdateInputs, :491-495 */
+int cnh_adam_update(cnh_net* net, float lr, float beta, int t);              /* CNet::adamUpdate, gpu/gpu_func.h:503-510 */
+int cnh_infer(cnh_net* net);                                                 /* ComplexNet::infer, impl/cnet.h:379-389 */
 int cnh_get_losses(cnh_net* net, float* out, int n);                         /* getLoss, :906-926 */
 int cnh_sync(cnh_net* net);
 int cnh_read_output(cnh_net* net, int uid, int what, float* re, float* im); /* testDataFromGpu, :840-862 */

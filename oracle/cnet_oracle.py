@@ -18,7 +18,7 @@ conjugate of what is stored.
 import numpy as np
 
 # layer type ids: the reference's own (impl/cnet.h:31-44)
-HADAMARD, EMBEDDING, LINEAR, FOURIER, CROSSENT, RESIDUAL, SOFTMAX, INPUT, CRELU, GELU = range(1, 11)
+HADAMARD, EMBEDDING, LINEAR, FOURIER, CROSSENT, RESIDUAL, SOFTMAX, INPUT, CRELU, GELU, L2OUT, TRIFOURIER = range(1, 13)
 
 GELU_K = np.float32(np.sqrt(np.float32(2.0) / np.float32(np.pi)))  # sqrtf(2/pi), impl/relu.h:10
 
@@ -49,13 +49,14 @@ class _Fn:
             self.in_len, self.out = a + b, b // a
         elif type_ in (HADAMARD, RESIDUAL):
             self.in_len, self.out = 2 * a, a
-        elif type_ == CROSSENT:
+        elif type_ in (CROSSENT, L2OUT):
             self.in_len, self.out = a, 1
         else:
             self.in_len, self.out = a, a
         self.is_input = type_ in (INPUT, EMBEDDING)
         self.value = None                  # complex [len] for inputs
         self.wgrad = None                  # accumulated dL/dz* for inputs
+        self.momentum = None               # Adam momentum (the reference keeps it in the dz planes)
 
 
 class OracleNet:
@@ -165,7 +166,13 @@ class OracleNet:
                 n = np.maximum(np.sqrt((np.abs(z) ** 2).sum(1, keepdims=True)), 1e-15)
                 f._n = n
                 self.act[uid] = z / n
-            elif t == CROSSENT:
+            elif t == CRELU:
+                z = parts[0]                                           # impl/relu.h:31-45
+                self.act[uid] = np.where((z.real > 0) & (z.imag > 0), z, 0)
+            elif t == TRIFOURIER:
+                # impl/ft.h:139-161: y_p = N^-1/2 sum_{q <= p} x_q e^{-2 pi i pq/N}
+                self.act[uid] = parts[0] @ self._tri(f.a).T
+            elif t in (CROSSENT, L2OUT):
                 ce_uid = uid
                 f._z = parts[0]
             else:
@@ -173,6 +180,10 @@ class OracleNet:
         # ---------------------------------------------------------------- loss
         f = self.fn[ce_uid]
         z = f._z
+        if f.type == L2OUT:
+            # impl/l2out.h:31-57: loss = sum |z|^2; generic out_backward (impl/cfunc.h:327-339) seeds dz* = z
+            losses = (np.abs(z) ** 2).sum(1)
+            return self._backward(main_uid, ce_uid, z.copy(), losses, B)
         # impl/crossent.h:57-78 + 50-55: S = max(sum |z|^2, 1e-15); p = |z_l / sqrt(S)|^2
         S = np.maximum((np.abs(z) ** 2).sum(1), 1e-15)
         zl = z[np.arange(B), labels]
@@ -184,6 +195,13 @@ class OracleNet:
         g = z / S[:, None]
         m = np.maximum(np.abs(zl) ** 2, 1e-15)
         g[np.arange(B), labels] = -zl * (S - m) / (m * S)
+        return self._backward(main_uid, ce_uid, g, losses, B)
+
+    def _tri(self, n):
+        p, q = np.meshgrid(np.arange(n), np.arange(n), indexing="ij")
+        return np.where(q <= p, np.exp(-2j * np.pi * ((p * q) % n) / n), 0) / np.sqrt(n)
+
+    def _backward(self, main_uid, ce_uid, g, losses, B):
         gin = {ce_uid: [g]}                 # per function: dL/dz* of its input block parts
         for uid in reversed(self.order):
             f = self.fn[uid]
@@ -210,7 +228,7 @@ class OracleNet:
                 valid = tok >= 0
                 np.add.at(acc, tok[valid], gg[valid])
                 continue
-            if t == CROSSENT:
+            if t in (CROSSENT, L2OUT):
                 continue
             parts = self._input_block(f, B)
             if t == FOURIER:
@@ -226,6 +244,12 @@ class OracleNet:
                 z = parts[0]
                 dx, dy = 0.5 * _dgelu(z.real), 0.5 * _dgelu(z.imag)
                 gin[uid] = [np.conj(go) * (dx - dy) + go * (dx + dy)]
+            elif t == CRELU:
+                z = parts[0]                                          # impl/relu.h:47-62
+                gin[uid] = [np.where((z.real > 0) & (z.imag > 0), go, 0)]
+            elif t == TRIFOURIER:
+                # impl/ft.h:163-188: dz*_q = N^-1/2 sum_{p >= q} g*_p conj(w^{pq})
+                gin[uid] = [go @ np.conj(self._tri(f.a))]
             elif t == LINEAR:
                 # impl/linear.h:73-110: dX*[b,i] = sum_o g*[b,o] conj(W[o,i]);
                 # dW*[o,i] = g*[b,o] conj(x[b,i]) (per sample; the weight CInput sums over b)
@@ -240,6 +264,17 @@ class OracleNet:
                 gin[uid] = [go / n - z * s / n ** 3]
         self.losses = losses
         return losses.astype(np.float64)
+
+    # impl/cnet.h:423-431 + impl/cfunc.h:273-287: m = beta m + (1-beta) dz*; w -= (lr/batch) m / (1 - beta^(t+1));
+    # dz* zeroed (the momentum lives in the dz planes, which update() would zero but adamUpdate does not)
+    def adam(self, lr, batch_size, beta, t):
+        for f in self.fn.values():
+            if f.is_input:
+                if f.momentum is None:
+                    f.momentum = np.zeros_like(f.wgrad)
+                f.momentum = beta * f.momentum + (1 - beta) * f.wgrad
+                f.value = f.value - (lr / batch_size) * f.momentum / (1 - beta ** (t + 1))
+                f.wgrad[:] = 0
 
     def get_record(self, uid, what):
         a = self.act[uid] if what == 0 else self.gstar[uid]

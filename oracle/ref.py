@@ -36,6 +36,7 @@ def lib():
         _lib.ref_out_size.argtypes = [C.c_void_p, C.c_int]
         _lib.ref_update.argtypes = [C.c_void_p, C.c_float, C.c_int]
         _lib.ref_set_threads.argtypes = [C.c_int]
+        _lib.ref_adam_update.argtypes = [C.c_void_p, C.c_float, C.c_int, C.c_float, C.c_int]
         _lib.ref_save.argtypes = [C.c_void_p, C.c_char_p]
         _lib.ref_restore.argtypes = [C.c_char_p]
         _lib.ref_restore.restype = C.c_void_p
@@ -153,3 +154,6 @@ class RefNet:
 
     def update(self, lr, batch_size):
         lib().ref_update(self.h, float(lr), int(batch_size))
+
+    def adam(self, lr, batch_size, beta, t):
+        lib().ref_adam_update(self.h, float(lr), int(batch_size), float(beta), int(t))

@@ -68,6 +68,9 @@ int ref_add(void* h, int type, int a, int b, int c, const int* prev, int nprev) 
 	case isResidual:     f = new Residual(InSize(a)); break;
 	case isSoftMax:      f = new SoftMax(InSize(a)); break;
 	case isCrossEntropy: f = new CrossEntropy(InSize(a)); break;
+	case isL2Out:        f = new L2Out(InSize(a)); break;
+	case isCrelu:        f = new CRelu(InSize(a)); break;
+	case isTrianFourier: f = new TriangFourier(InSize(a)); break;
 	default: return -1;
 	}
 	std::vector<int> p(prev, prev + nprev);
@@ -120,9 +123,9 @@ int ref_run_batch(void* h, int main_uid, const float* xre, const float* xim,
 	CFunc* in = fn(r, main_uid);
 	if (!in) return -1;
 	CEmbedding* emb = dynamic_cast<CEmbedding*>(in);
-	CrossEntropy* ce = NULL;
+	OutputFunc* ce = NULL;                 // the loss layer: CrossEntropy or L2Out
 	for (int uid : r->uids) {
-		if (CrossEntropy* c = dynamic_cast<CrossEntropy*>(fn(r, uid))) ce = c;
+		if (OutputFunc* c = dynamic_cast<OutputFunc*>(fn(r, uid))) ce = c;
 	}
 	if (!ce) return -2;
 	r->batch = B;
@@ -216,6 +219,11 @@ int ref_num_funcs(void* h) { return (int) static_cast<RefNet*>(h)->uids.size(); 
 int ref_uid_at(void* h, int i) { return static_cast<RefNet*>(h)->uids[i]; }
 int ref_type_of(void* h, int uid) { return ComplexNet::getType(fn(static_cast<RefNet*>(h), uid)); }
 int ref_in_len(void* h, int uid) { return fn(static_cast<RefNet*>(h), uid)->input().length_; }
+
+int ref_adam_update(void* h, float lr, int batch_size, float beta, int t) {
+	static_cast<RefNet*>(h)->net.adamUpdate(lr, batch_size, beta, t);
+	return 0;
+}
 
 int ref_update(void* h, float lr, int batch_size) {
 	static_cast<RefNet*>(h)->net.update(lr, batch_size);

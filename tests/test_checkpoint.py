@@ -17,7 +17,8 @@ FIXTURE = os.path.join(util.GOLDEN_DIR, "embed_lm_small.cnet")     # written by 
 def _small_nets():
     return [(configs.build_classifier, dict(n=16, m=4)),
             (configs.build_mixer, dict(n=8, blocks=2, m=3)),
-            (configs.build_embed_lm, dict(tokens=4, vocab=32, dim=8, hidden=16))]
+            (configs.build_embed_lm, dict(tokens=4, vocab=32, dim=8, hidden=16)),
+            (configs.build_relu_tri, dict(n=12, m=3))]
 
 
 def test_restore_reference_written_fixture(built_lib, tmp_path):
@@ -38,7 +39,7 @@ def test_restore_reference_written_fixture(built_lib, tmp_path):
 
 
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
-@pytest.mark.parametrize("k", range(3))
+@pytest.mark.parametrize("k", range(4))
 def test_round_trip_with_live_reference(built_lib, tmp_path, k):
     builder, kw = _small_nets()[k]
     ours, theirs = Net(), ref.RefNet()

@@ -17,7 +17,11 @@ CASES = {
     "linear_48x40": (configs.build_linear, dict(n_in=48, n_out=40), 7, "fanin", 1),
     # large enough for the tensor-core GEMM with cached operand splits (all dims >= 64), two updates
     "mixer_64x1_b64": (configs.build_mixer, dict(n=64, blocks=1, m=10), 64, "normal", 2),
+    # the layers outside the benchmark configs (TriangFourier, CRelu, L2Out), trained with the reference's Adam
+    "relu_tri_adam": (configs.build_relu_tri, dict(n=24, m=6), 5, "normal", 3),
 }
+ADAM_CASES = {"relu_tri_adam"}
+ADAM_BETA = 0.9
 LR = 0.01
 
 
@@ -88,7 +92,10 @@ def run_case(net, name, post_alloc=None):
                         continue
                     out["act_%s_re" % lname], out["act_%s_im" % lname] = a
                     out["gstar_%s_re" % lname], out["gstar_%s_im" % lname] = g
-        net.update(LR, B)
+        if name in ADAM_CASES:
+            net.adam(LR, B, ADAM_BETA, s)
+        else:
+            net.update(LR, B)
     for lname, uid in spec.layers.items():
         if uid in weight_uids:
             v = net.get_values(uid)
