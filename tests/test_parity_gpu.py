@@ -185,3 +185,21 @@ def test_restored_checkpoint_trains_on_the_device(tmp_path):
     again = Net.restore(out)
     for name in ("emb", "w1", "w2"):
         assert util.relerr(again.get_values(spec.layers[name]), ora.get_values(spec.layers[name])) < 1e-4
+
+
+def test_infer_gives_the_losses_without_touching_gradients():
+    net = Net()
+    spec = configs.build_classifier(net, n=64, m=10)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    net.allocate(8)
+    x, labels = configs.make_batch(spec, 8, 0)
+    want = net.run_batch(spec.main, x=x, labels=labels)
+    g1 = net.get_wgrad(spec.layers["w"])
+    gs1 = net.get_record(spec.layers["lin"], 1)
+    net.upload(x=(x[0] * 0 + 1, x[1]), labels=labels)      # a different batch ...
+    net.infer()                                            # ... forward only
+    net.sync()
+    assert not np.allclose(net.losses(), want)
+    assert np.array_equal(net.get_record(spec.layers["lin"], 1)[0], gs1[0])   # seed of the last backward untouched
+    assert np.array_equal(net.get_wgrad(spec.layers["w"])[0], g1[0])
