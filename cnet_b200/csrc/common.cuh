@@ -81,12 +81,29 @@ int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr
 bool fft_supported(int N);
 int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, int B, int N, int inverse,
             int accumulate, cudaStream_t st);
+// Forward FFT whose epilogue also applies Hadamard(h) -> CGelu: u = FFT(x) -> (ur, ui); y = gelu(u o h) ->
+// (yr, yi) and, when sp != NULL, the hi/lo split planes of y.
+int fft_hadamard_gelu(cnb_ctx* ctx, const float* xr, const float* xi, const float* hr, const float* hi, float* ur,
+                      float* ui, float* yr, float* yi, float* sp, int B, int N, cudaStream_t st);
 
 // [R, C] -> [C, R] transpose of a re/im plane pair (operand staging for the K-major GEMM).
 int transpose_planes(const float* s_re, const float* s_im, float* d_re, float* d_im,
                      int R, int C, cudaStream_t st);
 
 }  // namespace cnb
+
+// CGelu of the reference (impl/relu.h:119-131): tanh form; the derivative uses sech^2 = 1 - tanh^2.
+__device__ __forceinline__ float cnb_gelu(float x) {
+    float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x));
+    return 0.5f * x * (1.0f + t);
+}
+
+__device__ __forceinline__ float cnb_dgelu(float x) {
+    float x2 = x * x;
+    float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x2));
+    float sech2 = 1.0f - t * t;
+    return 0.5f * (1.0f + t) + 0.5f * x * sech2 * 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2);
+}
 
 #define CNB_CHECK_ARG(cond, ...) \
     do { if (!(cond)) return cnb::set_error(CNB_ERR_ARG, __VA_ARGS__); } while (0)

@@ -10,8 +10,6 @@
 
 namespace {
 
-constexpr float kGeluK = 0.7978845608028654f;   // sqrtf(2/pi)
-constexpr float kGeluC = 0.044715f;
 
 template <int W> struct Pack { float v[W]; };
 
@@ -34,18 +32,8 @@ template <int W> __device__ __forceinline__ void st(float* p, size_t i, const Pa
     }
 }
 
-__device__ __forceinline__ float gelu_f(float x) {
-    float t = tanhf(kGeluK * (x + kGeluC * x * x * x));
-    return 0.5f * x * (1.0f + t);
-}
-
-// gelu'(x) with sech^2 = 1 - tanh^2
-__device__ __forceinline__ float dgelu_f(float x) {
-    float x2 = x * x;
-    float t = tanhf(kGeluK * (x + kGeluC * x * x2));
-    float sech2 = 1.0f - t * t;
-    return 0.5f * (1.0f + t) + 0.5f * x * sech2 * kGeluK * (1.0f + 3.0f * kGeluC * x2);
-}
+__device__ __forceinline__ float gelu_f(float x) { return cnb_gelu(x); }
+__device__ __forceinline__ float dgelu_f(float x) { return cnb_dgelu(x); }
 
 inline int grid_for(size_t work_items, int threads, int sm_count) {
     size_t blocks = (work_items + threads - 1) / threads;
@@ -125,7 +113,15 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
             size_t i = (size_t) b * N + col;
             Pack<W> tr = ld<W>(gr, i), ti = ld<W>(gi, i), xr = ld<W>(ur, i), xi = ld<W>(ui, i);
             if (MODE == 1) {
-                Pack<W> zr = ld<W>(ar, i), zi = ld<W>(ai, i), vr, vi;
+                Pack<W> zr, zi, vr, vi;
+                if (ar) { zr = ld<W>(ar, i); zi = ld<W>(ai, i); }
+                else {                                   // the Hadamard output was not kept: a = u o h again
+#pragma unroll
+                    for (int k = 0; k < W; ++k) {
+                        zr.v[k] = xr.v[k] * hre.v[k] - xi.v[k] * him.v[k];
+                        zi.v[k] = xr.v[k] * him.v[k] + xi.v[k] * hre.v[k];
+                    }
+                }
                 if (dur && accumulate_u) { vr = ld<W>(dur, i); vi = ld<W>(dui, i); }
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
@@ -349,7 +345,7 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
                      float* dur, float* dui, int acc_u, float* dvr, float* dvi, int acc_v,
                      int B, int N, cudaStream_t stm) {
     bool vec = (N % 4 == 0) && aligned16(gr) && aligned16(gi) && aligned16(ur) && aligned16(ui) &&
-               (mode == 0 || (aligned16(ar) && aligned16(ai) && aligned16(hr) && aligned16(hi))) &&
+               (mode == 0 || (aligned16(ar) && aligned16(ai) && aligned16(hr) && aligned16(hi))) &&   // NULL is aligned
                (!dur || (aligned16(dur) && aligned16(dui)));
     int w = vec ? 4 : 1;
     int col_blocks = (N + 32 * w - 1) / (32 * w);
@@ -480,8 +476,9 @@ int cnb_hadamard_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, co
                           const float* a_im, const float* u_re, const float* u_im, const float* h_re,
                           const float* h_im, float* du_re, float* du_im, int accumulate_u, float* dh_re,
                           float* dh_im, int accumulate_h, int B, int N, void* stream) {
-    CNB_CHECK_ARG(ctx && g_re && g_im && a_re && a_im && u_re && u_im && h_re && h_im && dh_re && dh_im,
+    CNB_CHECK_ARG(ctx && g_re && g_im && u_re && u_im && h_re && h_im && dh_re && dh_im,
                   "cnb_hadamard_gelu_bwd: null pointer");
+    CNB_CHECK_ARG((a_re == nullptr) == (a_im == nullptr), "cnb_hadamard_gelu_bwd: a planes must be a pair");
     CNB_CHECK_ARG((du_re == nullptr) == (du_im == nullptr), "cnb_hadamard_gelu_bwd: du planes must be a pair");
     CNB_CHECK_ARG(B > 0 && N > 0, "cnb_hadamard_gelu_bwd: B=%d N=%d", B, N);
     return colreduce_launch(ctx, 1, g_re, g_im, a_re, a_im, u_re, u_im, h_re, h_im, du_re, du_im, accumulate_u,

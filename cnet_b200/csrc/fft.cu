@@ -55,10 +55,20 @@ template <int R> __device__ __forceinline__ void row_sync() {
     if constexpr (R <= 32) __syncwarp(); else __syncthreads();
 }
 
+// Optional fused tail of the forward transform: Hadamard with a shared vector h, then CGelu.
+struct FftEpilogue {
+    const float* hr = nullptr;      // h planes [N]; NULL = plain transform
+    const float* hi = nullptr;
+    float* gr = nullptr;            // gelu(u o h) planes [B, N]
+    float* gi = nullptr;
+    float* sp = nullptr;            // hi/lo split of that (4 planes of np floats) or NULL
+    size_t np = 0;
+};
+
 template <int R, int SIGN>
 __global__ void __launch_bounds__(256, (R <= 32 ? 2 : 1))
 fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __restrict__ yr, float* __restrict__ yi,
-         const float2* __restrict__ tw, int B, int accumulate) {
+         const float2* __restrict__ tw, int B, int accumulate, const FftEpilogue ep) {
     constexpr int N = R * R;
     constexpr int ROWS = 256 / R;                        // rows per block
     extern __shared__ float smem_f[];
@@ -72,15 +82,35 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
         const bool live = row < B;
         float re[R], im[R];
         if (live) {
-            const float* pr = xr + row * N + t;
-            const float* pi = xi + row * N + t;
+            // the row comes in with 16-byte loads (R/4 per thread and plane) and is parked in shared memory in
+            // natural order; each thread then picks its stride-R elements from there (conflict-free)
+            constexpr int V = R / 4;
+            const float* pr = xr + row * N;
+            const float* pi = xi + row * N;
+            float4 a[V], b[V];
 #pragma unroll
-            for (int n1 = 0; n1 < R; ++n1) { re[n1] = pr[n1 * R]; im[n1] = pi[n1 * R]; }
+            for (int v = 0; v < V; ++v) {
+                a[v] = *reinterpret_cast<const float4*>(pr + 4 * (t + v * R));
+                b[v] = *reinterpret_cast<const float4*>(pi + 4 * (t + v * R));
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                *reinterpret_cast<float4*>(sr + 4 * (t + v * R)) = a[v];
+                *reinterpret_cast<float4*>(si + 4 * (t + v * R)) = b[v];
+            }
+        }
+        row_sync<R>();
+        if (live) {
+#pragma unroll
+            for (int n1 = 0; n1 < R; ++n1) { re[n1] = sr[n1 * R + t]; im[n1] = si[n1 * R + t]; }
+        }
+        row_sync<R>();                                   // the parked row is consumed before it is overwritten
+        if (live) {
             fft_regs<R, SIGN>(re, im);
 #pragma unroll
             for (int p = 0; p < R; ++p) {
                 const int k1 = bitrev<R>(p);             // position p holds frequency k1
-                float2 w = tw[(t * k1) & (N - 1)];       // e^{-2 pi i t k1/N}
+                float2 w = tw[k1 * R + t];               // e^{-2 pi i t k1/N}: consecutive threads, consecutive entries
                 float c = w.x, s = SIGN < 0 ? w.y : -w.y;
                 float vr = re[p] * c - im[p] * s, vi = re[p] * s + im[p] * c;
                 sr[k1 * (R + 1) + t] = vr;
@@ -134,23 +164,48 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                 }
                 *reinterpret_cast<float4*>(qr + e) = vr;
                 *reinterpret_cast<float4*>(qi + e) = vi;
+                if (ep.hr) {
+                    const float4 h0 = *reinterpret_cast<const float4*>(ep.hr + e), h1 = *reinterpret_cast<const float4*>(ep.hi + e);
+                    const float ur[4] = {vr.x, vr.y, vr.z, vr.w}, ui[4] = {vi.x, vi.y, vi.z, vi.w};
+                    const float pr[4] = {h0.x, h0.y, h0.z, h0.w}, pi[4] = {h1.x, h1.y, h1.z, h1.w};
+                    float gr[4], gi[4], rh[4], rl[4], sh[4], sl[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        gr[k] = cnb_gelu(ur[k] * pr[k] - ui[k] * pi[k]);
+                        gi[k] = cnb_gelu(ur[k] * pi[k] + ui[k] * pr[k]);
+                        rh[k] = __uint_as_float(__float_as_uint(gr[k]) & 0xFFFFE000u); rl[k] = gr[k] - rh[k];
+                        sh[k] = __uint_as_float(__float_as_uint(gi[k]) & 0xFFFFE000u); sl[k] = gi[k] - sh[k];
+                    }
+                    const size_t o = (size_t) row * N + e;
+                    *reinterpret_cast<float4*>(ep.gr + o) = make_float4(gr[0], gr[1], gr[2], gr[3]);
+                    *reinterpret_cast<float4*>(ep.gi + o) = make_float4(gi[0], gi[1], gi[2], gi[3]);
+                    if (ep.sp) {
+                        *reinterpret_cast<float4*>(ep.sp + o) = make_float4(rh[0], rh[1], rh[2], rh[3]);
+                        *reinterpret_cast<float4*>(ep.sp + ep.np + o) = make_float4(sh[0], sh[1], sh[2], sh[3]);
+                        *reinterpret_cast<float4*>(ep.sp + 2 * ep.np + o) = make_float4(rl[0], rl[1], rl[2], rl[3]);
+                        *reinterpret_cast<float4*>(ep.sp + 3 * ep.np + o) = make_float4(sl[0], sl[1], sl[2], sl[3]);
+                    }
+                }
             }
         }
         row_sync<R>();
     }
 }
 
-__global__ void fft_twiddle_k(float2* __restrict__ tw, int N) {
+// tw[k1 * R + t] = e^{-2 pi i t k1 / N}: laid out so that the R threads of a row read one contiguous line
+// per frequency k1 (a table indexed by the product t*k1 costs one cache line per thread).
+__global__ void fft_twiddle_k(float2* __restrict__ tw, int R) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= N) return;
+    if (i >= R * R) return;
+    int k1 = i / R, t = i % R;
     double s, c;
-    sincospi(-2.0 * (double) i / (double) N, &s, &c);
+    sincospi(-2.0 * (double) (t * k1) / (double) (R * R), &s, &c);
     tw[i] = make_float2((float) c, (float) s);
 }
 
 template <int R>
 int launch(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, const float2* tw, int B, int inverse,
-           int accumulate, cudaStream_t st) {
+           int accumulate, const FftEpilogue& ep, cudaStream_t st) {
     constexpr int ROWS = 256 / R;
     size_t smem = (size_t) ROWS * 2 * R * (R + 1) * sizeof(float);
     static bool attr_done[2] = {false, false};
@@ -162,8 +217,8 @@ int launch(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi,
     int blocks = (B + ROWS - 1) / ROWS;
     int cap = ctx->sm_count * 8;
     if (blocks > cap) blocks = cap;
-    if (inverse) fft_rr_k<R, 1><<<blocks, 256, smem, st>>>(xr, xi, yr, yi, tw, B, accumulate);
-    else fft_rr_k<R, -1><<<blocks, 256, smem, st>>>(xr, xi, yr, yi, tw, B, accumulate);
+    if (inverse) fft_rr_k<R, 1><<<blocks, 256, smem, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep);
+    else fft_rr_k<R, -1><<<blocks, 256, smem, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep);
     CNB_LAUNCH_CHECK("fft_rr");
     return CNB_OK;
 }
@@ -174,9 +229,9 @@ namespace cnb {
 
 bool fft_supported(int N) { return N == 256 || N == 1024 || N == 4096; }
 
-int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, int B, int N, int inverse,
-            int accumulate, cudaStream_t st) {
-    // the N-point twiddle table lives in the arena; the map key -N keeps it apart from DFT matrices
+static int fft_dispatch(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, int B, int N, int inverse,
+                        int accumulate, const FftEpilogue& ep, cudaStream_t st) {
+    // the inter-pass twiddle table lives in the arena; the map key -N keeps it apart from DFT matrices
     cnb_twiddle t;
     auto it = ctx->twiddles.find(-N);
     if (it == ctx->twiddles.end()) {
@@ -184,17 +239,30 @@ int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi
         int rc = cnb_alloc(ctx, (size_t) N * sizeof(float2), &p);
         if (rc != CNB_OK) return rc;
         t.re = static_cast<float*>(p);
-        fft_twiddle_k<<<(N + 255) / 256, 256, 0, st>>>(reinterpret_cast<float2*>(p), N);
+        fft_twiddle_k<<<(N + 255) / 256, 256, 0, st>>>(reinterpret_cast<float2*>(p), N == 256 ? 16 : N == 1024 ? 32 : 64);
         CNB_LAUNCH_CHECK("fft_twiddle");
         ctx->twiddles[-N] = t;
     } else {
         t = it->second;
     }
     const float2* tw = reinterpret_cast<const float2*>(t.re);
-    if (N == 256) return launch<16>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, st);
-    if (N == 1024) return launch<32>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, st);
-    if (N == 4096) return launch<64>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, st);
+    if (N == 256) return launch<16>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
+    if (N == 1024) return launch<32>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
+    if (N == 4096) return launch<64>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
     return set_error(CNB_ERR_UNSUPPORTED, "fft: N=%d", N);
+}
+
+int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, int B, int N, int inverse,
+            int accumulate, cudaStream_t st) {
+    return fft_dispatch(ctx, xr, xi, yr, yi, B, N, inverse, accumulate, FftEpilogue(), st);
+}
+
+int fft_hadamard_gelu(cnb_ctx* ctx, const float* xr, const float* xi, const float* hr, const float* hi, float* ur,
+                      float* ui, float* yr, float* yi, float* sp, int B, int N, cudaStream_t st) {
+    FftEpilogue ep;
+    ep.hr = hr; ep.hi = hi; ep.gr = yr; ep.gi = yi; ep.sp = sp;
+    ep.np = ((size_t) B * N + 63) & ~size_t(63);
+    return fft_dispatch(ctx, xr, xi, ur, ui, B, N, 0, 0, ep, st);
 }
 
 }  // namespace cnb

@@ -223,6 +223,18 @@ int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_sp
                                   cnb::S(stream));
 }
 
+int cnb_dft_fused_ok(int N) { return cnb::fft_supported(N) ? 1 : 0; }
+
+int cnb_dft_hadamard_gelu_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, const float* h_re,
+                              const float* h_im, float* u_re, float* u_im, float* y_re, float* y_im, float* y_split,
+                              int B, int N, void* stream) {
+    CNB_CHECK_ARG(ctx && x_re && x_im && h_re && h_im && u_re && u_im && y_re && y_im,
+                  "cnb_dft_hadamard_gelu_fwd: null pointer");
+    CNB_CHECK_ARG(B > 0 && cnb::fft_supported(N), "cnb_dft_hadamard_gelu_fwd: B=%d, N=%d is not an FFT-kernel length", B, N);
+    cnb::g_last_engine = 3;
+    return cnb::fft_hadamard_gelu(ctx, x_re, x_im, h_re, h_im, u_re, u_im, y_re, y_im, y_split, B, N, cnb::S(stream));
+}
+
 int cnb_tdft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, float* y_re, float* y_im, int B, int N,
                  void* stream) {
     CNB_CHECK_ARG(ctx && x_re && x_im && y_re && y_im, "cnb_tdft_fwd: null pointer");

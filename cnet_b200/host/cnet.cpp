@@ -143,6 +143,13 @@ void CEmbedding::init_inputs(uint64_t seed) {
 // ------------------------------------------------------------- FourierTrans
 void FourierTrans::forward() {
 	const Vars& x = in(0);
+	if (fused_hg_) {
+		const Vars& h = fused_hg_->previous(1)->output();
+		Vars& y = fused_hg_->fused_gelu_->out_;
+		check(cnb_dft_hadamard_gelu_fwd(ctx(), x.real_, x.imag_, h.real_, h.imag_, out_.real_, out_.imag_, y.real_,
+				y.imag_, fused_hg_->consumerSplit(), batch(), in_size_, stream()));
+		return;
+	}
 	check(cnb_dft_fwd(ctx(), x.real_, x.imag_, out_.real_, out_.imag_, batch(), in_size_, stream()));
 }
 
@@ -154,21 +161,25 @@ void FourierTrans::backward() {
 }
 
 // ----------------------------------------------------------------- Hadamard
+float* Hadamard::consumerSplit() {
+	// a Linear that is the only consumer of the GELU output gets its operand split planes from the producer
+	if (!fused_gelu_ || fused_gelu_->no_outputs() != 1) return nullptr;
+	Linear* l = dynamic_cast<Linear*>(fused_gelu_->next(0));
+	if (l && l->use_split_ && l->previous(0) == fused_gelu_ &&
+			cnb_linear_split_ok(batch(), l->firstInputLength(), l->outSize())) {
+		l->x_presplit_ = true;
+		return l->x_split_;
+	}
+	return nullptr;
+}
+
 void Hadamard::forward() {
+	if (in_fft_epilogue_) return;
 	const Vars& u = in(0);
 	const Vars& v = in(1);
 	if (fused_gelu_) {
 		Vars& y = fused_gelu_->out_;
-		// a Linear that is the only consumer of the GELU output gets its operand split planes from here
-		float* ysplit = nullptr;
-		if (fused_gelu_->no_outputs() == 1) {
-			Linear* l = dynamic_cast<Linear*>(fused_gelu_->next(0));
-			if (l && l->use_split_ && l->previous(0) == fused_gelu_ &&
-					cnb_linear_split_ok(batch(), l->firstInputLength(), l->outSize())) {
-				ysplit = l->x_split_;
-				l->x_presplit_ = true;
-			}
-		}
+		float* ysplit = consumerSplit();
 		check(cnb_hadamard_gelu_fwd_split(ctx(), u.real_, u.imag_, v.real_, v.imag_, out_.real_, out_.imag_, y.real_,
 				y.imag_, ysplit, batch(), out_size_, stream()));
 		return;
@@ -523,6 +534,12 @@ bool CNet::planFusion() {
 				CGelu* g = dynamic_cast<CGelu*>(h->next_func_[0]);
 				if (g && g->prev_func_.size() == 1) { h->fused_gelu_ = g; g->fused_away_ = true; }
 			}
+			// ... and the whole pair moves into the epilogue of the FFT that feeds it
+			FourierTrans* ft = dynamic_cast<FourierTrans*>(h->prev_func_[0]);
+			if (h->fused_gelu_ && ft && ft->next_func_.size() == 1 && cnb_dft_fused_ok(ft->in_size_)) {
+				ft->fused_hg_ = h;
+				h->in_fft_epilogue_ = true;
+			}
 		}
 		if (Linear* l = dynamic_cast<Linear*>(f)) {
 			if (l->next_func_.size() == 1) {
@@ -705,6 +722,8 @@ bool CNet::allocateOnGpu(int B) {
 		bool alias = false;
 		if (Linear* l = dynamic_cast<Linear*>(f)) alias = l->fused_residual_ != nullptr;
 		if (alias) continue;                    // bound to the Residual's tensors below
+		if (Hadamard* hd = dynamic_cast<Hadamard*>(f))
+			if (hd->in_fft_epilogue_) continue;         // a = u o h is never stored (recomputed in the backward)
 		bool need_grad = !(dynamic_cast<Hadamard*>(f) && static_cast<Hadamard*>(f)->fused_gelu_);
 		size_t planes = need_grad ? 4 : 2;
 		if ((rc = cnb_alloc(ctx_, planes * n * sizeof(float), &p)) != CNB_OK) { fail(rc, f->getName()); return false; }

@@ -209,7 +209,10 @@ public:
 	void init_inputs(uint64_t seed) override;       // impl/embed.h:101-107 distribution
 };
 
+class Hadamard;
 class FourierTrans : public CFunc {                 // impl/ft.h:11-113
+	friend class CNet;
+	Hadamard* fused_hg_ = nullptr;                  // FFT epilogue does Hadamard(shared h) -> CGelu
 public:
 	FourierTrans(Uid uid, InSize n) : CFunc(uid, n, OutSize(n.value())) {}
 	explicit FourierTrans(InSize n) : CFunc(n, OutSize(n.value())) {}
@@ -222,7 +225,10 @@ public:
 class Hadamard : public CFunc {                     // impl/hadamard.h:11-107
 	friend class CNet;
 	friend class CGelu;
+	friend class FourierTrans;
 	CFunc* fused_gelu_ = nullptr;                   // Hadamard(shared h) -> CGelu run as one kernel pair
+	bool in_fft_epilogue_ = false;                  // the producing FourierTrans computes this layer's forward
+	float* consumerSplit();                         // split planes of the Linear fed by the fused GELU, or NULL
 public:
 	Hadamard(Uid uid, InSize a, InSize b) : CFunc(uid, InSize(a.value() + b.value()), OutSize(a.value())) {}
 	Hadamard(InSize a, InSize b) : CFunc(InSize(a.value() + b.value()), OutSize(a.value())) {}

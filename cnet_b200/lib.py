@@ -49,6 +49,8 @@ SIGNATURES = {
     "cnb_reserve_scratch": (C.c_int, [_vp, _sz]),
     "cnb_dft_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 2 + [_vp]),
     "cnb_dft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
+    "cnb_dft_fused_ok": (C.c_int, [C.c_int]),
+    "cnb_dft_hadamard_gelu_fwd": (C.c_int, [_vp] + [_P] * 9 + [C.c_int] * 2 + [_vp]),
     "cnb_tdft_fwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 2 + [_vp]),
     "cnb_tdft_bwd": (C.c_int, [_vp] + [_P] * 4 + [C.c_int] * 3 + [_vp]),
     "cnb_crelu_fwd": (C.c_int, [_vp] + [_P] * 4 + [_sz, _vp]),

@@ -135,6 +135,16 @@ int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
  * CPU: impl/ft.h:57-80. */
 int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                 float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
+/* FourierTrans -> Hadamard(shared h) -> CGelu in one pass over the row (N = 256, 1024, 4096, see
+ * cnb_dft_fused_ok): u = DFT(x) is kept for the backward, y = gelu(u o h), optionally with the
+ * hi/lo split planes of y for the Linear that follows.  The Hadamard product a = u o h is not
+ * stored: cnb_hadamard_gelu_bwd recomputes it when a_re == NULL.  Same reference kernels as
+ * cnb_dft_fwd + cnb_hadamard_gelu_fwd. */
+int cnb_dft_fused_ok(int N);
+int cnb_dft_hadamard_gelu_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
+                              const float* h_re, const float* h_im,
+                              float* u_re, float* u_im, float* y_re, float* y_im,
+                              float* y_split, int B, int N, void* stream);
 /* TriangFourier: Y[b,p] = N^-1/2 sum_{q <= p} X[b,q] e^{-2 pi i pq/N} and its backward
  * dX*[b,q] (+)= N^-1/2 sum_{p >= q} G*[b,p] e^{+2 pi i pq/N}: the complex GEMM against the
  * lower-triangular twiddle matrix.  Replaces TrianFourierGpu::gpu_T_fft_forward / _backward
@@ -209,7 +219,8 @@ int cnb_hadamard_gelu_fwd_split(cnb_ctx* ctx, const float* u_re, const float* u_
                                 const float* h_re, const float* h_im,
                                 float* a_re, float* a_im, float* y_re, float* y_im,
                                 float* y_split, int B, int N, void* stream);
-/* Fused backward of the pair: t = gelu_bwd(g*, a); du* (+)= t o conj(h); dh* (+)= sum_b t o conj(u). */
+/* Fused backward of the pair: t = gelu_bwd(g*, a); du* (+)= t o conj(h); dh* (+)= sum_b t o conj(u).
+ * a_re == a_im == NULL: a = u o h is recomputed. */
 int cnb_hadamard_gelu_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                           const float* a_re, const float* a_im,
                           const float* u_re, const float* u_im,
