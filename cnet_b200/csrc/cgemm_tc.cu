@@ -513,8 +513,6 @@ bool cgemm_tc_shape_ok(int M, int N, int K) {
     return (K % 4 == 0) && K >= 32 && M >= 64 && N >= 64;
 }
 
-void cgemm_tc_release(cnb_ctx*) {}
-
 size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
     return 4 * ((size_t) M * K + (size_t) N * K) * sizeof(float) + 4096;
 }
@@ -529,10 +527,10 @@ void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* const d
 int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
                       const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
                       int accumulate, cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};                       // the attribute is per device
+    if (!attr_set[ctx->device & 63]) {
         CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        attr_set = true;
+        attr_set[ctx->device & 63] = true;
     }
     if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
         return set_error(CNB_ERR_ARG, "cgemm_tc: misaligned output");

@@ -208,7 +208,8 @@ size_t skinny_workspace_bytes(int B, int in, int out, int sm_count) {
 int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, const float* wi, float* yr, float* yi,
                int B, int in, int out, cudaStream_t st) {
     size_t smem = (size_t) out * in * 2 * sizeof(float);
-    static size_t smem_set = 0;
+    static size_t smem_set_dev[64] = {};                 // the attribute is per device
+    size_t& smem_set = smem_set_dev[ctx->device & 63];
     if (smem > smem_set) {
         CNB_CUDA(cudaFuncSetAttribute(skinny_fwd_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
         smem_set = smem;

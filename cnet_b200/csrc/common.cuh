@@ -65,7 +65,6 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
                       int accumulate, cudaStream_t st);
 // split = 4 consecutive planes of pad64(n) floats: hi_re, hi_im, lo_re, lo_im
 int split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, cudaStream_t st);
-void cgemm_tc_release(cnb_ctx* ctx);
 
 // Skinny Linear (out <= 16): HBM-bound fp32 kernels.
 bool skinny_ok(int B, int in, int out);
@@ -85,10 +84,6 @@ int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi
 // (yr, yi) and, when sp != NULL, the hi/lo split planes of y.
 int fft_hadamard_gelu(cnb_ctx* ctx, const float* xr, const float* xi, const float* hr, const float* hi, float* ur,
                       float* ui, float* yr, float* yi, float* sp, int B, int N, cudaStream_t st);
-
-// [R, C] -> [C, R] transpose of a re/im plane pair (operand staging for the K-major GEMM).
-int transpose_planes(const float* s_re, const float* s_im, float* d_re, float* d_im,
-                     int R, int C, cudaStream_t st);
 
 }  // namespace cnb
 

@@ -88,7 +88,6 @@ int cnb_create_external(int device, void* arena, size_t arena_bytes, cnb_ctx** o
 
 int cnb_destroy(cnb_ctx* ctx) {
     if (!ctx) return CNB_OK;
-    cnb::cgemm_tc_release(ctx);
     if (ctx->owns && ctx->base) cudaFree(ctx->base);
     delete ctx;
     return CNB_OK;
@@ -107,7 +106,6 @@ int cnb_alloc(cnb_ctx* ctx, size_t bytes, void** out) {
 
 int cnb_reset(cnb_ctx* ctx) {
     CNB_CHECK_ARG(ctx, "cnb_reset: null context");
-    cnb::cgemm_tc_release(ctx);
     ctx->used = 256;            // keep the status word
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;

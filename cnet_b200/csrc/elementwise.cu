@@ -1,5 +1,5 @@
 // HBM-bound element-wise layers of the complex training step: Hadamard, CGelu (and the
-// fused pair), Residual, gradient pass-through, SGD update, plane transposes.
+// fused pair), CRelu, Residual, gradient pass-through, SGD and Adam updates.
 // All kernels stream each plane once with 16-byte accesses where the row length allows
 // it (W = 4), else scalar (W = 1); grids are sized in multiples of the SM count.
 #include <algorithm>
@@ -315,29 +315,6 @@ __global__ void sgd_k(float* __restrict__ w, float* __restrict__ g, size_t total
     }
 }
 
-// 32x32 smem-tiled transpose of a plane pair: dst[c][r] = src[r][c]
-__global__ void transpose_k(const float* __restrict__ sr, const float* __restrict__ si,
-                            float* __restrict__ dr, float* __restrict__ di, int R, int C) {
-    __shared__ float tr[32][33], ti[32][33];
-    int c = blockIdx.x * 32 + threadIdx.x;
-    for (int k = threadIdx.y; k < 32; k += 8) {
-        int r = blockIdx.y * 32 + k;
-        if (r < R && c < C) {
-            tr[k][threadIdx.x] = sr[(size_t) r * C + c];
-            ti[k][threadIdx.x] = si[(size_t) r * C + c];
-        }
-    }
-    __syncthreads();
-    int r = blockIdx.y * 32 + threadIdx.x;
-    for (int k = threadIdx.y; k < 32; k += 8) {
-        int cc = blockIdx.x * 32 + k;
-        if (r < R && cc < C) {
-            dr[(size_t) cc * R + r] = tr[threadIdx.x][k];
-            di[(size_t) cc * R + r] = ti[threadIdx.x][k];
-        }
-    }
-}
-
 template <typename... P> bool all_aligned(P... p) { return (aligned16(p) && ...); }
 
 int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, const float* ar, const float* ai,
@@ -374,15 +351,6 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
 
 }  // namespace
 
-namespace cnb {
-int transpose_planes(const float* s_re, const float* s_im, float* d_re, float* d_im, int R, int C,
-                     cudaStream_t st) {
-    dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
-    transpose_k<<<grid, block, 0, st>>>(s_re, s_im, d_re, d_im, R, C);
-    CNB_LAUNCH_CHECK("transpose");
-    return CNB_OK;
-}
-}  // namespace cnb
 
 #define DISPATCH_W(vec_ok, KERNEL, total, ...)                                              \
     do {                                                                                    \

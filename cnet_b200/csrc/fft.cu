@@ -208,11 +208,12 @@ int launch(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi,
            int accumulate, const FftEpilogue& ep, cudaStream_t st) {
     constexpr int ROWS = 256 / R;
     size_t smem = (size_t) ROWS * 2 * R * (R + 1) * sizeof(float);
-    static bool attr_done[2] = {false, false};
-    if (!attr_done[inverse]) {
+    static bool attr_done[64][2] = {};                   // the attribute is per device
+    bool& done = attr_done[ctx->device & 63][inverse];
+    if (!done) {
         if (inverse) CNB_CUDA(cudaFuncSetAttribute(fft_rr_k<R, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
         else CNB_CUDA(cudaFuncSetAttribute(fft_rr_k<R, -1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-        attr_done[inverse] = true;
+        done = true;
     }
     int blocks = (B + ROWS - 1) / ROWS;
     int cap = ctx->sm_count * 8;
