@@ -562,8 +562,13 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     ctas = (total + upc - 1) / upc;
     bool splits_tiles = (upc % k_blocks) != 0;
     if (splits_tiles && !accumulate) {
-        CNB_CUDA(cudaMemsetAsync(d_re, 0, (size_t) M * N * sizeof(float), st));
-        CNB_CUDA(cudaMemsetAsync(d_im, 0, (size_t) M * N * sizeof(float), st));
+        const size_t plane = (size_t) M * N;
+        if (d_im == d_re + plane) {                      // adjacent planes: one fill
+            CNB_CUDA(cudaMemsetAsync(d_re, 0, 2 * plane * sizeof(float), st));
+        } else {
+            CNB_CUDA(cudaMemsetAsync(d_re, 0, plane * sizeof(float), st));
+            CNB_CUDA(cudaMemsetAsync(d_im, 0, plane * sizeof(float), st));
+        }
     }
     TcParams p;
     p.d_re = d_re; p.d_im = d_im; p.r_re = r_re; p.r_im = r_im;
@@ -581,7 +586,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
 // [K, rows]; it is then consumed MN-major in place (rows % 32 == 0) or transposed while it is split.
 int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
                  const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
-                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st) {
+                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st, const float* b_split) {
     float* ws = nullptr;
     int rc = ensure_scratch(ctx, cgemm_tc_workspace_bytes(M, N, K), &ws);
     if (rc != CNB_OK) return rc;
@@ -603,7 +608,11 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
         return CNB_OK;
     };
     if ((rc = split(a_re, a_im, ap, M, a_trans, &a_mn)) != CNB_OK) return rc;
-    if ((rc = split(b_re, b_im, bp, N, b_trans, &b_mn)) != CNB_OK) return rc;
+    if (b_split) {                                 // a constant B operand split once by its owner, [N, K]
+        for (int q = 0; q < 4; ++q) bp[q] = const_cast<float*>(b_split) + q * nb;
+    } else if ((rc = split(b_re, b_im, bp, N, b_trans, &b_mn)) != CNB_OK) {
+        return rc;
+    }
     return cgemm_tc_presplit(ctx, ap, a_mn, bp, b_mn, conjB, r_re, r_im, d_re, d_im, M, N, K, accumulate, st);
 }
 

@@ -12,6 +12,7 @@
 struct cnb_twiddle {
     float* re = nullptr;   // [N, N] planes, F[p,q] = N^-1/2 e^{-2 pi i pq/N}
     float* im = nullptr;
+    float* split = nullptr;   // hi/lo TF32 planes of the matrix (made once), or null when the tiles cannot take it
 };
 
 struct cnb_ctx {
@@ -57,7 +58,8 @@ bool cgemm_tc_shape_ok(int M, int N, int K);
 // General form: a_trans / b_trans = the source planes are stored [K, rows] (transposed while splitting).
 int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
                  const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
-                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st);
+                 float* d_im, int M, int N, int K, int accumulate, cudaStream_t st,
+                 const float* b_split = nullptr);
 size_t cgemm_tc_workspace_bytes(int M, int N, int K);
 // Operands already split into [hi_re, hi_im, lo_re, lo_im] planes; major 0 = [rows, K], 1 = [K, rows].
 int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,

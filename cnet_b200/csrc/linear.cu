@@ -50,9 +50,31 @@ int get_twiddle(cnb_ctx* ctx, int key, cudaStream_t st, cnb_twiddle* out) {
         tri_mask_k<<<ctx->sm_count * 4, 256, 0, st>>>(t.re, t.im, N);
         CNB_LAUNCH_CHECK("tri_mask");
     }
+    if (cnb::cgemm_tc_shape_ok(64, N, N) && (!cnb::fft_supported(N) || (key & kTriKey))) {
+        // the matrix is a constant: where the GEMM is the transform's engine, its hi/lo split is
+        // made here, not by every product
+        rc = cnb_alloc(ctx, cnb_split_floats((size_t) N * N) * sizeof(float), &p);
+        if (rc != CNB_OK) return rc;
+        t.split = static_cast<float*>(p);
+        rc = cnb::split_planes(ctx, t.re, t.im, (size_t) N * N, t.split, st);
+        if (rc != CNB_OK) return rc;
+    }
     ctx->twiddles[key] = t;
     *out = t;
     return CNB_OK;
+}
+
+// X F^T (conj = 0) or G conj(F) (conj = 1) with F symmetric, so F itself is the K-major operand
+int twiddle_product(cnb_ctx* ctx, const cnb_twiddle& t, const float* x_re, const float* x_im, float* y_re, float* y_im,
+                    int B, int N, int conj, int accumulate, cudaStream_t st) {
+    if (cnb::cgemm_tc_shape_ok(B, N, N)) {
+        cnb::g_last_engine = 1;
+        return cnb::cgemm_tc_run(ctx, x_re, x_im, 0, t.re, t.im, 0, conj, nullptr, nullptr, y_re, y_im, B, N, N,
+                                 accumulate, st, t.split);
+    }
+    cnb::g_last_engine = 2;
+    return cnb::cgemm_simt(ctx, x_re, x_im, N, 1, t.re, t.im, N, 1, conj, nullptr, nullptr, y_re, y_im, B, N, N,
+                           accumulate, st);
 }
 
 }  // namespace
@@ -132,8 +154,7 @@ int cnb_dft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, float* y_re,
     cnb_twiddle t;
     int rc = get_twiddle(ctx, N, cnb::S(stream), &t);
     if (rc != CNB_OK) return rc;
-    // Y = X F^T with F symmetric: the Linear forward with W = F
-    return cnb_linear_fwd(ctx, x_re, x_im, t.re, t.im, nullptr, nullptr, y_re, y_im, B, N, N, stream);
+    return twiddle_product(ctx, t, x_re, x_im, y_re, y_im, B, N, 0, 0, cnb::S(stream));
 }
 
 int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re, float* dx_im, int B, int N,
@@ -148,15 +169,7 @@ int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re
     cnb_twiddle t;
     int rc = get_twiddle(ctx, N, st, &t);
     if (rc != CNB_OK) return rc;
-    // dX* = G* conj(F); F symmetric, so F itself is the K-major [N(in), N(out)] operand: no staging copy
-    if (cnb::cgemm_tc_shape_ok(B, N, N)) {
-        cnb::g_last_engine = 1;
-        return cnb::cgemm_tc_nt(ctx, g_re, g_im, t.re, t.im, 1, nullptr, nullptr, dx_re, dx_im, B, N, N, accumulate,
-                                st);
-    }
-    cnb::g_last_engine = 2;
-    return cnb::cgemm_simt(ctx, g_re, g_im, N, 1, t.re, t.im, N, 1, 1, nullptr, nullptr, dx_re, dx_im, B, N, N,
-                           accumulate, st);
+    return twiddle_product(ctx, t, g_re, g_im, dx_re, dx_im, B, N, 1, accumulate, st);
 }
 
 /* Scratch the three Linear products and the column reductions of one layer may need. */
@@ -242,7 +255,8 @@ int cnb_tdft_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, float* y_re
     cnb_twiddle t;
     int rc = get_twiddle(ctx, N | kTriKey, cnb::S(stream), &t);
     if (rc != CNB_OK) return rc;
-    return cnb_linear_fwd(ctx, x_re, x_im, t.re, t.im, nullptr, nullptr, y_re, y_im, B, N, N, stream);
+    // the forward product takes the masked matrix as the Linear weight; it is not symmetric
+    return twiddle_product(ctx, t, x_re, x_im, y_re, y_im, B, N, 0, 0, cnb::S(stream));
 }
 
 int cnb_tdft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, float* dx_re, float* dx_im, int B, int N,

@@ -578,7 +578,8 @@ size_t CNet::requiredArenaBytes(int B) const {
 		if (weight) floats += 4 * pad64(f->out_size_);
 		else floats += 4 * pad64((size_t) B * f->out_size_);
 		if (CEmbedding* e = dynamic_cast<CEmbedding*>(f)) floats += 4 * pad64((size_t) e->inSize());
-		if (dynamic_cast<FourierTrans*>(f) || dynamic_cast<TriangFourier*>(f)) dft += (size_t) 2 * f->in_size_ * f->in_size_ * 4 + 512;
+		if ((dynamic_cast<FourierTrans*>(f) && !cnb_dft_fused_ok((int) f->in_size_)) || dynamic_cast<TriangFourier*>(f))     // twiddle planes + their split
+			dft += (size_t) 2 * f->in_size_ * f->in_size_ * 4 + cnb_split_floats((size_t) f->in_size_ * f->in_size_) * 4 + 1024;
 		extra += f->extraBytes(B) + 256;
 	}
 	size_t gs = 0;
