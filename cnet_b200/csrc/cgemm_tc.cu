@@ -504,6 +504,23 @@ int make_map_mn(CUtensorMap* m, const float* base, int rows, int K) {
     return CNB_OK;
 }
 
+// Clears the two output planes of a product whose tiles are summed with atomics.
+__global__ void zero_pair_k(float* __restrict__ a, float* __restrict__ b, size_t n) {
+    const size_t n4 = n / 4;
+    const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+    const size_t tid = (size_t) blockIdx.x * blockDim.x + threadIdx.x, step = (size_t) gridDim.x * blockDim.x;
+    if (vec) {
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (size_t i = tid; i < n4; i += step) {
+            reinterpret_cast<float4*>(a)[i] = z;
+            reinterpret_cast<float4*>(b)[i] = z;
+        }
+        for (size_t i = 4 * n4 + tid; i < n; i += step) { a[i] = 0.f; b[i] = 0.f; }
+    } else {
+        for (size_t i = tid; i < n; i += step) { a[i] = 0.f; b[i] = 0.f; }
+    }
+}
+
 }  // namespace
 
 namespace cnb {
@@ -562,13 +579,12 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     ctas = (total + upc - 1) / upc;
     bool splits_tiles = (upc % k_blocks) != 0;
     if (splits_tiles && !accumulate) {
+        // one launch clears both planes (they need not be adjacent or in one allocation)
         const size_t plane = (size_t) M * N;
-        if (d_im == d_re + plane) {                      // adjacent planes: one fill
-            CNB_CUDA(cudaMemsetAsync(d_re, 0, 2 * plane * sizeof(float), st));
-        } else {
-            CNB_CUDA(cudaMemsetAsync(d_re, 0, plane * sizeof(float), st));
-            CNB_CUDA(cudaMemsetAsync(d_im, 0, plane * sizeof(float), st));
-        }
+        const size_t vec = plane / 4 + 1;
+        const int blocks = (int) std::min<size_t>((vec + 255) / 256, (size_t) ctx->sm_count * 8);
+        zero_pair_k<<<blocks, 256, 0, st>>>(d_re, d_im, plane);
+        CNB_LAUNCH_CHECK("zero_pair");
     }
     TcParams p;
     p.d_re = d_re; p.d_im = d_im; p.r_re = r_re; p.r_im = r_im;

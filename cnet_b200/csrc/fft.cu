@@ -10,60 +10,17 @@
 // table is generated once per N in double precision.  direction = +1 gives the conjugate
 // (backward) transform dX*[q] = N^-1/2 sum_p G*[p] e^{+2 pi i pq/N}.
 #include "common.cuh"
+#include "fft_regs.cuh"
 
 namespace {
 
-__device__ constexpr float kCos64[32] = {1.000000000e+00f, 9.951847267e-01f, 9.807852804e-01f, 9.569403357e-01f, 9.238795325e-01f, 8.819212643e-01f, 8.314696123e-01f, 7.730104534e-01f, 7.071067812e-01f, 6.343932842e-01f, 5.555702330e-01f, 4.713967368e-01f, 3.826834324e-01f, 2.902846773e-01f, 1.950903220e-01f, 9.801714033e-02f, 6.123233996e-17f, -9.801714033e-02f, -1.950903220e-01f, -2.902846773e-01f, -3.826834324e-01f, -4.713967368e-01f, -5.555702330e-01f, -6.343932842e-01f, -7.071067812e-01f, -7.730104534e-01f, -8.314696123e-01f, -8.819212643e-01f, -9.238795325e-01f, -9.569403357e-01f, -9.807852804e-01f, -9.951847267e-01f};
-__device__ constexpr float kSin64[32] = {0.000000000e+00f, 9.801714033e-02f, 1.950903220e-01f, 2.902846773e-01f, 3.826834324e-01f, 4.713967368e-01f, 5.555702330e-01f, 6.343932842e-01f, 7.071067812e-01f, 7.730104534e-01f, 8.314696123e-01f, 8.819212643e-01f, 9.238795325e-01f, 9.569403357e-01f, 9.807852804e-01f, 9.951847267e-01f, 1.000000000e+00f, 9.951847267e-01f, 9.807852804e-01f, 9.569403357e-01f, 9.238795325e-01f, 8.819212643e-01f, 8.314696123e-01f, 7.730104534e-01f, 7.071067812e-01f, 6.343932842e-01f, 5.555702330e-01f, 4.713967368e-01f, 3.826834324e-01f, 2.902846773e-01f, 1.950903220e-01f, 9.801714033e-02f};
-
-template <int R> __device__ __forceinline__ constexpr int bitrev(int v) {
-    int r = 0;
-    for (int b = 1; b < R; b <<= 1) { r = (r << 1) | (v & 1); v >>= 1; }
-    return r;
-}
-
-// In-register radix-2 decimation-in-frequency FFT of R points; output index k is found at
-// position bitrev(k).  SIGN = -1: e^{-2 pi i jk/R}; +1: conjugate.
-template <int R, int SIGN>
-__device__ __forceinline__ void fft_regs(float (&re)[R], float (&im)[R]) {
-#pragma unroll
-    for (int len = R; len >= 2; len >>= 1) {
-        const int half = len >> 1;
-#pragma unroll
-        for (int base = 0; base < R; base += len) {
-#pragma unroll
-            for (int j = 0; j < half; ++j) {
-                const int i0 = base + j, i1 = base + j + half;
-                float ar = re[i0], ai = im[i0], br = re[i1], bi = im[i1];
-                re[i0] = ar + br; im[i0] = ai + bi;
-                float dr = ar - br, di = ai - bi;
-                const int t = j * (64 / len);            // w_len^j = w_64^(j*64/len)
-                if (t == 0) { re[i1] = dr; im[i1] = di; }
-                else {
-                    const float c = kCos64[t], s = SIGN * kSin64[t];   // e^{SIGN * 2 pi i t/64}
-                    re[i1] = dr * c - di * s;
-                    im[i1] = dr * s + di * c;
-                }
-            }
-        }
-    }
-}
+using namespace cnb_fft;
 
 // Barrier among the R threads that share a row: they sit in one warp when R <= 32, so warps run
 // their load / transform / store phases independently and overlap each other's memory latency.
 template <int R> __device__ __forceinline__ void row_sync() {
     if constexpr (R <= 32) __syncwarp(); else __syncthreads();
 }
-
-// Optional fused tail of the forward transform: Hadamard with a shared vector h, then CGelu.
-struct FftEpilogue {
-    const float* hr = nullptr;      // h planes [N]; NULL = plain transform
-    const float* hi = nullptr;
-    float* gr = nullptr;            // gelu(u o h) planes [B, N]
-    float* gi = nullptr;
-    float* sp = nullptr;            // hi/lo split of that (4 planes of np floats) or NULL
-    size_t np = 0;
-};
 
 template <int R, int SIGN>
 __global__ void __launch_bounds__(256, (R <= 32 ? 2 : 1))
@@ -248,7 +205,7 @@ static int fft_dispatch(cnb_ctx* ctx, const float* xr, const float* xi, float* y
     }
     const float2* tw = reinterpret_cast<const float2*>(t.re);
     if (N == 256) return launch<16>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
-    if (N == 1024) return launch<32>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
+    if (N == 1024) return fft1024_pipe(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
     if (N == 4096) return launch<64>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
     return set_error(CNB_ERR_UNSUPPORTED, "fft: N=%d", N);
 }
