@@ -91,7 +91,7 @@ __global__ void hadamard_bwd_elem_k(const float* __restrict__ gr, const float* _
 // Block = 32 column groups of W columns x 8 row lanes; with W = 4 every access is 16 bytes and a
 // warp touches 512 contiguous bytes of each plane per row.
 template <int MODE, int W>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)       // 4 CTAs per SM: the grid below is one full wave
 colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
                    const float* __restrict__ ar, const float* __restrict__ ai,
                    const float* __restrict__ ur, const float* __restrict__ ui,
@@ -326,7 +326,17 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
                (!dur || (aligned16(dur) && aligned16(dui)));
     int w = vec ? 4 : 1;
     int col_blocks = (N + 32 * w - 1) / (32 * w);
-    int chunks = (ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
+    // one full wave: as many row chunks as the resident CTAs of the whole device allow
+    static int occ[4] = {0, 0, 0, 0};
+    int& per_sm = occ[(mode ? 2 : 0) + (vec ? 1 : 0)];
+    if (!per_sm) {
+        cudaError_t e = mode ? (vec ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, colreduce_stage1_k<1, 4>, 256, 0)
+                                    : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, colreduce_stage1_k<1, 1>, 256, 0))
+                             : (vec ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, colreduce_stage1_k<0, 4>, 256, 0)
+                                    : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, colreduce_stage1_k<0, 1>, 256, 0));
+        if (e != cudaSuccess || per_sm < 1) per_sm = 4;
+    }
+    int chunks = std::max(1, ctx->sm_count * per_sm / col_blocks);
     int max_chunks = (B + 7) / 8;
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks > 128) chunks = 128;

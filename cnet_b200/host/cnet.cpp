@@ -732,11 +732,40 @@ bool CNet::allocateOnGpu(int B) {
 		f->out_.real_ = base; f->out_.imag_ = base + n;
 		if (need_grad) { f->out_.dz_star_real_ = base + 2 * n; f->out_.dz_star_imag_ = base + 3 * n; }
 	}
+	// A Residual hands its dL/dz* to both operands unchanged.  Where the skip operand p gets every other
+	// contribution later in the backward pass than the last reader of the Residual's gradient, p's gradient
+	// planes ARE the Residual's planes: the pass-through copy disappears and the later contributions
+	// accumulate in place.  Walked from the output side so that a chain of blocks shares one tensor.
+	{
+		std::map<CFunc*, size_t> pos;
+		for (size_t k = 0; k < func_list_.size(); ++k) pos[func_list_[k]] = k;
+		for (auto it = func_list_.rbegin(); it != func_list_.rend(); ++it) {
+			Residual* r = dynamic_cast<Residual*>(*it);
+			if (!r || !r->out_.dz_star_real_ || r->prev_func_[0] == r->prev_func_[1]) continue;
+			for (int k = 0; k < 2; ++k) {
+				CFunc* sp = r->prev_func_[k];
+				CFunc* q = r->prev_func_[1 - k];
+				Linear* ql = dynamic_cast<Linear*>(q);
+				Linear* pl = dynamic_cast<Linear*>(sp);
+				if (!sp->batched_ || !sp->out_.dz_star_real_ || (pl && pl->fused_residual_ == r)) continue;
+				// the Residual itself reads the gradient; a Linear fused with it reads it again in its own backward
+				size_t reader = (ql && ql->fused_residual_ == r) ? pos[q] : pos[r];
+				bool later = true;
+				for (auto c : sp->next_func_) if (c != r && pos[c] >= reader) later = false;
+				if (!later) continue;
+				sp->out_.dz_star_real_ = r->out_.dz_star_real_;
+				sp->out_.dz_star_imag_ = r->out_.dz_star_imag_;
+				r->grad_transient_ = true;
+				break;
+			}
+		}
+	}
 	for (auto f : func_list_) {
 		if (Linear* l = dynamic_cast<Linear*>(f)) {
 			if (l->fused_residual_) {
 				Vars v = l->fused_residual_->out_;
 				l->out_ = v;
+				l->grad_transient_ = l->fused_residual_->grad_transient_;
 			}
 		}
 		size_t eb = f->extraBytes(B);
@@ -1120,6 +1149,7 @@ bool CNet::readOutput(int uid, int what, float* re, float* im) {
 	if (Linear* l = dynamic_cast<Linear*>(f)) {
 		if (l->fused_residual_ && what == 0) sr = nullptr;   // only the post-Residual sum exists
 	}
+	if (what != 0 && f->grad_transient_) sr = nullptr;       // overwritten by the gradient of the Residual's operand
 	if (!sr) { fail(CNB_ERR_ARG, f->getName() + ": tensor not materialised (fused)"); return false; }
 	size_t n = (size_t) (f->batched_ ? cur_batch_ : 1) * f->out_size_;
 	int rc = cnb_d2h(ctx_, re, sr, n * sizeof(float), stream_);

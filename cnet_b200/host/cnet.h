@@ -141,6 +141,7 @@ public:
 	Vars out_;
 	bool batched_ = true;        // false: one row shared by the batch (weights)
 	bool grad_written_ = false;  // has a consumer already written dL/dz* of out_ in this backward?
+	bool grad_transient_ = false; // dL/dz* planes are shared with a Residual operand and accumulated over in place
 	bool fused_away_ = false;    // a neighbour's fused kernel does this layer's work
 
 	CFunc(Uid uid, InSize in, OutSize out) : uid_(uid.value()), in_size_(in.value()), out_size_(out.value()) {}
