@@ -15,40 +15,71 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// Forward: W (out x in, both planes) is staged once per CTA in shared memory; every warp then walks
-// batch rows two at a time: each lane owns a strided slice of the input, accumulates the `out`
-// products against shared-memory W, and the warp reduces them with shuffles.  X is read once.
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ void ldv(const float* p, float (&v)[4]) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ldv(const float* p, float (&v)[1]) { v[0] = __ldg(p); }
+
+// OT is a compile-time bound of `out` (4, 8, 10 or 16): the accumulators of the unused outputs cost
+// no registers.  W = 4: every lane works on 4 consecutive inputs with 16-byte accesses (in % 4 == 0).
+
+// Forward: W (out x in, both planes) is staged once per CTA in shared memory (one fat CTA per SM, so the
+// staging is paid once per SM); every warp then walks batch rows two at a time: each lane owns a strided
+// set of input groups, accumulates the `out` products against W, and the warp reduces them with
+// shuffles.  X is read once.
+template <int OT, int W>
+__global__ void __launch_bounds__(512)
 skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const float* __restrict__ wr,
              const float* __restrict__ wi, float* __restrict__ yr, float* __restrict__ yi, int B, int in, int out) {
-    extern __shared__ float sw[];                        // [out][in] re, then [out][in] im
+    extern __shared__ __align__(16) float sw[];          // [out][in] re, then [out][in] im
     float* swr = sw;
     float* swi = sw + (size_t) out * in;
-    for (int e = threadIdx.x; e < out * in; e += blockDim.x) { swr[e] = wr[e]; swi[e] = wi[e]; }
+    const int total = out * in;
+    if constexpr (W == 4) {
+        for (int e = threadIdx.x * 4; e < total; e += blockDim.x * 4) {
+            *reinterpret_cast<float4*>(swr + e) = __ldg(reinterpret_cast<const float4*>(wr + e));
+            *reinterpret_cast<float4*>(swi + e) = __ldg(reinterpret_cast<const float4*>(wi + e));
+        }
+    } else {
+        for (int e = threadIdx.x; e < total; e += blockDim.x) { swr[e] = wr[e]; swi[e] = wi[e]; }
+    }
     __syncthreads();
     const int lane = threadIdx.x & 31;
     const long warp = ((long) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long nwarps = ((long) gridDim.x * blockDim.x) >> 5;
+    const int groups = in / W;
     for (long b0 = warp * 2; b0 < B; b0 += nwarps * 2) {
         const bool two = b0 + 1 < B;
-        float ar[2][MAXO], ai[2][MAXO];
+        float ar[2][OT], ai[2][OT];
 #pragma unroll
-        for (int o = 0; o < MAXO; ++o) { ar[0][o] = ai[0][o] = ar[1][o] = ai[1][o] = 0.f; }
+        for (int o = 0; o < OT; ++o) { ar[0][o] = ai[0][o] = ar[1][o] = ai[1][o] = 0.f; }
         const float* x0r = xr + b0 * in; const float* x0i = xi + b0 * in;
         const float* x1r = x0r + (two ? in : 0); const float* x1i = x0i + (two ? in : 0);
-        for (int i = lane; i < in; i += 32) {
-            float p0r = x0r[i], p0i = x0i[i], p1r = x1r[i], p1i = x1i[i];
+#pragma unroll 2
+        for (int c = lane; c < groups; c += 32) {
+            const int i = c * W;
+            float p0r[W], p0i[W], p1r[W], p1i[W];
+            ldv(x0r + i, p0r); ldv(x0i + i, p0i); ldv(x1r + i, p1r); ldv(x1i + i, p1i);
 #pragma unroll
-            for (int o = 0; o < MAXO; ++o) {
+            for (int o = 0; o < OT; ++o) {
                 if (o < out) {
-                    float cr = swr[o * in + i], ci = swi[o * in + i];
-                    ar[0][o] += p0r * cr - p0i * ci; ai[0][o] += p0r * ci + p0i * cr;
-                    ar[1][o] += p1r * cr - p1i * ci; ai[1][o] += p1r * ci + p1i * cr;
+                    float cr[W], ci[W];
+                    if constexpr (W == 4) {
+                        const float4 t = *reinterpret_cast<const float4*>(swr + o * in + i);
+                        const float4 u = *reinterpret_cast<const float4*>(swi + o * in + i);
+                        cr[0] = t.x; cr[1] = t.y; cr[2] = t.z; cr[3] = t.w; ci[0] = u.x; ci[1] = u.y; ci[2] = u.z; ci[3] = u.w;
+                    } else { cr[0] = swr[o * in + i]; ci[0] = swi[o * in + i]; }
+#pragma unroll
+                    for (int k = 0; k < W; ++k) {
+                        ar[0][o] += p0r[k] * cr[k] - p0i[k] * ci[k]; ai[0][o] += p0r[k] * ci[k] + p0i[k] * cr[k];
+                        ar[1][o] += p1r[k] * cr[k] - p1i[k] * ci[k]; ai[1][o] += p1r[k] * ci[k] + p1i[k] * cr[k];
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int o = 0; o < MAXO; ++o) {
+        for (int o = 0; o < OT; ++o) {
             if (o < out) {
                 float s0r = warp_sum(ar[0][o]), s0i = warp_sum(ai[0][o]);
                 float s1r = warp_sum(ar[1][o]), s1i = warp_sum(ai[1][o]);
@@ -61,43 +92,45 @@ skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const f
     }
 }
 
-// dX*: W columns for 4 consecutive inputs are read as float4; G[b, :] is broadcast.
-template <int W>
-__global__ void __launch_bounds__(256)
+// dX*: a thread keeps the W columns of its W consecutive inputs in registers and walks a chunk of batch
+// rows; G[b, :] is a broadcast read.  W is fetched once per (column group, row chunk).
+template <int OT, int W>
+__global__ void __launch_bounds__(256, (OT * W > 40 ? 1 : 2))
 skinny_bwd_x_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ wr,
                const float* __restrict__ wi, float* __restrict__ dr, float* __restrict__ di, int B, int in, int out,
-               int accumulate) {
-    const int per_row = in / W;
-    size_t total = (size_t) B * per_row;
-    for (size_t e = (size_t) blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t) gridDim.x * blockDim.x) {
-        size_t b = e / per_row;
-        int i = (int) (e % per_row) * W;
+               int accumulate, int rows_per_chunk) {
+    const int i = (blockIdx.x * 256 + threadIdx.x) * W;
+    if (i >= in) return;
+    float wre[OT][W], wim[OT][W];
+#pragma unroll
+    for (int o = 0; o < OT; ++o) {
+        if (o < out) { ldv(wr + (size_t) o * in + i, wre[o]); ldv(wi + (size_t) o * in + i, wim[o]); }
+        else {
+#pragma unroll
+            for (int k = 0; k < W; ++k) wre[o][k] = wim[o][k] = 0.f;
+        }
+    }
+    const int r0 = blockIdx.y * rows_per_chunk, r1 = min(B, r0 + rows_per_chunk);
+    for (int b = r0; b < r1; ++b) {
         float sr[W], si[W];
 #pragma unroll
         for (int k = 0; k < W; ++k) sr[k] = si[k] = 0.f;
 #pragma unroll
-        for (int o = 0; o < MAXO; ++o) {
+        for (int o = 0; o < OT; ++o) {
             if (o < out) {
-                float a = gr[b * out + o], c = gi[b * out + o];
-                float wre[W], wim[W];
-                if constexpr (W == 4) {
-                    float4 t = *reinterpret_cast<const float4*>(wr + (size_t) o * in + i);
-                    float4 u = *reinterpret_cast<const float4*>(wi + (size_t) o * in + i);
-                    wre[0] = t.x; wre[1] = t.y; wre[2] = t.z; wre[3] = t.w;
-                    wim[0] = u.x; wim[1] = u.y; wim[2] = u.z; wim[3] = u.w;
-                } else { wre[0] = wr[(size_t) o * in + i]; wim[0] = wi[(size_t) o * in + i]; }
+                const float a = __ldg(gr + (size_t) b * out + o), c = __ldg(gi + (size_t) b * out + o);
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
-                    sr[k] += a * wre[k] + c * wim[k];      // (a + ic)(wre - i wim)
-                    si[k] += c * wre[k] - a * wim[k];
+                    sr[k] += a * wre[o][k] + c * wim[o][k];      // (a + ic)(wre - i wim)
+                    si[k] += c * wre[o][k] - a * wim[o][k];
                 }
             }
         }
-        size_t off = b * in + i;
+        const size_t off = (size_t) b * in + i;
         if constexpr (W == 4) {
             float4 vr = make_float4(sr[0], sr[1], sr[2], sr[3]), vi = make_float4(si[0], si[1], si[2], si[3]);
             if (accumulate) {
-                float4 pr = *reinterpret_cast<const float4*>(dr + off), pi = *reinterpret_cast<const float4*>(di + off);
+                const float4 pr = *reinterpret_cast<const float4*>(dr + off), pi = *reinterpret_cast<const float4*>(di + off);
                 vr.x += pr.x; vr.y += pr.y; vr.z += pr.z; vr.w += pr.w;
                 vi.x += pi.x; vi.y += pi.y; vi.z += pi.z; vi.w += pi.w;
             }
@@ -112,31 +145,28 @@ skinny_bwd_x_k(const float* __restrict__ gr, const float* __restrict__ gi, const
 
 // stage 1: partial[c][o][i] = sum over the rows of chunk c of G[b,o] conj(X[b,i]);
 // block = 32 column groups of W columns x 8 row lanes (W = 4: 16-byte reads of X)
-template <int W>
-__global__ void __launch_bounds__(256)
+template <int OT, int W>
+__global__ void __launch_bounds__(256, (OT * W > 40 ? 1 : 2))
 skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ xr,
                       const float* __restrict__ xi, float* __restrict__ pr, float* __restrict__ pi, int B, int in,
                       int out, int rows_per_chunk) {
     __shared__ float sr[8][32 * W + 1], si[8][32 * W + 1];
     const int col = (blockIdx.x * 32 + threadIdx.x) * W;
     const int r0 = blockIdx.y * rows_per_chunk, r1 = min(B, r0 + rows_per_chunk);
-    float ar[MAXO][W], ai[MAXO][W];
+    float ar[OT][W], ai[OT][W];
 #pragma unroll
-    for (int o = 0; o < MAXO; ++o)
+    for (int o = 0; o < OT; ++o)
 #pragma unroll
         for (int k = 0; k < W; ++k) ar[o][k] = ai[o][k] = 0.f;
     if (col < in) {
+#pragma unroll 2
         for (int b = r0 + threadIdx.y; b < r1; b += 8) {
             float x[W], y[W];
-            if constexpr (W == 4) {
-                float4 t = *reinterpret_cast<const float4*>(xr + (size_t) b * in + col);
-                float4 u = *reinterpret_cast<const float4*>(xi + (size_t) b * in + col);
-                x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w; y[0] = u.x; y[1] = u.y; y[2] = u.z; y[3] = u.w;
-            } else { x[0] = xr[(size_t) b * in + col]; y[0] = xi[(size_t) b * in + col]; }
+            ldv(xr + (size_t) b * in + col, x); ldv(xi + (size_t) b * in + col, y);
 #pragma unroll
-            for (int o = 0; o < MAXO; ++o) {
+            for (int o = 0; o < OT; ++o) {
                 if (o < out) {
-                    float a = gr[(size_t) b * out + o], c = gi[(size_t) b * out + o];
+                    const float a = __ldg(gr + (size_t) b * out + o), c = __ldg(gi + (size_t) b * out + o);
 #pragma unroll
                     for (int k = 0; k < W; ++k) {
                         ar[o][k] += a * x[k] + c * y[k];       // (a + ic)(x - iy)
@@ -148,7 +178,7 @@ skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi
     }
     const int t = threadIdx.y * 32 + threadIdx.x;
 #pragma unroll
-    for (int o = 0; o < MAXO; ++o) {
+    for (int o = 0; o < OT; ++o) {
         if (o < out) {
             __syncthreads();
 #pragma unroll
@@ -205,40 +235,63 @@ size_t skinny_workspace_bytes(int B, int in, int out, int sm_count) {
     return (size_t) chunks * out * in * 2 * sizeof(float);
 }
 
+// picks the instantiation whose output bound is the smallest one that covers `out`
+#define CNB_SKINNY_DISPATCH(KERNEL, W, ...)                                   \
+    do {                                                                      \
+        if (out <= 4) KERNEL<4, W> __VA_ARGS__;                               \
+        else if (out <= 8) KERNEL<8, W> __VA_ARGS__;                          \
+        else if (out <= 10) KERNEL<10, W> __VA_ARGS__;                        \
+        else KERNEL<16, W> __VA_ARGS__;                                       \
+    } while (0)
+
+static bool aligned16(const void* a, const void* b, const void* c = nullptr, const void* d = nullptr) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+             reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
+
 int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, const float* wi, float* yr, float* yi,
                int B, int in, int out, cudaStream_t st) {
-    size_t smem = (size_t) out * in * 2 * sizeof(float);
+    const bool vec = (in % 4 == 0) && aligned16(xr, xi, wr, wi);
+    const size_t smem = (size_t) out * in * 2 * sizeof(float);
     static size_t smem_set_dev[64] = {};                 // the attribute is per device
     size_t& smem_set = smem_set_dev[ctx->device & 63];
     if (smem > smem_set) {
-        CNB_CUDA(cudaFuncSetAttribute(skinny_fwd_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+#define CNB_SKINNY_ATTR(OT, W) CNB_CUDA(cudaFuncSetAttribute(skinny_fwd_k<OT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem))
+        CNB_SKINNY_ATTR(4, 4); CNB_SKINNY_ATTR(8, 4); CNB_SKINNY_ATTR(10, 4); CNB_SKINNY_ATTR(16, 4);
+        CNB_SKINNY_ATTR(4, 1); CNB_SKINNY_ATTR(8, 1); CNB_SKINNY_ATTR(10, 1); CNB_SKINNY_ATTR(16, 1);
+#undef CNB_SKINNY_ATTR
         smem_set = smem;
     }
-    long blocks = ((B + 1) / 2 + 7) / 8;                 // 8 warps per CTA, 2 rows per warp and pass
-    long cap = (long) ctx->sm_count * (smem > 100 * 1024 ? 1 : 2);
-    skinny_fwd_k<<<(int) std::max<long>(1, std::min(blocks, cap)), 256, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out);
+    const long blocks = ((B + 1) / 2 + 15) / 16;         // 16 warps per CTA, 2 rows per warp and pass
+    const int grid = (int) std::max<long>(1, std::min<long>(blocks, ctx->sm_count));
+    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, <<<grid, 512, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
+    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, <<<grid, 512, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
     CNB_LAUNCH_CHECK("skinny_fwd");
     return CNB_OK;
 }
 
 int skinny_bwd_x(cnb_ctx* ctx, const float* gr, const float* gi, const float* wr, const float* wi, float* dr, float* di,
                  int B, int in, int out, int accumulate, cudaStream_t st) {
-    bool vec = (in % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) | reinterpret_cast<uintptr_t>(wi) |
-                                  reinterpret_cast<uintptr_t>(dr) | reinterpret_cast<uintptr_t>(di)) & 15) == 0;
-    size_t total = (size_t) B * (vec ? in / 4 : in);
-    size_t blocks = (total + 255) / 256, cap = (size_t) ctx->sm_count * 16;
-    if (vec) skinny_bwd_x_k<4><<<(int) std::min(blocks, cap), 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate);
-    else skinny_bwd_x_k<1><<<(int) std::min(blocks, cap), 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate);
+    const bool vec = (in % 4 == 0) && aligned16(wr, wi, dr, di);
+    const int w = vec ? 4 : 1;
+    const int col_blocks = (in + 256 * w - 1) / (256 * w);
+    int chunks = std::max(1, ctx->sm_count * 2 / col_blocks);            // two CTAs per SM are resident
+    chunks = std::min(chunks, B);
+    const int rows = (B + chunks - 1) / chunks;
+    chunks = (B + rows - 1) / rows;
+    const dim3 grid(col_blocks, chunks);
+    if (vec) CNB_SKINNY_DISPATCH(skinny_bwd_x_k, 4, <<<grid, 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate, rows));
+    else CNB_SKINNY_DISPATCH(skinny_bwd_x_k, 1, <<<grid, 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate, rows));
     CNB_LAUNCH_CHECK("skinny_bwd_x");
     return CNB_OK;
 }
 
 int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr, const float* xi, float* dr, float* di,
                  int B, int in, int out, int accumulate, cudaStream_t st) {
-    bool vec = (in % 4 == 0) && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(xi)) & 15) == 0;
+    const bool vec = (in % 4 == 0) && aligned16(xr, xi);
     int w = vec ? 4 : 1;
     int col_blocks = (in + 32 * w - 1) / (32 * w);
-    int chunks = (ctx->sm_count * 4 + col_blocks - 1) / col_blocks;
+    int chunks = (ctx->sm_count * 2 + col_blocks - 1) / col_blocks;      // two CTAs per SM are resident
     chunks = std::max(1, std::min(chunks, std::min((B + 7) / 8, 128)));
     int rows = (B + chunks - 1) / chunks;
     chunks = (B + rows - 1) / rows;
@@ -248,8 +301,9 @@ int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr
     if (rc != CNB_OK) return rc;
     float* pr = ws;
     float* pi = ws + (size_t) chunks * n;
-    if (vec) skinny_bwd_w_stage1_k<4><<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
-    else skinny_bwd_w_stage1_k<1><<<dim3(col_blocks, chunks), dim3(32, 8), 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows);
+    const dim3 grid(col_blocks, chunks), block(32, 8);
+    if (vec) CNB_SKINNY_DISPATCH(skinny_bwd_w_stage1_k, 4, <<<grid, block, 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows));
+    else CNB_SKINNY_DISPATCH(skinny_bwd_w_stage1_k, 1, <<<grid, block, 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows));
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage1");
     skinny_bwd_w_stage2_k<<<(int) ((n + 31) / 32), dim3(32, 8), 0, st>>>(pr, pi, dr, di, chunks, n, accumulate);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage2");

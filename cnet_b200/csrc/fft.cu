@@ -134,8 +134,10 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                         sh[k] = __uint_as_float(__float_as_uint(gi[k]) & 0xFFFFE000u); sl[k] = gi[k] - sh[k];
                     }
                     const size_t o = (size_t) row * N + e;
-                    *reinterpret_cast<float4*>(ep.gr + o) = make_float4(gr[0], gr[1], gr[2], gr[3]);
-                    *reinterpret_cast<float4*>(ep.gi + o) = make_float4(gi[0], gi[1], gi[2], gi[3]);
+                    if (ep.gr) {
+                        *reinterpret_cast<float4*>(ep.gr + o) = make_float4(gr[0], gr[1], gr[2], gr[3]);
+                        *reinterpret_cast<float4*>(ep.gi + o) = make_float4(gi[0], gi[1], gi[2], gi[3]);
+                    }
                     if (ep.sp) {
                         *reinterpret_cast<float4*>(ep.sp + o) = make_float4(rh[0], rh[1], rh[2], rh[3]);
                         *reinterpret_cast<float4*>(ep.sp + ep.np + o) = make_float4(sh[0], sh[1], sh[2], sh[3]);

@@ -164,8 +164,7 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
                 const float hr = __ldg(ep.hr + e + t), hi = __ldg(ep.hi + e + t);
                 const float gr = cnb_gelu(re[p] * hr - im[p] * hi);
                 const float gi = cnb_gelu(re[p] * hi + im[p] * hr);
-                ep.gr[o + e] = gr;
-                ep.gi[o + e] = gi;
+                if (ep.gr) { ep.gr[o + e] = gr; ep.gi[o + e] = gi; }
                 if (ep.sp) {
                     const float rh = __uint_as_float(__float_as_uint(gr) & 0xFFFFE000u);
                     const float sh = __uint_as_float(__float_as_uint(gi) & 0xFFFFE000u);

@@ -46,7 +46,7 @@ __device__ __forceinline__ void fft_regs(float (&re)[R], float (&im)[R]) {
 struct FftEpilogue {
     const float* hr = nullptr;      // h planes [N]; NULL = plain transform
     const float* hi = nullptr;
-    float* gr = nullptr;            // gelu(u o h) planes [B, N]
+    float* gr = nullptr;            // gelu(u o h) planes [B, N]; may be NULL when sp is given (hi + lo is the value)
     float* gi = nullptr;
     float* sp = nullptr;            // hi/lo split of that (4 planes of np floats) or NULL
     size_t np = 0;

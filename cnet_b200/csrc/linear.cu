@@ -241,8 +241,9 @@ int cnb_dft_fused_ok(int N) { return cnb::fft_supported(N) ? 1 : 0; }
 int cnb_dft_hadamard_gelu_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im, const float* h_re,
                               const float* h_im, float* u_re, float* u_im, float* y_re, float* y_im, float* y_split,
                               int B, int N, void* stream) {
-    CNB_CHECK_ARG(ctx && x_re && x_im && h_re && h_im && u_re && u_im && y_re && y_im,
-                  "cnb_dft_hadamard_gelu_fwd: null pointer");
+    CNB_CHECK_ARG(ctx && x_re && x_im && h_re && h_im && u_re && u_im, "cnb_dft_hadamard_gelu_fwd: null pointer");
+    CNB_CHECK_ARG((y_re == nullptr) == (y_im == nullptr) && (y_re || y_split),
+                  "cnb_dft_hadamard_gelu_fwd: y planes must be a pair, and may only be left out when y_split is given");
     CNB_CHECK_ARG(B > 0 && cnb::fft_supported(N), "cnb_dft_hadamard_gelu_fwd: B=%d, N=%d is not an FFT-kernel length", B, N);
     cnb::g_last_engine = 3;
     return cnb::fft_hadamard_gelu(ctx, x_re, x_im, h_re, h_im, u_re, u_im, y_re, y_im, y_split, B, N, cnb::S(stream));

@@ -146,8 +146,11 @@ void FourierTrans::forward() {
 	if (fused_hg_) {
 		const Vars& h = fused_hg_->previous(1)->output();
 		Vars& y = fused_hg_->fused_gelu_->out_;
-		check(cnb_dft_hadamard_gelu_fwd(ctx(), x.real_, x.imag_, h.real_, h.imag_, out_.real_, out_.imag_, y.real_,
-				y.imag_, fused_hg_->consumerSplit(), batch(), in_size_, stream()));
+		// the only reader of y is the Linear that takes the split planes: y itself is not stored a second time
+		float* ysplit = fused_hg_->consumerSplit();
+		fused_hg_->fused_gelu_->value_split_ = ysplit;
+		check(cnb_dft_hadamard_gelu_fwd(ctx(), x.real_, x.imag_, h.real_, h.imag_, out_.real_, out_.imag_,
+				ysplit ? nullptr : y.real_, ysplit ? nullptr : y.imag_, ysplit, batch(), in_size_, stream()));
 		return;
 	}
 	check(cnb_dft_fwd(ctx(), x.real_, x.imag_, out_.real_, out_.imag_, batch(), in_size_, stream()));
@@ -1152,6 +1155,19 @@ bool CNet::readOutput(int uid, int what, float* re, float* im) {
 	if (what != 0 && f->grad_transient_) sr = nullptr;       // overwritten by the gradient of the Residual's operand
 	if (!sr) { fail(CNB_ERR_ARG, f->getName() + ": tensor not materialised (fused)"); return false; }
 	size_t n = (size_t) (f->batched_ ? cur_batch_ : 1) * f->out_size_;
+	if (what == 0 && f->value_split_) {                       // hi + lo is the value, exactly
+		const size_t np = cnb_split_floats((size_t) cur_batch_ * f->out_size_) / 4;   // plane pitch of the batch in flight
+		std::vector<float> lo(n);
+		for (int q = 0; q < 2; ++q) {
+			float* dst = q ? im : re;
+			int rc = cnb_d2h(ctx_, dst, f->value_split_ + q * np, n * sizeof(float), stream_);
+			if (rc == CNB_OK) rc = cnb_d2h(ctx_, lo.data(), f->value_split_ + (2 + q) * np, n * sizeof(float), stream_);
+			if (rc == CNB_OK) rc = cnb_sync(ctx_, stream_);
+			if (rc != CNB_OK) { fail(rc, "readOutput"); return false; }
+			for (size_t k = 0; k < n; ++k) dst[k] += lo[k];
+		}
+		return true;
+	}
 	int rc = cnb_d2h(ctx_, re, sr, n * sizeof(float), stream_);
 	if (rc == CNB_OK) rc = cnb_d2h(ctx_, im, si, n * sizeof(float), stream_);
 	if (rc != CNB_OK) { fail(rc, "readOutput"); return false; }

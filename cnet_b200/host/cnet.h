@@ -141,6 +141,7 @@ public:
 	Vars out_;
 	bool batched_ = true;        // false: one row shared by the batch (weights)
 	bool grad_written_ = false;  // has a consumer already written dL/dz* of out_ in this backward?
+	const float* value_split_ = nullptr; // value planes are not stored: out = hi + lo of these 4 split planes
 	bool grad_transient_ = false; // dL/dz* planes are shared with a Residual operand and accumulated over in place
 	bool fused_away_ = false;    // a neighbour's fused kernel does this layer's work
 

@@ -137,8 +137,9 @@ int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                 float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
 /* FourierTrans -> Hadamard(shared h) -> CGelu in one pass over the row (N = 256, 1024, 4096, see
  * cnb_dft_fused_ok): u = DFT(x) is kept for the backward, y = gelu(u o h), optionally with the
- * hi/lo split planes of y for the Linear that follows.  The Hadamard product a = u o h is not
- * stored: cnb_hadamard_gelu_bwd recomputes it when a_re == NULL.  Same reference kernels as
+ * hi/lo split planes of y for the Linear that follows; y_re = y_im = NULL is allowed when y_split
+ * is given (hi + lo is y exactly, so a caller that only feeds the Linear need not store y twice).
+ * The Hadamard product a = u o h is not stored: cnb_hadamard_gelu_bwd recomputes it when a_re == NULL.  Same reference kernels as
  * cnb_dft_fwd + cnb_hadamard_gelu_fwd. */
 int cnb_dft_fused_ok(int N);
 int cnb_dft_hadamard_gelu_fwd(cnb_ctx* ctx, const float* x_re, const float* x_im,
