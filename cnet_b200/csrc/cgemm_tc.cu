@@ -51,6 +51,7 @@ struct TcParams {
     int M, N, K, conjB, accumulate;
     int units_per_cta;        // consecutive (tile, k-block) work units per CTA (stream-K)
     int a_mn, b_mn;           // operand stored [K, rows] (MN-major) instead of [rows, K] (K-major)
+    int cluster;              // > 1: that many CTAs of one cluster share a tile, each a slice of K
     int* status;
 };
 
@@ -173,6 +174,32 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;"
 // by the row so that both the row-per-thread writes and the row-segment reads are conflict-free.
 __device__ __forceinline__ int stage_off(int row, int chunk) { return row * 32 + ((chunk ^ (row & 7)) << 2); }
 
+// Partial tile of one CTA in cluster mode: 128 rows x 128 floats per plane over the (then idle) operand
+// stages, 16-byte chunks XOR-swizzled by the row like the staging tile.
+__device__ __forceinline__ int part_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 2); }
+constexpr int PART_PLANE_BYTES = 128 * 128 * 4;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// all threads of all CTAs of the cluster; orders shared-memory writes before the peers' reads
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float4 ld_peer(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
            const __grid_constant__ CUtensorMap a_lo_re, const __grid_constant__ CUtensorMap a_lo_im,
@@ -194,8 +221,14 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     const int tiles_m = (p.M + BM - 1) / BM;
     const int k_blocks = (p.K + BK - 1) / BK;
     const long total_units = (long) tiles_m * tiles_n * k_blocks;
-    const long u_begin = (long) blockIdx.x * p.units_per_cta;
-    const long u_end = min(total_units, u_begin + p.units_per_cta);
+    long u_begin = (long) blockIdx.x * p.units_per_cta;
+    long u_end = min(total_units, u_begin + p.units_per_cta);
+    const uint32_t crank = p.cluster > 1 ? cluster_rank() : 0;
+    if (p.cluster > 1) {                                 // one tile per cluster, an even slice of its k-blocks per CTA
+        const long tile = blockIdx.x / p.cluster;
+        u_begin = tile * k_blocks + (long) k_blocks * crank / p.cluster;
+        u_end = tile * k_blocks + (long) k_blocks * (crank + 1) / p.cluster;
+    }
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_base = smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -302,6 +335,36 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             ((reinterpret_cast<uintptr_t>(p.d_re) | reinterpret_cast<uintptr_t>(p.d_im) |
               reinterpret_cast<uintptr_t>(p.r_re) | reinterpret_cast<uintptr_t>(p.r_im)) & 15) == 0;
         int seg = 0;
+        if (p.cluster > 1) {
+            // the whole k-slice is one segment; its partial sums go to shared memory for the cluster reduction
+            mbar_wait(acc_full, 0u, abort_flag, p.status, 3);
+            epi_bar_sync();
+            if (!*abort_flag) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float* part_re = reinterpret_cast<float*>(smem);
+                float* part_im = part_re + 128 * 128;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float a[16], f[16], b[16], e[16];
+                    tmem_ld16(tl + c0, a);                   // A_re.B_re
+                    tmem_ld16(tl + 384 + c0, f);             // A_im.B_im
+                    tmem_ld16(tl + 128 + c0, b);             // A_re.B_im
+                    tmem_ld16(tl + 256 + c0, e);             // A_im.B_re
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4) {
+                        const int o = part_off(row, (c0 + i) >> 2);
+                        *reinterpret_cast<float4*>(part_re + o) =
+                            make_float4(a[i] + sgn * f[i], a[i + 1] + sgn * f[i + 1], a[i + 2] + sgn * f[i + 2],
+                                        a[i + 3] + sgn * f[i + 3]);
+                        *reinterpret_cast<float4*>(part_im + o) =
+                            make_float4(e[i] - sgn * b[i], e[i + 1] - sgn * b[i + 1], e[i + 2] - sgn * b[i + 2],
+                                        e[i + 3] - sgn * b[i + 3]);
+                    }
+                }
+            }
+            u_end = u_begin;                             // nothing left for the stream-K loop below
+        }
         for (long u = u_begin; u < u_end; ++seg) {
             int tile = (int) (u / k_blocks), kb0 = (int) (u % k_blocks);
             int kb1 = (int) min((long) k_blocks, kb0 + (u_end - u));
@@ -396,6 +459,55 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
+    if (p.cluster > 1) {
+        // Every thread of every CTA of the cluster reaches both barriers, also after a bounded wait gave up.
+        cluster_sync();                                  // all partial tiles are in shared memory
+        if (warp >= 2 && !*abort_flag) {
+            const int tile = blockIdx.x / p.cluster;
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int rows_per = BM / p.cluster;         // this CTA sums and writes out its band of rows
+            const int et = (warp - 2) * 32 + lane;
+            const bool vec_ok = (p.N % 4 == 0) &&
+                ((reinterpret_cast<uintptr_t>(p.d_re) | reinterpret_cast<uintptr_t>(p.d_im) |
+                  reinterpret_cast<uintptr_t>(p.r_re) | reinterpret_cast<uintptr_t>(p.r_im)) & 15) == 0;
+            for (int idx = et; idx < rows_per * 32; idx += 128) {
+                const int r = (int) crank * rows_per + (idx >> 5), ch = idx & 31;
+                const int gm = m0 + r, gn = n0 + ch * 4;
+                if (gm >= p.M || gn >= p.N) continue;
+                const uint32_t local = smem_base + 4u * (uint32_t) part_off(r, ch);
+                float4 vr = make_float4(0.f, 0.f, 0.f, 0.f), vi = vr;
+                for (int c = 0; c < p.cluster; ++c) {    // fixed order: the sum does not depend on timing
+                    const float4 xr = ld_peer(local, (uint32_t) c), xi = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c);
+                    vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
+                    vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                }
+                const size_t o = (size_t) gm * p.N + gn;
+                if (vec_ok) {
+                    if (p.r_re) {
+                        const float4 xr = *reinterpret_cast<const float4*>(p.r_re + o), xi = *reinterpret_cast<const float4*>(p.r_im + o);
+                        vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
+                        vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                    }
+                    if (p.accumulate) {
+                        const float4 xr = *reinterpret_cast<const float4*>(p.d_re + o), xi = *reinterpret_cast<const float4*>(p.d_im + o);
+                        vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
+                        vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                    }
+                    *reinterpret_cast<float4*>(p.d_re + o) = vr;
+                    *reinterpret_cast<float4*>(p.d_im + o) = vi;
+                } else {
+                    const float wr[4] = {vr.x, vr.y, vr.z, vr.w}, wi[4] = {vi.x, vi.y, vi.z, vi.w};
+                    for (int k = 0; k < 4 && gn + k < p.N; ++k) {
+                        float xr = wr[k], xi = wi[k];
+                        if (p.r_re) { xr += p.r_re[o + k]; xi += p.r_im[o + k]; }
+                        if (p.accumulate) { xr += p.d_re[o + k]; xi += p.d_im[o + k]; }
+                        p.d_re[o + k] = xr; p.d_im[o + k] = xi;
+                    }
+                }
+            }
+        }
+        cluster_sync();                                  // no CTA leaves while a peer still reads its shared memory
+    }
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -577,7 +689,16 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     long upc = (total + ctas - 1) / ctas;
     if (whole_tiles) upc = k_blocks;
     ctas = (total + upc - 1) / upc;
-    bool splits_tiles = (upc % k_blocks) != 0;
+    // Few tiles (small batches): a cluster of 2, 4 or 8 CTAs takes one tile, every CTA a slice of K, and
+    // the partial tiles are summed through distributed shared memory: no atomics, no cleared output,
+    // a fixed summation order.
+    int cluster = 1;
+    if (!whole_tiles) {
+        for (int c = 8; c >= 2; c >>= 1)
+            if ((long) tiles * c <= sms && k_blocks / c >= 4) { cluster = c; break; }
+    }
+    if (cluster > 1) { ctas = (long) tiles * cluster; upc = 0; }
+    bool splits_tiles = cluster == 1 && (upc % k_blocks) != 0;
     if (splits_tiles && !accumulate) {
         // one launch clears both planes (they need not be adjacent or in one allocation)
         const size_t plane = (size_t) M * N;
@@ -591,9 +712,27 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     p.M = M; p.N = N; p.K = K; p.conjB = conjB; p.accumulate = accumulate;
     p.units_per_cta = (int) upc;
     p.a_mn = a_mn; p.b_mn = b_mn;
+    p.cluster = cluster;
     p.status = ctx->d_status;
-    cgemm_tc_k<<<(int) ctas, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
-                                                           maps[7], p);
+    if (cluster > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) ctas);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned) cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CNB_CUDA(cudaLaunchKernelEx(&cfg, cgemm_tc_k, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
+                                    maps[7], p));
+    } else {
+        cgemm_tc_k<<<(int) ctas, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                                                               maps[6], maps[7], p);
+    }
     CNB_LAUNCH_CHECK("cgemm_tc");
     return CNB_OK;
 }
