@@ -262,10 +262,15 @@ int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, 
 #undef CNB_SKINNY_ATTR
         smem_set = smem;
     }
-    const long blocks = ((B + 1) / 2 + 15) / 16;         // 16 warps per CTA, 2 rows per warp and pass
+    // 2 rows per warp and pass; small batches take thinner CTAs so that the rows still spread over the SMs
+    const long pairs = (B + 1) / 2;
+    int warps = 16;
+    while (warps > 4 && pairs < (long) ctx->sm_count * warps) warps /= 2;
+    const long blocks = (pairs + warps - 1) / warps;
     const int grid = (int) std::max<long>(1, std::min<long>(blocks, ctx->sm_count));
-    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, <<<grid, 512, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
-    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, <<<grid, 512, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
+    const int threads = warps * 32;
+    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, <<<grid, threads, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
+    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, <<<grid, threads, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
     CNB_LAUNCH_CHECK("skinny_fwd");
     return CNB_OK;
 }

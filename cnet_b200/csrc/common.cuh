@@ -23,6 +23,8 @@ struct cnb_ctx {
     size_t used = 0;
     bool owns = false;
     int* d_status = nullptr;          // device error word (bounded waits report here)
+    int* d_counters = nullptr;        // 8 sets of 64 "CTAs done" counters, zero between launches
+    unsigned counter_set = 0;
     float* scratch = nullptr;         // column-reduction partials and GEMM operand staging
     size_t scratch_bytes = 0;
     std::map<int, cnb_twiddle> twiddles;

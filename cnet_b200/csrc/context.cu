@@ -69,10 +69,11 @@ static int create_common(int device, void* arena, size_t bytes, bool owns, cnb_c
     c->size = bytes;
     cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
     void* st = nullptr;
-    int rc = cnb_alloc(c, 256, &st);
+    int rc = cnb_alloc(c, 4096, &st);                    // error word, then the completion counters of reductions
     if (rc != CNB_OK) { cnb_destroy(c); return rc; }
     c->d_status = static_cast<int*>(st);
-    cudaMemset(c->d_status, 0, 256);
+    c->d_counters = c->d_status + 256;
+    cudaMemset(c->d_status, 0, 4096);
     *out = c;
     return CNB_OK;
 }
@@ -106,7 +107,7 @@ int cnb_alloc(cnb_ctx* ctx, size_t bytes, void** out) {
 
 int cnb_reset(cnb_ctx* ctx) {
     CNB_CHECK_ARG(ctx, "cnb_reset: null context");
-    ctx->used = 256;            // keep the status word
+    ctx->used = 4096;           // keep the status word and the counters
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
     ctx->twiddles.clear();

@@ -98,8 +98,10 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
                    const float* __restrict__ hr, const float* __restrict__ hi,
                    float* __restrict__ dur, float* __restrict__ dui, int accumulate_u,
                    float* __restrict__ pr, float* __restrict__ pi,
-                   int B, int N, int rows_per_chunk) {
+                   int B, int N, int rows_per_chunk,
+                   int* __restrict__ done, float* __restrict__ dvr, float* __restrict__ dvi, int accumulate_v) {
     __shared__ float sr[8][32 * W + 1], si[8][32 * W + 1];
+    __shared__ int s_last;
     const int col = (blockIdx.x * 32 + threadIdx.x) * W;
     const int r0 = blockIdx.y * rows_per_chunk;
     const int r1 = min(B, r0 + rows_per_chunk);
@@ -160,6 +162,37 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
             pi[(size_t) blockIdx.y * N + c] = d;
         }
     }
+    if (!done) return;                                   // a second launch sums the partial rows
+    // The CTA that finishes last among those of this column block sums the partial rows, always in
+    // chunk order (deterministic); nobody waits for anybody.
+    __threadfence();
+    __syncthreads();
+    if (t == 0) s_last = atomicAdd(done + blockIdx.x, 1) == (int) gridDim.y - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int chunks = gridDim.y;
+    {
+        const int cx = t % (32 * W), lane8 = t / (32 * W);        // W = 4: 128 columns x 2 lanes; W = 1: 32 x 8
+        constexpr int LANES = 256 / (32 * W);
+        const int c = blockIdx.x * 32 * W + cx;
+        float a = 0.f, d = 0.f;
+        if (c < N)
+            for (int k = lane8; k < chunks; k += LANES) {
+                a += __ldcg(pr + (size_t) k * N + c);
+                d += __ldcg(pi + (size_t) k * N + c);
+            }
+        sr[lane8][cx] = a;
+        si[lane8][cx] = d;
+        __syncthreads();
+        if (lane8 == 0 && c < N) {
+#pragma unroll
+            for (int k = 1; k < LANES; ++k) { a += sr[k][cx]; d += si[k][cx]; }
+            if (accumulate_v) { a += dvr[c]; d += dvi[c]; }
+            dvr[c] = a; dvi[c] = d;
+        }
+    }
+    if (t == 0) done[blockIdx.x] = 0;                    // ready for the next launch
 }
 
 // Stage 2: dv[n] (+)= sum_c partial[c][n], always in the same order (deterministic).
@@ -315,6 +348,41 @@ __global__ void sgd_k(float* __restrict__ w, float* __restrict__ g, size_t total
     }
 }
 
+// The update with the hi/lo TF32 split of the new values written in the same pass for the spans of the
+// arena that are Linear weights (span begins and lengths are multiples of 4 floats).
+struct SplitSpans {
+    size_t begin[CNB_MAX_SPLIT_SPANS];
+    size_t count[CNB_MAX_SPLIT_SPANS];
+    float* hi[CNB_MAX_SPLIT_SPANS];
+    float* lo[CNB_MAX_SPLIT_SPANS];
+    int n;
+};
+
+__global__ void sgd_split_k(float* __restrict__ w, float* __restrict__ g, size_t total, float lr, int zero_grad,
+                            const SplitSpans sp) {
+    size_t stride = (size_t) gridDim.x * blockDim.x * 4;
+    for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += stride) {
+        Pack<4> a = ld<4>(w, i), b = ld<4>(g, i);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { a.v[k] -= lr * b.v[k]; b.v[k] = 0.f; }
+        st<4>(w, i, a);
+        if (zero_grad) st<4>(g, i, b);
+        for (int s = 0; s < sp.n; ++s) {
+            if (i >= sp.begin[s] && i < sp.begin[s] + sp.count[s]) {
+                Pack<4> h, l;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    h.v[k] = __uint_as_float(__float_as_uint(a.v[k]) & 0xFFFFE000u);
+                    l.v[k] = a.v[k] - h.v[k];
+                }
+                st<4>(sp.hi[s], i - sp.begin[s], h);
+                st<4>(sp.lo[s], i - sp.begin[s], l);
+                break;
+            }
+        }
+    }
+}
+
 template <typename... P> bool all_aligned(P... p) { return (aligned16(p) && ...); }
 
 int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, const float* ar, const float* ai,
@@ -349,13 +417,17 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
     float* pr = part;
     float* pi = part + (size_t) chunks * N;
     dim3 grid(col_blocks, chunks), block(32, 8);
-#define CNB_COLREDUCE(MODE, W) colreduce_stage1_k<MODE, W><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows)
+    // up to 64 column blocks: the last CTA of each column block finishes the sum in the same launch
+    int* done = (col_blocks <= 64 && ctx->d_counters) ? ctx->d_counters + 64 * (ctx->counter_set++ & 7) : nullptr;
+#define CNB_COLREDUCE(MODE, W) colreduce_stage1_k<MODE, W><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows, done, dvr, dvi, acc_v)
     if (mode == 0) { if (vec) CNB_COLREDUCE(0, 4); else CNB_COLREDUCE(0, 1); }
     else { if (vec) CNB_COLREDUCE(1, 4); else CNB_COLREDUCE(1, 1); }
 #undef CNB_COLREDUCE
     CNB_LAUNCH_CHECK("colreduce_stage1");
-    colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
-    CNB_LAUNCH_CHECK("colreduce_stage2");
+    if (!done) {
+        colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
+        CNB_LAUNCH_CHECK("colreduce_stage2");
+    }
     return CNB_OK;
 }
 
@@ -523,6 +595,26 @@ int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zer
     return CNB_OK;
 }
 
+int cnb_sgd_update_split(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
+                         const cnb_split_span* spans, int nspans, void* stream) {
+    CNB_CHECK_ARG(ctx && w && g && n > 0 && n % 4 == 0 && all_aligned(w, g), "cnb_sgd_update_split: bad argument");
+    CNB_CHECK_ARG(nspans >= 0 && nspans <= CNB_MAX_SPLIT_SPANS && (nspans == 0 || spans),
+                  "cnb_sgd_update_split: %d spans (at most %d)", nspans, CNB_MAX_SPLIT_SPANS);
+    SplitSpans sp;
+    sp.n = nspans;
+    for (int k = 0; k < nspans; ++k) {
+        CNB_CHECK_ARG(spans[k].begin % 4 == 0 && spans[k].count % 4 == 0 && spans[k].begin + spans[k].count <= n &&
+                      all_aligned(spans[k].hi, spans[k].lo) && spans[k].hi && spans[k].lo,
+                      "cnb_sgd_update_split: span %d is not a 16-byte aligned range of the arena", k);
+        sp.begin[k] = spans[k].begin; sp.count[k] = spans[k].count; sp.hi[k] = spans[k].hi; sp.lo[k] = spans[k].lo;
+    }
+    cudaStream_t stm = cnb::S(stream);
+    size_t blocks = (n / 4 + 255) / 256, cap = (size_t) ctx->sm_count * 16;
+    sgd_split_k<<<(int) std::min(blocks, cap), 256, 0, stm>>>(w, g, n, lr, zero_grad, sp);
+    CNB_LAUNCH_CHECK("sgd_split");
+    return CNB_OK;
+}
+
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------
@@ -607,7 +699,7 @@ extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, con
     float* pi = sc.ptr + (size_t) kStaticMaxChunks * kStaticMaxN;
     dim3 grid(col_blocks, chunks), block(32, 8);
     colreduce_stage1_k<0, 1><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
-                                                      nullptr, nullptr, 0, pr, pi, B, N, rows);
+                                                      nullptr, nullptr, 0, pr, pi, B, N, rows, nullptr, nullptr, nullptr, 0);
     CNB_LAUNCH_CHECK("colreduce_stage1");
     colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dv_re, dv_im, accumulate_v, chunks, N);
     CNB_LAUNCH_CHECK("colreduce_stage2");

@@ -1065,12 +1065,28 @@ void CNet::updateInputs(float lr) {
 	if (!ctx_ || !wgrad_count_) return;
 	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, 0);
 	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
-	int rc = cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_);
+	// the new Linear weights leave the update already split, once, for the next forward and dX* products
+	std::vector<cnb_split_span> spans;
+	std::vector<Linear*> fused;
+	for (auto f : func_list_) {
+		Linear* l = dynamic_cast<Linear*>(f);
+		if (!l || !l->use_split_ || spans.size() + 2 > CNB_MAX_SPLIT_SPANS || wgrad_count_ % 4) continue;
+		const Vars& w = l->prev_func_[1]->out_;
+		const size_t np = cnb_split_floats((size_t) l->in2_len) / 4;
+		if (l->in2_len % 4 || w.real_ < weight_base_ || w.imag_ + l->in2_len > weight_base_ + wgrad_count_) continue;
+		spans.push_back({(size_t) (w.real_ - weight_base_), (size_t) l->in2_len, l->w_split_, l->w_split_ + 2 * np});
+		spans.push_back({(size_t) (w.imag_ - weight_base_), (size_t) l->in2_len, l->w_split_ + np, l->w_split_ + 3 * np});
+		fused.push_back(l);
+	}
+	int rc = spans.empty()
+		? cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_)
+		: cnb_sgd_update_split(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, spans.data(), (int) spans.size(), stream_);
 	if (rc != CNB_OK) { fail(rc, "updateInputs"); return; }
-	// the new weights are split here, once, for the next forward and dX* products
 	++weights_version_;
+	for (auto l : fused) l->w_split_version_ = weights_version_;
 	for (auto f : func_list_)
-		if (Linear* l = dynamic_cast<Linear*>(f)) l->splitWeights();
+		if (Linear* l = dynamic_cast<Linear*>(f))
+			if (l->w_split_version_ != weights_version_) l->splitWeights();
 }
 
 void CNet::adamUpdate(float lr, float beta, int t) {

@@ -19,6 +19,11 @@ BUCKET_HOOK = C.CFUNCTYPE(C.c_int, _vp, _vp, _sz, C.c_int, C.c_int)
 # name -> (restype, argtypes); the complete export list of include/cnet_b200.h and
 # include/cnet_b200_host.h (tests check that every declared symbol is here and exported)
 _P = _vp   # device or host pointer passed as an integer address
+class SplitSpan(C.Structure):
+    """cnb_split_span of include/cnet_b200.h."""
+    _fields_ = [("begin", C.c_size_t), ("count", C.c_size_t), ("hi", C.c_void_p), ("lo", C.c_void_p)]
+
+
 SIGNATURES = {
     "cnb_last_error": (C.c_char_p, []),
     "cnb_create": (C.c_int, [C.c_int, _sz, C.POINTER(_vp)]),
@@ -74,6 +79,7 @@ SIGNATURES = {
     "cnb_embed_fwd": (C.c_int, [_vp] + [_P] * 5 + [C.c_int] * 4 + [_vp]),
     "cnb_embed_bwd": (C.c_int, [_vp] + [_P] * 5 + [C.c_int] * 4 + [_vp]),
     "cnb_sgd_update": (C.c_int, [_vp, _P, _P, _sz, C.c_float, C.c_int, _vp]),
+    "cnb_sgd_update_split": (C.c_int, [_vp, _P, _P, _sz, C.c_float, C.c_int, _vp, C.c_int, _vp]),
     "cnb_launch_count": (C.c_ulonglong, []),
     # host facade
     "cnh_create": (_vp, [C.c_int, _sz, _P]),

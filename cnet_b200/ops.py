@@ -209,6 +209,14 @@ class Context:
                                           B, T, D, V, self._stream()), "embed_bwd")
         return dtable
 
+    def sgd_update_split(self, w, g, lr, spans, zero_grad=True):
+        """spans: [(begin, count, hi_tensor, lo_tensor)]; the updated floats of each span also leave their split."""
+        arr = (_lib.SplitSpan * len(spans))()
+        for k, (begin, count, hi, lo) in enumerate(spans):
+            arr[k].begin, arr[k].count, arr[k].hi, arr[k].lo = begin, count, hi.data_ptr(), lo.data_ptr()
+        _lib.check(self.lib.cnb_sgd_update_split(self.h, _p(w), _p(g), w.numel(), lr, int(zero_grad), arr, len(spans),
+                                                 self._stream()), "sgd_update_split")
+
     def sgd_update(self, w, g, lr, zero_grad=True):
         _lib.check(self.lib.cnb_sgd_update(self.h, _p(w), _p(g), w.numel(), lr, int(zero_grad), self._stream()),
                    "sgd_update")

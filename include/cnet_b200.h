@@ -285,6 +285,14 @@ int cnb_embed_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
  * CPU: impl/cfunc.h:147-152 + impl/cnet.h:413-421. */
 int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
                    void* stream);
+/* The same update; the floats of [begin, begin + count) of every span (the planes of Linear weights)
+ * also leave their hi/lo TF32 split in hi[i - begin], lo[i - begin], so the products of the next step
+ * need no split pass over the weights.  n, begins and counts are multiples of 4; at most
+ * CNB_MAX_SPLIT_SPANS spans.  Same reference call site as cnb_sgd_update. */
+#define CNB_MAX_SPLIT_SPANS 48
+typedef struct cnb_split_span { size_t begin; size_t count; float* hi; float* lo; } cnb_split_span;
+int cnb_sgd_update_split(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
+                         const cnb_split_span* spans, int nspans, void* stream);
 
 /* The reference's momentum-only "Adam": m = beta m + (1 - beta) g; w -= lr m / (1 - beta^(t+1));
  * g = 0.  Replaces gpu_update_adam_input (gpu/kernels.h:77, gpu/kernels.cpp:494-525).

@@ -190,6 +190,26 @@ def test_sgd_update(ctx):
         assert float(G.abs().max()) == 0.0
 
 
+def test_sgd_update_with_weight_split(ctx):
+    """The fused update leaves hi + lo == the new weight exactly, hi a TF32 value, only inside the spans."""
+    import torch
+    rng = np.random.default_rng(6)
+    n = 1 << 16
+    w = rng.standard_normal(n).astype(np.float32)
+    g = rng.standard_normal(n).astype(np.float32)
+    W, G = torch.from_numpy(w).cuda(), torch.from_numpy(g).cuda()
+    spans = [(256, 4096), (8192, 1 << 15)]
+    outs = [(torch.full((c,), 7.0, device="cuda"), torch.full((c,), 7.0, device="cuda")) for _, c in spans]
+    ctx.sgd_update_split(W, G, 0.25, [(b, c, hi, lo) for (b, c), (hi, lo) in zip(spans, outs)])
+    want = w - np.float32(0.25) * g
+    assert np.array_equal(W.cpu().numpy(), want)
+    assert float(G.abs().max()) == 0.0
+    for (b, c), (hi, lo) in zip(spans, outs):
+        h, l = hi.cpu().numpy(), lo.cpu().numpy()
+        assert np.array_equal(h + l, want[b:b + c])
+        assert not np.any(h.view(np.uint32) & np.uint32(0x1FFF))
+
+
 def test_bad_arguments_are_rejected_not_fatal(ctx):
     import ctypes as C
     from cnet_b200 import lib
