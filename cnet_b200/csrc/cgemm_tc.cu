@@ -683,7 +683,14 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     long min_units = 8;                                  // do not split below 8 k-blocks per CTA
     // leaving a few SMs free (gemm_cta_limit) lets a concurrent collective's kernels run beside the GEMM
     const int sms = ctx->gemm_cta_limit > 0 ? std::min(ctx->gemm_cta_limit, ctx->sm_count) : ctx->sm_count;
-    const bool whole_tiles = tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0;
+    // Whole tiles (plain stores: no atomics, no cleared output, a fixed summation order) when there are
+    // many tiles, or when D is not read and the waves of one-tile CTAs are at least 85 % full; a grid
+    // capped for a concurrent collective only when one wave holds all tiles.
+    const int waves = (tiles + sms - 1) / sms;
+    // (not for K > 4096: one fp32 accumulation chain in tensor memory that long costs accuracy)
+    const bool full_waves = !accumulate && (long) tiles * 100 >= (long) waves * sms * 85 && k_blocks <= 256 &&
+                            (ctx->gemm_cta_limit <= 0 || tiles <= sms);
+    const bool whole_tiles = (tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0) || full_waves;
     long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
     if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
     long upc = (total + ctas - 1) / ctas;
