@@ -699,8 +699,10 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     // Few tiles (small batches): a cluster of 2, 4 or 8 CTAs takes one tile, every CTA a slice of K, and
     // the partial tiles are summed through distributed shared memory: no atomics, no cleared output,
     // a fixed summation order.
+    // Worth it while a stream-K run would be short (<= 48 k-blocks): with long runs the atomics are
+    // amortised and using every SM wins over the clusters' rounded-down CTA count.
     int cluster = 1;
-    if (!whole_tiles) {
+    if (!whole_tiles && upc <= 48) {
         for (int c = 8; c >= 2; c >>= 1)
             if ((long) tiles * c <= sms && k_blocks / c >= 4) { cluster = c; break; }
     }
