@@ -265,7 +265,7 @@ int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, 
     // 2 rows per warp and pass; small batches take thinner CTAs so that the rows still spread over the SMs
     const long pairs = (B + 1) / 2;
     int warps = 16;
-    while (warps > 4 && pairs < (long) ctx->sm_count * warps) warps /= 2;
+    while (warps > 4 && pairs < (long) ctx->sm_count * warps / 2) warps /= 2;
     const long blocks = (pairs + warps - 1) / warps;
     const int grid = (int) std::max<long>(1, std::min<long>(blocks, ctx->sm_count));
     const int threads = warps * 32;
