@@ -52,6 +52,7 @@ struct TcParams {
     int units_per_cta;        // consecutive (tile, k-block) work units per CTA (stream-K)
     int a_mn, b_mn;           // operand stored [K, rows] (MN-major) instead of [rows, K] (K-major)
     int cluster;              // > 1: that many CTAs of one cluster share a tile, each a slice of K
+    int whole_per_cta;        // > 0: every CTA first takes that many whole tiles, then its run of the remaining units
     int* status;
 };
 
@@ -221,8 +222,18 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     const int tiles_m = (p.M + BM - 1) / BM;
     const int k_blocks = (p.K + BK - 1) / BK;
     const long total_units = (long) tiles_m * tiles_n * k_blocks;
+    // up to two consecutive runs of (tile, k-block) units per CTA
     long u_begin = (long) blockIdx.x * p.units_per_cta;
     long u_end = min(total_units, u_begin + p.units_per_cta);
+    long u2_begin = 0, u2_end = 0;
+    if (p.whole_per_cta > 0) {
+        const long lead = (long) p.whole_per_cta * k_blocks;             // whole tiles first ...
+        const long rest0 = lead * gridDim.x;                              // ... then a share of what is left
+        u2_begin = min(total_units, rest0 + (long) blockIdx.x * p.units_per_cta);
+        u2_end = min(total_units, u2_begin + p.units_per_cta);
+        u_begin = lead * blockIdx.x;
+        u_end = u_begin + lead;
+    }
     const uint32_t crank = p.cluster > 1 ? cluster_rank() : 0;
     if (p.cluster > 1) {                                 // one tile per cluster, an even slice of its k-blocks per CTA
         const long tile = blockIdx.x / p.cluster;
@@ -258,12 +269,14 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         if (lane == 0) {
             const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_lo_re, &a_lo_im, &b_hi_re, &b_hi_im, &b_lo_re, &b_lo_im};
             long it = 0;
-            for (long u = u_begin; u < u_end; ++u, ++it) {
+            bool live = true;
+            for (int pass = 0; pass < 2 && live; ++pass)
+            for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue; ++u, ++it) {
                 int tile = (int) (u / k_blocks), kb = (int) (u % k_blocks);
                 int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
                 int s = (int) (it % STAGES);
                 uint32_t phase = (uint32_t) (it / STAGES) & 1;
-                if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, 1)) break;
+                if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, 1)) { live = false; break; }
                 mbar_expect_tx(full_bar(s), STAGE_BYTES);
                 uint32_t dst = smem_base + s * STAGE_BYTES;
 #pragma unroll
@@ -282,9 +295,10 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             int seg = 0;
             // bits 15 / 16 of the instruction descriptor: operand A / B is MN-major
             const uint32_t idesc = kInstrDesc | (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
-            for (long u = u_begin; u < u_end && ok; ++seg) {
+            for (int pass = 0; pass < 2; ++pass)
+            for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue && ok; ++seg) {
                 int kb0 = (int) (u % k_blocks);
-                int kb1 = (int) min((long) k_blocks, kb0 + (u_end - u));
+                int kb1 = (int) min((long) k_blocks, kb0 + (ue - u));
                 // the epilogue must have drained the previous segment's accumulators
                 ok = mbar_wait(acc_empty, (uint32_t) (seg & 1) ^ 1, abort_flag, p.status, 4);
                 if (!ok) break;
@@ -363,17 +377,19 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     }
                 }
             }
-            u_end = u_begin;                             // nothing left for the stream-K loop below
+            u_end = u_begin;                             // nothing left for the loop below
         }
-        for (long u = u_begin; u < u_end; ++seg) {
+        bool live = true;
+        for (int pass = 0; pass < 2 && live; ++pass)
+        for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue; ++seg) {
             int tile = (int) (u / k_blocks), kb0 = (int) (u % k_blocks);
-            int kb1 = (int) min((long) k_blocks, kb0 + (u_end - u));
+            int kb1 = (int) min((long) k_blocks, kb0 + (ue - u));
             int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             const bool partial = !(kb0 == 0 && kb1 == k_blocks);   // split tiles are summed with atomics
             const bool add_res = p.r_re != nullptr && kb0 == 0;
             mbar_wait(acc_full, (uint32_t) seg & 1, abort_flag, p.status, 3);
             epi_bar_sync();                          // everyone arrives, then agree on the outcome
-            if (*abort_flag) break;
+            if (*abort_flag) { live = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -675,45 +691,56 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         rc = b_mn ? make_map_mn(&maps[4 + q], b[q], N, K) : make_map(&maps[4 + q], b[q], N, K);
         if (rc != CNB_OK) return rc;
     }
-    // stream-K: the (tile, k-block) units are dealt out in equal consecutive runs, one run per CTA,
-    // one CTA per SM; a tile whose k-range is shared by several CTAs is summed with atomics
     int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int k_blocks = (K + BK - 1) / BK;
     long total = (long) tiles * k_blocks;
     long min_units = 8;                                  // do not split below 8 k-blocks per CTA
     // leaving a few SMs free (gemm_cta_limit) lets a concurrent collective's kernels run beside the GEMM
     const int sms = ctx->gemm_cta_limit > 0 ? std::min(ctx->gemm_cta_limit, ctx->sm_count) : ctx->sm_count;
-    // Whole tiles (plain stores: no atomics, no cleared output, a fixed summation order) when there are
-    // many tiles, or when D is not read and the waves of one-tile CTAs are at least 85 % full; a grid
-    // capped for a concurrent collective only when one wave holds all tiles.
-    const int waves = (tiles + sms - 1) / sms;
-    // (not for K > 4096: one fp32 accumulation chain in tensor memory that long costs accuracy)
-    const bool full_waves = !accumulate && (long) tiles * 100 >= (long) waves * sms * 85 && k_blocks <= 256 &&
-                            (ctx->gemm_cta_limit <= 0 || tiles <= sms);
-    const bool whole_tiles = (tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0) || full_waves;
+    // Schedule, by tile count (sms = the SMs this launch may fill):
+    //  * tiles >= 4 x SMs, or one nearly full wave of one-tile CTAs when D is not read: whole tiles, grid =
+    //    tiles, plain stores, fixed summation order;
+    //  * more tiles than SMs: persistent CTAs, one per SM; each takes tiles / SMs whole tiles and then an
+    //    equal run of the remaining tiles' k-blocks (summed with atomics), so every SM finishes together
+    //    and only the remainder needs atomics and a cleared output;
+    //  * few tiles and short runs: a cluster per tile (below); otherwise plain stream-K.
+    // K > 4096 keeps to stream-K runs: one fp32 accumulation chain in tensor memory that long costs accuracy.
+    const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
+    const bool whole_tiles = (tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0) || full_wave;
+    const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
     long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
     if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
     long upc = (total + ctas - 1) / ctas;
     if (whole_tiles) upc = k_blocks;
     ctas = (total + upc - 1) / upc;
+    int whole_per_cta = 0;
+    int clear_from_row = 0;                              // rows of D below this one are only ever stored whole
+    if (lead_whole) {
+        ctas = sms;
+        whole_per_cta = tiles / sms;
+        const long rest = (long) (tiles - whole_per_cta * sms) * k_blocks;
+        upc = (rest + ctas - 1) / ctas;
+        clear_from_row = (whole_per_cta * sms / ((N + BN - 1) / BN)) * BM;
+    }
     // Few tiles (small batches): a cluster of 2, 4 or 8 CTAs takes one tile, every CTA a slice of K, and
     // the partial tiles are summed through distributed shared memory: no atomics, no cleared output,
     // a fixed summation order.
     // Worth it while a stream-K run would be short (<= 48 k-blocks): with long runs the atomics are
     // amortised and using every SM wins over the clusters' rounded-down CTA count.
     int cluster = 1;
-    if (!whole_tiles && upc <= 48) {
+    if (!whole_tiles && !lead_whole && upc <= 48) {
         for (int c = 8; c >= 2; c >>= 1)
             if ((long) tiles * c <= sms && k_blocks / c >= 4) { cluster = c; break; }
     }
     if (cluster > 1) { ctas = (long) tiles * cluster; upc = 0; }
-    bool splits_tiles = cluster == 1 && (upc % k_blocks) != 0;
+    bool splits_tiles = cluster == 1 && (lead_whole ? upc > 0 : (upc % k_blocks) != 0);
     if (splits_tiles && !accumulate) {
         // one launch clears both planes (they need not be adjacent or in one allocation)
-        const size_t plane = (size_t) M * N;
+        const size_t first = (size_t) clear_from_row * N;
+        const size_t plane = (size_t) M * N - first;
         const size_t vec = plane / 4 + 1;
         const int blocks = (int) std::min<size_t>((vec + 255) / 256, (size_t) ctx->sm_count * 8);
-        zero_pair_k<<<blocks, 256, 0, st>>>(d_re, d_im, plane);
+        zero_pair_k<<<blocks, 256, 0, st>>>(d_re + first, d_im + first, plane);
         CNB_LAUNCH_CHECK("zero_pair");
     }
     TcParams p;
@@ -722,6 +749,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     p.units_per_cta = (int) upc;
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.cluster = cluster;
+    p.whole_per_cta = whole_per_cta;
     p.status = ctx->d_status;
     if (cluster > 1) {
         cudaLaunchConfig_t cfg = {};
