@@ -43,7 +43,10 @@ def _pair(z):
 # runs that cover whole tiles plus a split remainder, one-tile-per-CTA grids, ragged M/N/K edges
 @pytest.mark.parametrize("B,n_in,n_out", [(1, 1, 1), (7, 48, 40), (64, 784, 10), (4095, 1024, 10), (3, 33, 16), (33, 100, 130), (256, 512, 384),
                                           (128, 1024, 1024), (4096, 256, 1024), (3072, 64, 3200), (200, 100, 72),
-                                          (1000, 36, 1000)])
+                                          (1000, 36, 1000),
+                                          # ragged tiles under every GEMM schedule: whole tiles first + shared remainder
+                                          # (180 tiles), stream-K, clusters of 2 and 4 with an uneven K split
+                                          (2500, 520, 1064), (300, 1024, 1024)])
 def test_linear_three_products(ctx, B, n_in, n_out):
     rng = np.random.default_rng(B * 1000 + n_in)
     x, w, g = _rand(rng, B, n_in), _rand(rng, n_out, n_in, scale=n_in ** -0.5), _rand(rng, B, n_out)
