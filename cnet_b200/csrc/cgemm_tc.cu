@@ -186,6 +186,32 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     return r;
 }
 
+// Brings `bytes` (a multiple of 16, 16-byte aligned) of global memory into L2 through the bulk-copy engine.
+// The epilogue reads residual / old-D tiles 128 bytes per row and round; fetched like that from DRAM each
+// row segment costs four scattered accesses, fetched here as one 512-byte piece per row, while the tile's
+// MMAs run, the later reads hit L2.
+__device__ __forceinline__ void l2_prefetch(const float* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tile_rows(const TcParams& p, const float* re, const float* im, int row,
+                                                  int n0) {
+    if (row >= p.M || (p.N & 3)) return;
+    const uint32_t bytes = (uint32_t) min(BN, p.N - n0) * 4u;
+    const size_t o = (size_t) row * p.N + n0;
+    if (((reinterpret_cast<uintptr_t>(re + o) | reinterpret_cast<uintptr_t>(im + o)) & 15) != 0) return;
+    l2_prefetch(re + o, bytes);
+    l2_prefetch(im + o, bytes);
+}
+
+// A 16-byte global load that stays where it is written (volatile asm keeps its place among the other
+// volatile asms: the tensor-memory loads and barriers), so a batch of them is in flight together.
+__device__ __forceinline__ float4 ld_global_now(const float* p) {
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
 // all threads of all CTAs of the cluster; orders shared-memory writes before the peers' reads
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -195,9 +221,9 @@ __device__ __forceinline__ void cluster_sync() {
 __device__ __forceinline__ float4 ld_peer(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    float4 v;
+    float4 v;   // volatile keeps it between the two cluster barriers; no memory clobber, so loads can be in flight together
     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
     return v;
 }
 
@@ -351,6 +377,14 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         int seg = 0;
         if (p.cluster > 1) {
             // the whole k-slice is one segment; its partial sums go to shared memory for the cluster reduction
+            {
+                const int tile = blockIdx.x / p.cluster, rows_per = BM / p.cluster;
+                const int row = (tile / tiles_n) * BM + (int) crank * rows_per + et, n0 = (tile % tiles_n) * BN;
+                if (et < rows_per) {                     // the band of rows this CTA will write out
+                    if (p.r_re) prefetch_tile_rows(p, p.r_re, p.r_im, row, n0);
+                    if (p.accumulate) prefetch_tile_rows(p, p.d_re, p.d_im, row, n0);
+                }
+            }
             mbar_wait(acc_full, 0u, abort_flag, p.status, 3);
             epi_bar_sync();
             if (!*abort_flag) {
@@ -387,12 +421,39 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             const bool partial = !(kb0 == 0 && kb1 == k_blocks);   // split tiles are summed with atomics
             const bool add_res = p.r_re != nullptr && kb0 == 0;
+            // one row of the tile per epilogue thread, requested before the wait for the MMAs
+            if (add_res) prefetch_tile_rows(p, p.r_re, p.r_im, m0 + et, n0);
+            if (!partial && p.accumulate) prefetch_tile_rows(p, p.d_re, p.d_im, m0 + et, n0);
             mbar_wait(acc_full, (uint32_t) seg & 1, abort_flag, p.status, 3);
             epi_bar_sync();                          // everyone arrives, then agree on the outcome
             if (*abort_flag) { live = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool need_old = !partial && p.accumulate;
+            const bool pre = vec_ok && (add_res || need_old);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
+                // What the write-out of this round adds from global memory (residual, old D) is requested
+                // now, so that it arrives while the accumulators are drained; asked for between the
+                // stores below, each load would wait for the store before it.
+                float4 gr[8], gi[8];
+                if (pre) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int idx = et + 128 * j;
+                        const int gm = m0 + (idx >> 3), gn = n0 + c0 + (idx & 7) * 4;
+                        gr[j] = make_float4(0.f, 0.f, 0.f, 0.f); gi[j] = gr[j];
+                        if (gm >= p.M || gn >= p.N) continue;
+                        const size_t o = (size_t) gm * p.N + gn;
+                        // the residual if there is one, else old D (both at once: old D is read at the store)
+                        if (add_res) {
+                            gr[j] = ld_global_now(p.r_re + o);
+                            gi[j] = ld_global_now(p.r_im + o);
+                        } else {
+                            gr[j] = ld_global_now(p.d_re + o);
+                            gi[j] = ld_global_now(p.d_im + o);
+                        }
+                    }
+                }
                 {
                     float a[16], f[16];
 #pragma unroll
@@ -438,8 +499,12 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     float4 vi = *reinterpret_cast<const float4*>(stage_im + stage_off(r, ch));
                     size_t o = (size_t) gm * p.N + gn;
                     if (vec_ok) {
-                        if (add_res) {
-                            float4 xr = *reinterpret_cast<const float4*>(p.r_re + o), xi = *reinterpret_cast<const float4*>(p.r_im + o);
+                        if (pre) {
+                            vr.x += gr[j].x; vr.y += gr[j].y; vr.z += gr[j].z; vr.w += gr[j].w;
+                            vi.x += gi[j].x; vi.y += gi[j].y; vi.z += gi[j].z; vi.w += gi[j].w;
+                        }
+                        if (add_res && need_old) {       // both at once: old D is read here
+                            const float4 xr = *reinterpret_cast<const float4*>(p.d_re + o), xi = *reinterpret_cast<const float4*>(p.d_im + o);
                             vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
                             vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
                         }
@@ -447,11 +512,6 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                             atomicAdd(reinterpret_cast<float4*>(p.d_re + o), vr);
                             atomicAdd(reinterpret_cast<float4*>(p.d_im + o), vi);
                         } else {
-                            if (p.accumulate) {
-                                float4 xr = *reinterpret_cast<const float4*>(p.d_re + o), xi = *reinterpret_cast<const float4*>(p.d_im + o);
-                                vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
-                                vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
-                            }
                             *reinterpret_cast<float4*>(p.d_re + o) = vr;
                             *reinterpret_cast<float4*>(p.d_im + o) = vi;
                         }
@@ -491,33 +551,44 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                 const int gm = m0 + r, gn = n0 + ch * 4;
                 if (gm >= p.M || gn >= p.N) continue;
                 const uint32_t local = smem_base + 4u * (uint32_t) part_off(r, ch);
-                float4 vr = make_float4(0.f, 0.f, 0.f, 0.f), vi = vr;
-                for (int c = 0; c < p.cluster; ++c) {    // fixed order: the sum does not depend on timing
-                    const float4 xr = ld_peer(local, (uint32_t) c), xi = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c);
-                    vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
-                    vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
-                }
                 const size_t o = (size_t) gm * p.N + gn;
+                // every load of this chunk is issued before the first sum: one round trip, not one per peer
+                float4 xr[8], xi[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    if (c < p.cluster) { xr[c] = ld_peer(local, (uint32_t) c); xi[c] = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c); }
+                float4 vr = make_float4(0.f, 0.f, 0.f, 0.f), vi = vr;
                 if (vec_ok) {
                     if (p.r_re) {
-                        const float4 xr = *reinterpret_cast<const float4*>(p.r_re + o), xi = *reinterpret_cast<const float4*>(p.r_im + o);
-                        vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
-                        vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                        vr = __ldg(reinterpret_cast<const float4*>(p.r_re + o));
+                        vi = __ldg(reinterpret_cast<const float4*>(p.r_im + o));
                     }
                     if (p.accumulate) {
-                        const float4 xr = *reinterpret_cast<const float4*>(p.d_re + o), xi = *reinterpret_cast<const float4*>(p.d_im + o);
-                        vr.x += xr.x; vr.y += xr.y; vr.z += xr.z; vr.w += xr.w;
-                        vi.x += xi.x; vi.y += xi.y; vi.z += xi.z; vi.w += xi.w;
+                        const float4 dr = *reinterpret_cast<const float4*>(p.d_re + o), di = *reinterpret_cast<const float4*>(p.d_im + o);
+                        vr.x += dr.x; vr.y += dr.y; vr.z += dr.z; vr.w += dr.w;
+                        vi.x += di.x; vi.y += di.y; vi.z += di.z; vi.w += di.w;
                     }
+                }
+                float4 sr = make_float4(0.f, 0.f, 0.f, 0.f), si = sr;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {            // fixed order: the sum does not depend on timing
+                    if (c < p.cluster) {
+                        sr.x += xr[c].x; sr.y += xr[c].y; sr.z += xr[c].z; sr.w += xr[c].w;
+                        si.x += xi[c].x; si.y += xi[c].y; si.z += xi[c].z; si.w += xi[c].w;
+                    }
+                }
+                if (vec_ok) {
+                    vr.x += sr.x; vr.y += sr.y; vr.z += sr.z; vr.w += sr.w;
+                    vi.x += si.x; vi.y += si.y; vi.z += si.z; vi.w += si.w;
                     *reinterpret_cast<float4*>(p.d_re + o) = vr;
                     *reinterpret_cast<float4*>(p.d_im + o) = vi;
                 } else {
-                    const float wr[4] = {vr.x, vr.y, vr.z, vr.w}, wi[4] = {vi.x, vi.y, vi.z, vi.w};
+                    const float wr[4] = {sr.x, sr.y, sr.z, sr.w}, wi[4] = {si.x, si.y, si.z, si.w};
                     for (int k = 0; k < 4 && gn + k < p.N; ++k) {
-                        float xr = wr[k], xi = wi[k];
-                        if (p.r_re) { xr += p.r_re[o + k]; xi += p.r_im[o + k]; }
-                        if (p.accumulate) { xr += p.d_re[o + k]; xi += p.d_im[o + k]; }
-                        p.d_re[o + k] = xr; p.d_im[o + k] = xi;
+                        float ar = wr[k], ai = wi[k];
+                        if (p.r_re) { ar += p.r_re[o + k]; ai += p.r_im[o + k]; }
+                        if (p.accumulate) { ar += p.d_re[o + k]; ai += p.d_im[o + k]; }
+                        p.d_re[o + k] = ar; p.d_im[o + k] = ai;
                     }
                 }
             }

@@ -158,10 +158,17 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
             // fused tail: y = gelu(u o h) and its hi/lo split, straight from the registers; a warp's
             // store covers 128 contiguous bytes
             const size_t o = (size_t) row * N + t;
+            // h of the next position is requested before this position's stores (a load placed after them
+            // would have to be issued after them: the compiler cannot tell that they do not alias)
+            float hr_next = __ldg(ep.hr + t), hi_next = __ldg(ep.hi + t);      // bitrev(0) = 0
 #pragma unroll
             for (int p = 0; p < R; ++p) {
                 const int e = bitrev<R>(p) * R;
-                const float hr = __ldg(ep.hr + e + t), hi = __ldg(ep.hi + e + t);
+                const float hr = hr_next, hi = hi_next;
+                if (p + 1 < R) {
+                    hr_next = __ldg(ep.hr + bitrev<R>(p + 1) * R + t);
+                    hi_next = __ldg(ep.hi + bitrev<R>(p + 1) * R + t);
+                }
                 const float gr = cnb_gelu(re[p] * hr - im[p] * hi);
                 const float gi = cnb_gelu(re[p] * hi + im[p] * hr);
                 if (ep.gr) { ep.gr[o + e] = gr; ep.gi[o + e] = gi; }
