@@ -559,12 +559,9 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     if (c < p.cluster) { xr[c] = ld_peer(local, (uint32_t) c); xi[c] = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c); }
                 float4 vr = make_float4(0.f, 0.f, 0.f, 0.f), vi = vr;
                 if (vec_ok) {
-                    if (p.r_re) {
-                        vr = __ldg(reinterpret_cast<const float4*>(p.r_re + o));
-                        vi = __ldg(reinterpret_cast<const float4*>(p.r_im + o));
-                    }
+                    if (p.r_re) { vr = ld_global_now(p.r_re + o); vi = ld_global_now(p.r_im + o); }
                     if (p.accumulate) {
-                        const float4 dr = *reinterpret_cast<const float4*>(p.d_re + o), di = *reinterpret_cast<const float4*>(p.d_im + o);
+                        const float4 dr = ld_global_now(p.d_re + o), di = ld_global_now(p.d_im + o);
                         vr.x += dr.x; vr.y += dr.y; vr.z += dr.z; vr.w += dr.w;
                         vi.x += di.x; vi.y += di.y; vi.z += di.z; vi.w += di.w;
                     }
