@@ -111,14 +111,30 @@ skinny_bwd_x_k(const float* __restrict__ gr, const float* __restrict__ gi, const
         }
     }
     const int r0 = blockIdx.y * rows_per_chunk, r1 = min(B, r0 + rows_per_chunk);
+    // G of the next row is requested before this row's stores (one row of look-ahead in registers)
+    float ga[OT], gc[OT];
+#pragma unroll
+    for (int o = 0; o < OT; ++o) {
+        const bool on = o < out && r0 < r1;
+        ga[o] = on ? __ldg(gr + (size_t) r0 * out + o) : 0.f;
+        gc[o] = on ? __ldg(gi + (size_t) r0 * out + o) : 0.f;
+    }
     for (int b = r0; b < r1; ++b) {
+        float a_[OT], c_[OT];
+#pragma unroll
+        for (int o = 0; o < OT; ++o) { a_[o] = ga[o]; c_[o] = gc[o]; }
+        if (b + 1 < r1) {
+#pragma unroll
+            for (int o = 0; o < OT; ++o)
+                if (o < out) { ga[o] = __ldg(gr + (size_t) (b + 1) * out + o); gc[o] = __ldg(gi + (size_t) (b + 1) * out + o); }
+        }
         float sr[W], si[W];
 #pragma unroll
         for (int k = 0; k < W; ++k) sr[k] = si[k] = 0.f;
 #pragma unroll
         for (int o = 0; o < OT; ++o) {
             if (o < out) {
-                const float a = __ldg(gr + (size_t) b * out + o), c = __ldg(gi + (size_t) b * out + o);
+                const float a = a_[o], c = c_[o];
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
                     sr[k] += a * wre[o][k] + c * wim[o][k];      // (a + ic)(wre - i wim)
