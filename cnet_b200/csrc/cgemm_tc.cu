@@ -227,6 +227,69 @@ __device__ __forceinline__ float4 ld_peer(uint32_t local_addr, uint32_t rank) {
     return v;
 }
 
+// Cluster mode, after the first cluster barrier: this CTA sums its band of rows of the tile over the CL
+// partial tiles (its own and its peers', through distributed shared memory), adds residual / old D and
+// stores.  Two 16-byte chunks per thread and round: every load of both (2 * CL peer loads per plane pair,
+// residual, old D) is issued before the first sum, so a round costs one round trip.  Fixed summation order.
+template <int CL>
+__device__ __forceinline__ void cluster_reduce(const TcParams& p, uint32_t smem_base, uint32_t crank, int m0, int n0,
+                                               int et, bool vec_ok) {
+    constexpr int ROWS = BM / CL;
+    constexpr int U = CL <= 4 ? 2 : 1;                   // chunks per thread and round
+    for (int base = et; base < ROWS * 32; base += 128 * U) {
+        float4 xr[U][CL], xi[U][CL], vr[U], vi[U];
+        size_t o[U];
+        bool live[U];
+        int gn[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + 128 * u;
+            const int r = (int) crank * ROWS + (idx >> 5), ch = idx & 31;
+            const int gm = m0 + r;
+            gn[u] = n0 + ch * 4;
+            live[u] = idx < ROWS * 32 && gm < p.M && gn[u] < p.N;
+            o[u] = (size_t) gm * p.N + gn[u];
+            vr[u] = make_float4(0.f, 0.f, 0.f, 0.f); vi[u] = vr[u];
+            if (!live[u]) continue;
+            const uint32_t local = smem_base + 4u * (uint32_t) part_off(r, ch);
+#pragma unroll
+            for (int c = 0; c < CL; ++c) { xr[u][c] = ld_peer(local, (uint32_t) c); xi[u][c] = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c); }
+            if (vec_ok) {
+                if (p.r_re) { vr[u] = ld_global_now(p.r_re + o[u]); vi[u] = ld_global_now(p.r_im + o[u]); }
+                if (p.accumulate) {
+                    const float4 dr = ld_global_now(p.d_re + o[u]), di = ld_global_now(p.d_im + o[u]);
+                    vr[u].x += dr.x; vr[u].y += dr.y; vr[u].z += dr.z; vr[u].w += dr.w;
+                    vi[u].x += di.x; vi[u].y += di.y; vi[u].z += di.z; vi[u].w += di.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (!live[u]) continue;
+            float4 sr = make_float4(0.f, 0.f, 0.f, 0.f), si = sr;
+#pragma unroll
+            for (int c = 0; c < CL; ++c) {
+                sr.x += xr[u][c].x; sr.y += xr[u][c].y; sr.z += xr[u][c].z; sr.w += xr[u][c].w;
+                si.x += xi[u][c].x; si.y += xi[u][c].y; si.z += xi[u][c].z; si.w += xi[u][c].w;
+            }
+            if (vec_ok) {
+                vr[u].x += sr.x; vr[u].y += sr.y; vr[u].z += sr.z; vr[u].w += sr.w;
+                vi[u].x += si.x; vi[u].y += si.y; vi[u].z += si.z; vi[u].w += si.w;
+                *reinterpret_cast<float4*>(p.d_re + o[u]) = vr[u];
+                *reinterpret_cast<float4*>(p.d_im + o[u]) = vi[u];
+            } else {
+                const float wr[4] = {sr.x, sr.y, sr.z, sr.w}, wi[4] = {si.x, si.y, si.z, si.w};
+                for (int k = 0; k < 4 && gn[u] + k < p.N; ++k) {
+                    float ar = wr[k], ai = wi[k];
+                    if (p.r_re) { ar += p.r_re[o[u] + k]; ai += p.r_im[o[u] + k]; }
+                    if (p.accumulate) { ar += p.d_re[o[u] + k]; ai += p.d_im[o[u] + k]; }
+                    p.d_re[o[u] + k] = ar; p.d_im[o[u] + k] = ai;
+                }
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
            const __grid_constant__ CUtensorMap a_lo_re, const __grid_constant__ CUtensorMap a_lo_im,
@@ -541,53 +604,14 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         if (warp >= 2 && !*abort_flag) {
             const int tile = blockIdx.x / p.cluster;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-            const int rows_per = BM / p.cluster;         // this CTA sums and writes out its band of rows
             const int et = (warp - 2) * 32 + lane;
             const bool vec_ok = (p.N % 4 == 0) &&
                 ((reinterpret_cast<uintptr_t>(p.d_re) | reinterpret_cast<uintptr_t>(p.d_im) |
                   reinterpret_cast<uintptr_t>(p.r_re) | reinterpret_cast<uintptr_t>(p.r_im)) & 15) == 0;
-            for (int idx = et; idx < rows_per * 32; idx += 128) {
-                const int r = (int) crank * rows_per + (idx >> 5), ch = idx & 31;
-                const int gm = m0 + r, gn = n0 + ch * 4;
-                if (gm >= p.M || gn >= p.N) continue;
-                const uint32_t local = smem_base + 4u * (uint32_t) part_off(r, ch);
-                const size_t o = (size_t) gm * p.N + gn;
-                // every load of this chunk is issued before the first sum: one round trip, not one per peer
-                float4 xr[8], xi[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    if (c < p.cluster) { xr[c] = ld_peer(local, (uint32_t) c); xi[c] = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c); }
-                float4 vr = make_float4(0.f, 0.f, 0.f, 0.f), vi = vr;
-                if (vec_ok) {
-                    if (p.r_re) { vr = ld_global_now(p.r_re + o); vi = ld_global_now(p.r_im + o); }
-                    if (p.accumulate) {
-                        const float4 dr = ld_global_now(p.d_re + o), di = ld_global_now(p.d_im + o);
-                        vr.x += dr.x; vr.y += dr.y; vr.z += dr.z; vr.w += dr.w;
-                        vi.x += di.x; vi.y += di.y; vi.z += di.z; vi.w += di.w;
-                    }
-                }
-                float4 sr = make_float4(0.f, 0.f, 0.f, 0.f), si = sr;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {            // fixed order: the sum does not depend on timing
-                    if (c < p.cluster) {
-                        sr.x += xr[c].x; sr.y += xr[c].y; sr.z += xr[c].z; sr.w += xr[c].w;
-                        si.x += xi[c].x; si.y += xi[c].y; si.z += xi[c].z; si.w += xi[c].w;
-                    }
-                }
-                if (vec_ok) {
-                    vr.x += sr.x; vr.y += sr.y; vr.z += sr.z; vr.w += sr.w;
-                    vi.x += si.x; vi.y += si.y; vi.z += si.z; vi.w += si.w;
-                    *reinterpret_cast<float4*>(p.d_re + o) = vr;
-                    *reinterpret_cast<float4*>(p.d_im + o) = vi;
-                } else {
-                    const float wr[4] = {sr.x, sr.y, sr.z, sr.w}, wi[4] = {si.x, si.y, si.z, si.w};
-                    for (int k = 0; k < 4 && gn + k < p.N; ++k) {
-                        float ar = wr[k], ai = wi[k];
-                        if (p.r_re) { ar += p.r_re[o + k]; ai += p.r_im[o + k]; }
-                        if (p.accumulate) { ar += p.d_re[o + k]; ai += p.d_im[o + k]; }
-                        p.d_re[o + k] = ar; p.d_im[o + k] = ai;
-                    }
-                }
+            switch (p.cluster) {
+                case 2: cluster_reduce<2>(p, smem_base, crank, m0, n0, et, vec_ok); break;
+                case 4: cluster_reduce<4>(p, smem_base, crank, m0, n0, et, vec_ok); break;
+                default: cluster_reduce<8>(p, smem_base, crank, m0, n0, et, vec_ok); break;
             }
         }
         cluster_sync();                                  // no CTA leaves while a peer still reads its shared memory
