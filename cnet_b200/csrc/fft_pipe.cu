@@ -202,7 +202,10 @@ int fft1024_pipe(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, floa
     const uintptr_t bits = reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(xi) |
                            reinterpret_cast<uintptr_t>(yr) | reinterpret_cast<uintptr_t>(yi);
     if (bits & 15) return set_error(CNB_ERR_ARG, "fft: planes must be 16-byte aligned");
-    int blocks = B < ctx->sm_count ? B : ctx->sm_count;  // persistent: one CTA per SM
+    // persistent: one CTA per SM; like the GEMM it fills an SM's shared memory, so while a collective's
+    // kernels need SMs (cnb_set_gemm_sm_limit) it leaves the same SMs free instead of waiting for them
+    const int sms = ctx->gemm_cta_limit > 0 && ctx->gemm_cta_limit < ctx->sm_count ? ctx->gemm_cta_limit : ctx->sm_count;
+    int blocks = B < sms ? B : sms;
     if (inverse) fft1024_pipe_k<1><<<blocks, THREADS, SMEM_BYTES, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep, ctx->d_status);
     else fft1024_pipe_k<-1><<<blocks, THREADS, SMEM_BYTES, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep, ctx->d_status);
     CNB_LAUNCH_CHECK("fft1024_pipe");
