@@ -127,10 +127,9 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
                 if (dur && accumulate_u) { vr = ld<W>(dur, i); vi = ld<W>(dui, i); }
 #pragma unroll
                 for (int k = 0; k < W; ++k) {
-                    float dx = 0.5f * dgelu_f(zr.v[k]), dy = 0.5f * dgelu_f(zi.v[k]);
-                    float p = dx + dy, m = dx - dy;
-                    // dz* = conj(g*) (dx-dy) + g* (dx+dy)
-                    float nr = tr.v[k] * m + tr.v[k] * p, ni = -ti.v[k] * m + ti.v[k] * p;
+                    // dz* = conj(g*) (dx-dy) + g* (dx+dy) with dx, dy = gelu'(Re a) / 2, gelu'(Im a) / 2:
+                    // the real part is Re g* . gelu'(Re a), the imaginary part Im g* . gelu'(Im a)
+                    float nr = tr.v[k] * dgelu_f(zr.v[k]), ni = ti.v[k] * dgelu_f(zi.v[k]);
                     tr.v[k] = nr; ti.v[k] = ni;
                     float wr = nr * hre.v[k] + ni * him.v[k], wi = ni * hre.v[k] - nr * him.v[k];   // t o conj(h)
                     if (dur && accumulate_u) { vr.v[k] += wr; vi.v[k] += wi; } else { vr.v[k] = wr; vi.v[k] = wi; }
@@ -240,10 +239,9 @@ __global__ void gelu_bwd_k(const float* __restrict__ gr, const float* __restrict
         if (accumulate) { r = ld<W>(dr, i); s = ld<W>(di, i); }
 #pragma unroll
         for (int k = 0; k < W; ++k) {
-            float dx = 0.5f * dgelu_f(x.v[k]), dy = 0.5f * dgelu_f(y.v[k]);
-            float p = dx + dy, m = dx - dy;
-            float nr = a.v[k] * m + a.v[k] * p;       // Re(conj(g) m + g p)
-            float ni = -b.v[k] * m + b.v[k] * p;      // Im
+            // conj(g) (dx-dy) + g (dx+dy), dx, dy = gelu'(x) / 2, gelu'(y) / 2: component-wise products
+            float nr = a.v[k] * dgelu_f(x.v[k]);
+            float ni = b.v[k] * dgelu_f(y.v[k]);
             r.v[k] = accumulate ? r.v[k] + nr : nr;
             s.v[k] = accumulate ? s.v[k] + ni : ni;
         }

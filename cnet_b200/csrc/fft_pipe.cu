@@ -95,16 +95,18 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
     float* si = sr + R * (R + 1);
     float* out_r = sr;                                   // the finished row, natural order, over the same memory
     float* out_i = sr + N;
-    for (int i = threadIdx.x; i < N; i += THREADS) tws[i] = tw[i];
+    const long stride = (long) gridDim.x * WARPS;
+    long row = blockIdx.x + (long) gridDim.x * w;
+    // the warp's barrier is set up and its first row requested by the same thread, before the twiddle table
+    // is staged: the first fetch runs under the staging
     if (t == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (row < B) row_fetch(smem_u32(in_r), xr + row * N, xi + row * N, bar);
     }
+    for (int i = threadIdx.x; i < N; i += THREADS) tws[i] = tw[i];
     __syncthreads();
 
-    const long stride = (long) gridDim.x * WARPS;
-    long row = blockIdx.x + (long) gridDim.x * w;
-    if (row < B && t == 0) row_fetch(smem_u32(in_r), xr + row * N, xi + row * N, bar);
     const float scale = rsqrtf((float) N);
     uint32_t phase = 0;
     bool stored = false;
