@@ -674,6 +674,17 @@ extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, con
     StaticScratch sc;
     int rc = static_scratch_for_current_device(&sc);
     if (rc != CNB_OK) return rc;
+    {   // the scratch belongs to the current device: kernels launched here must not be handed another GPU's planes
+        int dev = -1;
+        CNB_CUDA(cudaGetDevice(&dev));
+        const void* probe[2] = {g_re, dv_re};
+        for (const void* q : probe) {
+            cudaPointerAttributes at;
+            CNB_CUDA(cudaPointerGetAttributes(&at, q));
+            CNB_CHECK_ARG((at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) && at.device == dev,
+                          "cnb_hadamard_bwd_static: the planes are not memory of the current device %d", dev);
+        }
+    }
     cudaStream_t stm = cnb::S(stream);
     size_t total = (size_t) B * N;
     if (du_re) {
@@ -686,7 +697,10 @@ extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, con
                 g_re, g_im, v_re, v_im, 0, du_re, du_im, accumulate_u, total, N);
         CNB_LAUNCH_CHECK("hadamard_bwd_elem");
     }
-    int col_blocks = (N + 31) / 32;
+    // 16-byte form (4 columns per thread) where the planes allow it, as the arena-backed entry does
+    const bool vec = (N % 4 == 0) && all_aligned(g_re, g_im, u_re, u_im);
+    const int w = vec ? 4 : 1;
+    int col_blocks = (N + 32 * w - 1) / (32 * w);
     int chunks = (sc.sm_count * 4 + col_blocks - 1) / col_blocks;
     chunks = std::min(chunks, std::min((B + 7) / 8, kStaticMaxChunks));
     chunks = std::max(chunks, 1);
@@ -696,8 +710,12 @@ extern "C" int cnb_hadamard_bwd_static(const float* g_re, const float* g_im, con
     float* pr = sc.ptr;
     float* pi = sc.ptr + (size_t) kStaticMaxChunks * kStaticMaxN;
     dim3 grid(col_blocks, chunks), block(32, 8);
-    colreduce_stage1_k<0, 1><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
-                                                      nullptr, nullptr, 0, pr, pi, B, N, rows, nullptr, nullptr, nullptr, 0);
+    if (vec)
+        colreduce_stage1_k<0, 4><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
+                                                          nullptr, nullptr, 0, pr, pi, B, N, rows, nullptr, nullptr, nullptr, 0);
+    else
+        colreduce_stage1_k<0, 1><<<grid, block, 0, stm>>>(g_re, g_im, nullptr, nullptr, u_re, u_im, nullptr, nullptr,
+                                                          nullptr, nullptr, 0, pr, pi, B, N, rows, nullptr, nullptr, nullptr, 0);
     CNB_LAUNCH_CHECK("colreduce_stage1");
     colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dv_re, dv_im, accumulate_v, chunks, N);
     CNB_LAUNCH_CHECK("colreduce_stage2");

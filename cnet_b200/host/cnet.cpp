@@ -88,6 +88,9 @@ void CFunc::addOutput(CFunc* next, int offset) {
 	if (next->depth_ <= depth_) next->depth_ = depth_ + 1;
 }
 
+std::complex<float> CFunc::dz(int, int) { return std::complex<float>(NAN, NAN); }
+std::complex<float> CFunc::dz_star(int, int) { return std::complex<float>(NAN, NAN); }
+
 void CFunc::updateInput(float lr) {
 	if (!is_input_ || !out_.dz_star_real_ || batched_) return;
 	check(cnb_sgd_update(ctx(), out_.real_, out_.dz_star_real_, out_.count(), lr, 1, stream()));
@@ -453,6 +456,12 @@ int CNet::add(CFunc* f) {
 	else next_uid_ = std::max(next_uid_, f->uid_);
 	if (map_.count(f->uid_)) { fail(CNB_ERR_ARG, "add: duplicate uid " + std::to_string(f->uid_)); return -1; }
 	f->type_ = getType(f);
+	if (f->type_ == 0x7fffffff && !f->runsOnDevice()) {
+		fail(CNB_ERR_UNSUPPORTED, f->getName() + ": not a built-in layer and it does not run on the device: the generic "
+				"dz / dz_star Jacobian loop of the reference (impl/cfunc.h:290-325) has no device form; give the layer "
+				"forward() / backward() that launch kernels on stream() and return true from runsOnDevice()");
+		return -1;
+	}
 	f->net_ = this;
 	func_list_.push_back(f);
 	map_[f->uid_] = f;
@@ -814,6 +823,8 @@ bool CNet::setInputValues(int uid, const float* re, const float* im, int len) {
 	if (rc == CNB_OK) rc = cnb_sync(ctx_, stream_);
 	if (rc != CNB_OK) { fail(rc, "setInputValues"); return false; }
 	++weights_version_;
+	// a captured step holds no launch that re-splits the Linear weights: it would multiply by the old ones
+	if (graph_exec_) graph_stale_ = "weights were set from the host after the step was captured";
 	return true;
 }
 
@@ -995,6 +1006,16 @@ void CNet::backward() {
 
 bool CNet::reduceBucket(size_t k) {
 	const Bucket& b = buckets_[k];
+	if ((nccl_.active() || hook_) && k == 0) {
+		// The arena accumulates until the update and is summed over the ranks in place: a second backward()
+		// before the update would reduce the already reduced part again (earlier micro-batches x ranks).
+		if (reduced_since_update_) {
+			fail(CNB_ERR_UNSUPPORTED, "backward: a second backward pass before updateInputs while gradients are reduced over the "
+					"ranks in place; gradient accumulation over micro-batches is not available with data parallelism");
+			return false;
+		}
+		reduced_since_update_ = true;
+	}
 	if (nccl_.active()) {
 		if (!nccl_.allReduce(wgrad_base_ + b.begin, b.count, stream_)) { fail(CNB_ERR_CUDA, "all-reduce: " + nccl_.error()); return false; }
 	}
@@ -1028,11 +1049,15 @@ bool CNet::beginCapture() {
 	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("cudaStreamBeginCapture: ") + cudaGetErrorString(e)); return false; }
 	capturing_ = true;
 	graph_launches_ = cnb_launch_count();
+	graph_batch_ = cur_batch_;
 	return true;
 }
 
 bool CNet::endCapture() {
 	if (!capturing_) { fail(CNB_ERR_ARG, "endCapture: no capture in progress"); return false; }
+	// a backward() captured without an update leaves collectives on the communication stream: bring it back
+	// into the capturing stream, or the capture cannot end
+	if (!nccl_.join(stream_)) fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error());
 	capturing_ = false;
 	graph_launches_ = cnb_launch_count() - graph_launches_;
 	cudaGraph_t g = nullptr;
@@ -1045,11 +1070,19 @@ bool CNet::endCapture() {
 	cudaGraphDestroy(g);
 	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e)); return false; }
 	graph_exec_ = x;
+	graph_stale_.clear();
 	return true;
 }
 
 bool CNet::launchGraph() {
 	if (!graph_exec_) { fail(CNB_ERR_ARG, "launchGraph: capture a step first"); return false; }
+	// grids, row counts and the "weights are already split" decision were frozen at capture time
+	if (cur_batch_ != graph_batch_) {
+		fail(CNB_ERR_ARG, "launchGraph: the batch in flight has " + std::to_string(cur_batch_) + " rows, the captured step was sized for " +
+				std::to_string(graph_batch_) + "; capture again");
+		return false;
+	}
+	if (!graph_stale_.empty()) { fail(CNB_ERR_ARG, "launchGraph: " + graph_stale_ + "; capture again"); return false; }
 	cudaError_t e = cudaGraphLaunch((cudaGraphExec_t) graph_exec_, (cudaStream_t) stream_);
 	if (e != cudaSuccess) { fail(CNB_ERR_CUDA, std::string("cudaGraphLaunch: ") + cudaGetErrorString(e)); return false; }
 	return true;
@@ -1082,6 +1115,7 @@ void CNet::updateInputs(float lr) {
 		? cnb_sgd_update(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, stream_)
 		: cnb_sgd_update_split(ctx_, weight_base_, wgrad_base_, wgrad_count_, lr, 1, spans.data(), (int) spans.size(), stream_);
 	if (rc != CNB_OK) { fail(rc, "updateInputs"); return; }
+	reduced_since_update_ = false;
 	++weights_version_;
 	for (auto l : fused) l->w_split_version_ = weights_version_;
 	for (auto f : func_list_)
@@ -1091,6 +1125,11 @@ void CNet::updateInputs(float lr) {
 
 void CNet::adamUpdate(float lr, float beta, int t) {
 	if (!ctx_ || !wgrad_count_) return;
+	if (capturing_) {       // the bias correction 1 - beta^(t+1) is a launch parameter: a replay would reuse step t's
+		fail(CNB_ERR_UNSUPPORTED, "adamUpdate: cannot be captured in a CUDA graph (its step count is a launch parameter); "
+				"capture forward + backward and call adamUpdate outside the graph");
+		return;
+	}
 	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, 0);
 	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
 	if (!momentum_base_) {
@@ -1102,6 +1141,7 @@ void CNet::adamUpdate(float lr, float beta, int t) {
 	}
 	int rc = cnb_adam_update(ctx_, weight_base_, momentum_base_, wgrad_base_, wgrad_count_, lr, beta, t, stream_);
 	if (rc != CNB_OK) { fail(rc, "adamUpdate"); return; }
+	reduced_since_update_ = false;
 	++weights_version_;
 	for (auto f : func_list_)
 		if (Linear* l = dynamic_cast<Linear*>(f)) l->splitWeights();

@@ -152,6 +152,17 @@ public:
 	virtual CFunc* clone(Uid uid) = 0;
 	virtual std::string getName() = 0;
 	virtual void forward() = 0;
+	// Entries of the layer's Jacobians (impl/cfunc.h:144-145).  The reference's default backward() loops over
+	// them per sample on the CPU (impl/cfunc.h:290-325); nothing on the device path calls them: every layer
+	// here has a closed-form batched backward() kernel.  They are kept so that a layer written against the
+	// reference header still compiles; the built-in layers return NaN ("not used on the device path").
+	// A user layer that only supplies these two (and a CPU forward()) is refused by CNet::add unless it
+	// says it launches its own kernels (runsOnDevice).
+	virtual std::complex<float> dz(int out_indx, int in_indx);
+	virtual std::complex<float> dz_star(int out_indx, int in_indx);
+	// A layer outside the built-in set returns true once its forward()/backward() enqueue device work on
+	// stream() through the C ABI; the default (false) makes CNet::add refuse it.
+	virtual bool runsOnDevice() const { return false; }
 	virtual void backward() {}
 	virtual void backward(int label) { (void) label; backward(); }
 	virtual void updateInput(float learningRate);   // w -= lr dz*_w ; dz*_w = 0 (impl/cfunc.h:147-152 + impl/cnet.h:418)
@@ -405,6 +416,9 @@ class CNet {
 	void* graph_exec_ = nullptr;                    // cudaGraphExec_t of a captured step
 	bool capturing_ = false;
 	unsigned long long graph_launches_ = 0;         // kernels inside the captured step
+	int graph_batch_ = 0;                           // rows of the batch the captured launches were sized for
+	std::string graph_stale_;                       // why the captured step may no longer be replayed ("" = it may)
+	bool reduced_since_update_ = false;             // the gradient arena holds a sum over the ranks already
 	bool reduceBucket(size_t index);
 	// double-buffered input pipeline (prefetchBatch / commitBatch / readLossesAsync)
 	void* copy_stream_ = nullptr;                   // cudaStream_t for host <-> device copies

@@ -6,6 +6,7 @@
 //   CEmbedding : + dim, max tokens, vocab, re[len], im[len]
 //   Linear     : + in1_len, in2_len
 // every int32 / float32 big-endian.  Weights are read back from the device before saving.
+#include <climits>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -46,7 +47,7 @@ struct Reader {
 		return true;
 	}
 	bool getFloats(std::vector<float>* out, size_t n) {
-		if (at + 4 * n > s.size()) return false;
+		if (n > (s.size() - at) / 4) return false;       // also when 4 * n would wrap
 		out->resize(n);
 		for (size_t i = 0; i < n; ++i) {
 			int32_t v;
@@ -98,6 +99,12 @@ bool CNet::restoreFromString(const std::string& data) {
 		if (!r.get32(&uid) || !r.get32(&in_len) || !r.get32(&out_len) || !r.get32(&nprev) || nprev < 0 || nprev > 64) {
 			fail(CNB_ERR_ARG, "restore: truncated layer header"); return false;
 		}
+		// lengths come from the file: nothing below may size a buffer or a layer from a bad one
+		if (uid <= 0 || in_len <= 0 || out_len <= 0) {
+			fail(CNB_ERR_ARG, "restore: corrupt record (uid " + std::to_string(uid) + ", lengths " + std::to_string(in_len) +
+					" / " + std::to_string(out_len) + ")");
+			return false;
+		}
 		std::vector<int> prev(nprev);
 		for (int i = 0; i < nprev; ++i) if (!r.get32(&prev[i])) { fail(CNB_ERR_ARG, "restore: truncated producer list"); return false; }
 		CFunc* f = nullptr;
@@ -110,13 +117,16 @@ bool CNet::restoreFromString(const std::string& data) {
 		case isEmbedding: {
 			int32_t dim, toks, vocab;
 			if (!r.get32(&dim) || !r.get32(&toks) || !r.get32(&vocab)) { fail(CNB_ERR_ARG, "restore: truncated embedding"); return false; }
+			if (dim <= 0 || toks <= 0 || vocab <= 0 || (int64_t) dim * vocab != (int64_t) in_len || (int64_t) dim * toks > INT_MAX) {
+				fail(CNB_ERR_ARG, "restore: corrupt record (embedding dims)"); return false;
+			}
 			f = new CEmbedding(Uid(uid), dim, toks, vocab);
 			if (!r.getFloats(&re, (size_t) dim * vocab) || !r.getFloats(&im, (size_t) dim * vocab)) { delete f; fail(CNB_ERR_ARG, "restore: truncated planes"); return false; }
 			break;
 		}
 		case isLinear: {
 			int32_t in1, in2;
-			if (!r.get32(&in1) || !r.get32(&in2) || in1 <= 0 || in2 % in1) { fail(CNB_ERR_ARG, "restore: bad Linear record"); return false; }
+			if (!r.get32(&in1) || !r.get32(&in2) || in1 <= 0 || in2 <= 0 || in2 % in1) { fail(CNB_ERR_ARG, "restore: bad Linear record"); return false; }
 			f = new Linear(Uid(uid), InSize(in1), InSize(in2));
 			break;
 		}

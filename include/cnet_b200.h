@@ -183,6 +183,10 @@ int cnb_hadamard_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
  * partials live in a 2 MiB array built into the library (per GPU that loads it, until exit).
  * Limit: N <= CNB_STATIC_MAX_N, else CNB_ERR_ARG with a message.  The first call on a device
  * looks up the array's device address (make that call before any stream capture starts).
+ * With CUDA's lazy module loading that first call is also when the driver materialises the
+ * module's data segment on that device (the 2 MiB array included): "allocates nothing" holds
+ * from the second call on a device onwards.  The buffers must live on the current device
+ * (checked; CNB_ERR_ARG otherwise).
  * All calls share the one array, so two calls that overlap on the GPU (different streams)
  * race; contents from the previous call are never read. */
 #define CNB_STATIC_MAX_N 4096

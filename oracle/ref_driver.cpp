@@ -115,7 +115,8 @@ int ref_zero_wgrads(void* h) {
 // One batch of the reference's per-sample loop.  main_uid is the data CInput
 // (x planes [B, n]) or the CEmbedding (tokens [B, tok_per_sample], <0 = pad).
 // record != 0 keeps every function's output and the gradients of that output
-// for each sample.
+// for each sample; record == 2 leaves out the weight inputs (their "output" is the
+// weight itself, B copies of which are gigabytes at the benchmark widths).
 int ref_run_batch(void* h, int main_uid, const float* xre, const float* xim,
 		const int* tokens, int tok_per_sample, const int* labels, int B,
 		float* losses, int record) {
@@ -134,6 +135,7 @@ int ref_run_batch(void* h, int main_uid, const float* xre, const float* xim,
 		for (int uid : r->uids) {
 			CFunc* f = fn(r, uid);
 			if (!f->no_outputs()) continue;
+			if (record == 2 && f->isInput() && f != in) continue;
 			Record& rc = r->rec[uid];
 			rc.out_size = f->outSize();
 			size_t n = (size_t) B * rc.out_size;

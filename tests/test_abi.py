@@ -85,3 +85,18 @@ def test_case_inputs_are_deterministic():
     b = util.case_inputs("embed_lm_small")
     assert np.array_equal(a[2][0][0], b[2][0][0])
     assert a[2][0][0][0, -1] == -1
+
+
+def test_reference_style_user_layer_compiles_and_is_refused(built_lib, tmp_path):
+    """tests/cpp/user_layer_probe.cpp: a layer with the reference's dz / dz_star contract compiles against
+    the facade header; CNet::add refuses it with a message unless it runs its own device kernels."""
+    import subprocess
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / "probe")
+    libdir = os.path.dirname(built_lib)
+    env = dict(os.environ)
+    env.pop("CXX", None)
+    subprocess.run(["g++", "-std=c++17", "-I/usr/local/cuda/include", os.path.join(here, "cpp", "user_layer_probe.cpp"),
+                    "-o", exe, "-L" + libdir, "-l:libcnet_b200.so", "-Wl,-rpath," + libdir], check=True, env=env)
+    r = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout

@@ -77,3 +77,18 @@ def test_restore_rejects_garbage(built_lib, tmp_path):
         Net.restore(p)
     with pytest.raises(CnetError):
         Net.restore(tmp_path / "missing.cnet")
+
+
+def test_restore_rejects_corrupt_lengths(built_lib, tmp_path):
+    """Lengths come from the file: negative or absurd ones must be refused with a message, not sized."""
+    import struct
+    from cnet_b200.lib import CnetError
+    good = bytearray(open(FIXTURE, "rb").read())
+    # first record: magic | type | uid | input length | out size | #producers | dim | tokens | vocab
+    for field, value in ((3, -5), (3, 0x7FFFFFF0), (4, -1), (2, -7), (6, -8), (8, 0x7FFFFFF0)):
+        bad = bytearray(good)
+        bad[4 * field:4 * field + 4] = struct.pack(">i", value)
+        p = tmp_path / ("bad_%d_%d.cnet" % (field, value & 0xFFFF))
+        p.write_bytes(bytes(bad))
+        with pytest.raises(CnetError, match="corrupt|truncated"):
+            Net.restore(p)

@@ -203,3 +203,50 @@ def test_infer_gives_the_losses_without_touching_gradients():
     assert not np.allclose(net.losses(), want)
     assert np.array_equal(net.get_record(spec.layers["lin"], 1)[0], gs1[0])   # seed of the last backward untouched
     assert np.array_equal(net.get_wgrad(spec.layers["w"])[0], g1[0])
+
+
+def test_stale_graph_replay_is_refused():
+    """What a captured step froze (row count, 'weights already split', Adam's step count) is checked at
+    replay: a different batch, weights set from the host, or a captured adamUpdate fail with a message."""
+    import torch
+    from cnet_b200.dp import DataParallelTrainer
+    from cnet_b200.lib import CnetError
+    tr = DataParallelTrainer(configs.build_mixer, dict(n=128, blocks=1, m=10), global_batch=32, lr=0.5, device=0, seed=0)
+    (xr, xi), labels = configs.make_batch(tr.spec, 32, 0)
+    tr.step((xr, xi), labels)
+    tr.capture()
+    tr.step((xr, xi), labels)                              # replay at the captured batch: fine
+    tr.net.upload(x=(xr[:16].copy(), xi[:16].copy()), labels=labels[:16].copy())
+    with pytest.raises(CnetError, match="sized for 32"):
+        tr.net.graph_launch()
+    tr.net.upload(x=(xr, xi), labels=labels)
+    tr.net.graph_launch()
+    w = tr.net.get_values(tr.spec.layers["w0"])
+    tr.net.set_values(tr.spec.layers["w0"], w[0], w[1])
+    with pytest.raises(CnetError, match="set from the host"):
+        tr.net.graph_launch()
+    tr.capture()                                           # a fresh capture clears it
+    tr.net.graph_launch()
+    tr.net.capture_begin()
+    with pytest.raises(CnetError, match="adamUpdate"):
+        tr.net.adam_update(0.1, 0.9, 0)
+    tr.net.capture_end()
+    torch.cuda.synchronize()
+
+
+def test_second_backward_before_update_is_refused_when_gradients_are_reduced_in_place():
+    from cnet_b200.lib import CnetError
+    net = Net()
+    spec = configs.build_classifier(net, n=64, m=10)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    net.allocate(8)
+    seen = []
+    net.set_bucket_hook(lambda ptr, count, b, nb: seen.append((b, nb)) or 0)
+    x, labels = configs.make_batch(spec, 8, 0)
+    net.run_batch(spec.main, x=x, labels=labels)
+    assert seen and seen[-1][0] == seen[-1][1] - 1
+    with pytest.raises(CnetError, match="second backward"):
+        net.run_batch(spec.main, x=x, labels=labels)
+    net.update(0.01, 8)
+    net.run_batch(spec.main, x=x, labels=labels)           # after the update the next step is fine

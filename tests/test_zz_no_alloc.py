@@ -41,6 +41,13 @@ def test_static_scratch_entry_matches_arena_entry_on_two_calls():
             for got, want in zip(du + dv, du_ref + dv_ref):
                 err = float((got - want).norm() / want.norm())
                 assert err < 1e-6, (B, N, err)
+            # and directly against the definition in float64 (impl/hadamard.h:46-68): du* = g* o conj(v),
+            # dv* = sum over the batch of g* o conj(u)
+            g64, u64 = g[0].double() + 1j * g[1].double(), u[0].double() + 1j * u[1].double()
+            v64 = v[0].double() + 1j * v[1].double()
+            for got, want in (((du[0].double() + 1j * du[1].double()), g64 * v64.conj()),
+                              ((dv[0].double() + 1j * dv[1].double()), (g64 * u64.conj()).sum(0))):
+                assert float((got - want).abs().pow(2).sum().sqrt() / want.abs().pow(2).sum().sqrt()) < 1e-5
             # accumulate form: adds onto what is there
             rc = lib.cnb_hadamard_bwd_static(_p(g[0]), _p(g[1]), _p(u[0]), _p(u[1]), _p(v[0]), _p(v[1]),
                                              None, None, 0, _p(dv[0]), _p(dv[1]), 1, B, N, stream)

@@ -128,3 +128,102 @@ def compare(got, want, tol_act, tol_grad, skip_missing=True, label=""):
             if not e <= tol_act:
                 bad.append((k, e, tol_act))
     assert not bad, "%s: tensors beyond tolerance: %s" % (label, bad)
+
+
+# ----------------------------------------------------------------- benchmark widths
+# The benchmark configurations at their full widths.  The reference CPU path does the first
+# WIDTH_ROWS samples of the seeded batch (samples are independent, impl/cnet.h:366-411) and the
+# fixtures keep WIDTH_SAMPLES seeded entries of every tensor; the device runs the whole batch
+# (activations, per-sample dL/dz*) and a batch of those rows alone (accumulated weight gradients,
+# post-update weights).
+# name -> (builder, kwargs, benchmark batch, input kind)
+WIDTH_CASES = {
+    "width_classifier_784": (configs.build_classifier, dict(n=784, m=10), 64, "image"),
+    "width_linear_4096": (configs.build_linear, dict(n_in=4096, n_out=4096), 4096, "fanin"),
+    "width_mixer_1024x8": (configs.build_mixer, dict(n=1024, blocks=8, m=10), 512, "normal"),
+    "width_embed_lm": (configs.build_embed_lm, dict(tokens=64, vocab=8192, dim=256, hidden=2048), 1024, None),
+}
+WIDTH_ROWS = 64
+WIDTH_SAMPLES = 1024
+# one update with a step large enough that the weight change is well above the fp32 rounding of the
+# reference's own weights (at lr 0.01 the change is ~1e-6 of a weight of ~0.03)
+WIDTH_LR = 1.0
+
+
+def sample_index(key, size):
+    """The seeded flat indices of tensor `key` kept by the width fixtures."""
+    import zlib
+    if size <= WIDTH_SAMPLES:
+        return np.arange(size)
+    r = np.random.Generator(np.random.Philox(key=[zlib.crc32(key.encode()), 4242]))
+    return np.sort(r.integers(0, size, WIDTH_SAMPLES))
+
+
+def _sampled(out, key, pair, rows=None):
+    re, im = (np.asarray(p) for p in pair)
+    if rows is not None:
+        re, im = re[:rows], im[:rows]
+    idx = sample_index(key, re.size)
+    out[key + "_re"] = re.reshape(-1)[idx].astype(np.float32)
+    out[key + "_im"] = im.reshape(-1)[idx].astype(np.float32)
+
+
+def width_batch(name, rows=None):
+    builder, kw, B, kind = WIDTH_CASES[name]
+
+    class _Shape:
+        def __init__(self):
+            self.n = 0
+
+        def add(self, *a, **k):
+            self.n += 1
+            return self.n
+    spec = builder(_Shape(), **kw)
+    data, labels = configs.make_batch(spec, B, seed=0, step=0, kind=kind)
+    if rows is not None:
+        data = data[:rows].copy() if spec.tokens else (data[0][:rows].copy(), data[1][:rows].copy())
+        labels = labels[:rows].copy()
+    return spec, data, labels
+
+
+def run_width_case(net, name, batch, weights=None, alloc=None, record=True, train=True):
+    """One step of a width case on `net` at `batch` rows (the first rows of the seeded benchmark
+    batch); returns the sampled tensors of its first WIDTH_ROWS rows.  train: also the sampled
+    weight gradients and the sampled weight change of one update (lr / batch)."""
+    builder, kw, _, _ = WIDTH_CASES[name]
+    spec = builder(net, **kw)
+    if weights is None:
+        weights = configs.init_weights(spec, seed=0)
+    for uid, (re, im) in weights.items():
+        net.set_values(uid, re, im)
+    if alloc:
+        alloc(net, batch)
+    _, data, labels = width_batch(name, batch)
+    rows = min(batch, WIDTH_ROWS)
+    if spec.tokens:
+        losses = net.run_batch(spec.main, tokens=data, labels=labels, record=record)
+    else:
+        losses = net.run_batch(spec.main, x=data, labels=labels, record=record)
+    out = {"loss": np.asarray(losses, np.float64)[:rows]}
+    weight_uids = {u for u, _, _ in spec.weights}
+    for lname, uid in spec.layers.items():
+        if lname == "ce" or (uid in weight_uids and uid != spec.main):
+            continue
+        try:
+            a = net.get_record(uid, 0)
+            g = net.get_record(uid, 1)
+        except Exception:          # tensor fused away on the device / not recorded
+            continue
+        _sampled(out, "act_" + lname, a, rows)
+        _sampled(out, "gstar_" + lname, g, rows)
+    if train:
+        for lname, uid in spec.layers.items():
+            if uid in weight_uids:
+                _sampled(out, "wgrad_" + lname, net.get_wgrad(uid))
+        net.update(WIDTH_LR, batch)
+        for lname, uid in spec.layers.items():
+            if uid in weight_uids:
+                v = net.get_values(uid)
+                w0 = weights[uid]
+                _sampled(out, "delta_" + lname, (v[0].astype(np.float64) - w0[0], v[1].astype(np.float64) - w0[1]))
+    return out
