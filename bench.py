@@ -13,6 +13,14 @@ update.  One step = one pass over one synthetic batch.  Prints ONE JSON line on 
            the per-sample losses inside the timed region.
 `--impl reference`: the reference's own CPU implementation (oracle/_ref, built from the reference
            sources) on the host cores, on a bounded sample of the same workload.
+
+Timing: `--steps K` steps between a barrier + synchronize on both sides, CUDA events on the stream the
+step is launched on, max over ranks; that K-step measurement is repeated `--repeats` times (a fixed
+count, so that every N runs the same number of updates) and the MEDIAN is reported, with nvidia-smi
+clocks sampled over the whole timed region.  `e2e` is host wall-clock time around the same number of
+pipelined steps including the final wait for the losses.  `loss_global` is the mean loss of the WHOLE
+batch (summed over the ranks) after the last timed resident step: the same number at every N up to
+fp32 reassociation.
 """
 import argparse
 import json
@@ -67,12 +75,12 @@ class _Clocks:
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, interval_ms=100):
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q,
-                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                       "--format=csv,noheader,nounits", "-lms", str(interval_ms)],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             pass
@@ -115,6 +123,8 @@ def run_reference(args):
     if not ref.available():
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libcnet_ref.so is not built"}))
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks: use every host core, as at N = 1
+    ref.set_threads(os.cpu_count() or 1)
     net = ref.RefNet()
     spec = builder(net, **kw)
     for uid, (re, im) in configs.init_weights(spec, 0).items():
@@ -164,6 +174,9 @@ def cpu_baseline(workload, seconds=15.0):
     if not ref.available():
         return None
     builder, kw, gbatch, kind = WORKLOADS[workload]
+    if builder is None:
+        builder = configs.build_linear      # config 2 as a net: the three products + a loss on top
+    ref.set_threads(os.cpu_count() or 1)
     net = ref.RefNet()
     spec = builder(net, **kw)
     for uid, (re, im) in configs.init_weights(spec, 0).items():
@@ -187,13 +200,64 @@ def cpu_baseline(workload, seconds=15.0):
 # (dram__bytes_read.sum + dram__bytes_write.sum), keyed by (M, N, K); None where not captured.
 NCU_TRAFFIC_BYTES = {(4096, 1024, 1024): 114.9e6}
 
+_TF32 = {}
 
-def _time_launches(torch, fn, reps=20):
-    """Average device time of fn() in ms: CUDA events on the launching stream, L2 flushed in between."""
+
+def _tf32_peak(torch, gpu_index):
+    """Dense TF32 throughput of this GPU, measured the way MEASURED_PEAKS.json's bf16 figure was: torch.matmul
+    (cuBLAS, fp32 operands with TF32 allowed) at 8192^3, best of 10 launches (burst) and back to back for ~2 s
+    (sustained), clocks sampled during the sustained loop.  A measuring stick only: no kernel of the path uses it."""
+    if _TF32:
+        return _TF32
+    n = 8192
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        c = torch.empty(n, n, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        best = 1e30
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        clocks = _Clocks(gpu_index, interval_ms=50)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count = 0
+        t0 = time.perf_counter()
+        e0.record()
+        while time.perf_counter() - t0 < 2.0:
+            for _ in range(25):
+                torch.matmul(a, b, out=c)
+            count += 25
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        clk = clocks.stop()
+        flops = 2.0 * n ** 3
+        _TF32.update({"tf32_tflops": flops / (best * 1e-3) / 1e12,
+                      "tf32_tflops_sustained": flops * count / (e0.elapsed_time(e1) * 1e-3) / 1e12,
+                      "sm_mhz_sustained": clk.get("sm_mhz"), "reasons_sustained": clk.get("reasons"),
+                      "how": "torch.matmul fp32 with TF32 allowed, 8192^3: best of 10 (burst), back to back for 2 s (sustained)"})
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    del a, b, c
+    return _TF32
+
+
+def _time_launches(torch, fn, reps=20, clocks_for=None):
+    """Average device time of fn() in ms: CUDA events on the launching stream, L2 flushed in between.
+    clocks_for = GPU index: also the median SM clock sampled while the loop runs."""
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
     clean = torch.zeros(40 << 20, dtype=torch.float32, device="cuda")
     for _ in range(3):
         fn()
+    sampler = _Clocks(clocks_for, interval_ms=20) if clocks_for is not None else None
     tot = 0.0
     for _ in range(reps):
         flush.zero_()          # evict the working set ...
@@ -204,10 +268,30 @@ def _time_launches(torch, fn, reps=20):
         e1.record()
         torch.cuda.synchronize()
         tot += e0.elapsed_time(e1)
+    if sampler is not None:
+        return tot / reps, sampler.stop().get("sm_mhz")
     return tot / reps
 
 
-def _roofline(args, kw, B, gbatch, step_ms, device):
+def _tensor_roof(torch, peaks, dur, mhz, B, n_out, n_in, gpu_index):
+    flops = 8.0 * B * n_in * n_out
+    achieved = flops / (dur * 1e-3) / 1e12
+    tf = _tf32_peak(torch, gpu_index)
+    peak = tf["tf32_tflops"] / 3.0          # 3xTF32: three TF32 MMAs per real product
+    derived = peaks["bf16"] / 6.0           # what the peaks file alone gives: TF32 = bf16 / 2
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "frac_derived": achieved / derived, "peak_derived": derived,
+            "frac_sustained": achieved / (tf["tf32_tflops_sustained"] / 3.0),
+            "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)), "kernel": "cgemm_tc_k (tcgen05 3xTF32)",
+            "shape": [B, n_out, n_in], "ms_per_launch": dur, "sm_mhz_during": mhz,
+            "ms_x_mhz": (dur * mhz) if mhz else None, "tf32_peak": tf,
+            "peak_note": "dense TF32 measured in this run (cuBLAS 8192^3 burst %.1f TFLOP/s, sustained %.1f at %s MHz) / 3; "
+                         "frac_derived = against bf16 burst %.1f / 6 of %s"
+                         % (tf["tf32_tflops"], tf["tf32_tflops_sustained"], tf["sm_mhz_sustained"], peaks["bf16"],
+                            peaks["source"])}
+
+
+def _roofline(workload, kw, B, gbatch, step_ms, device, hbm_kernels=True):
     """The dominant kernel of the step (the complex GEMM of the Linear layers, or the skinny head kernel
     when the net has no square Linear) at this rank's shape, plus the HBM-bound kernels of one block."""
     import torch
@@ -215,9 +299,9 @@ def _roofline(args, kw, B, gbatch, step_ms, device):
     peaks = _peaks()
     ctx = Context(device=device, arena_bytes=2 << 30)
     n = kw.get("n", 1024)
-    if args.workload.startswith("embed"):
+    if workload.startswith("embed"):
         n_in, n_out = kw["tokens"] * kw["dim"], kw["hidden"]
-    elif args.workload.startswith("classifier"):
+    elif workload.startswith("classifier"):
         n_in, n_out = kw["n"], kw["m"]
     else:
         n_in, n_out = n, n
@@ -227,33 +311,56 @@ def _roofline(args, kw, B, gbatch, step_ms, device):
     if ctx.lib.cnb_linear_split_ok(B, n_in, n_out):
         xs, ws = ctx.split(x), ctx.split(w)
         y = ctx._new(B, n_out)
-        dur = _time_launches(torch, lambda: ctx.linear_fwd_split(xs, ws, B, n_in, n_out, out=y))
-        flops = 8.0 * B * n_in * n_out
-        achieved = flops / (dur * 1e-3) / 1e12
-        peak = peaks["bf16"] / 6.0       # dense TF32 = bf16 / 2; 3xTF32 = three MMAs per real product
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)), "kernel": "cgemm_tc_k (tcgen05 3xTF32)",
-                "shape": [B, n_out, n_in], "ms_per_launch": dur,
-                "peak_note": "bf16 burst %.1f TFLOP/s / 6 (TF32 = bf16/2, 3 MMAs per product), of %s"
-                             % (peaks["bf16"], peaks["source"])}
+        dur, mhz = _time_launches(torch, lambda: ctx.linear_fwd_split(xs, ws, B, n_in, n_out, out=y), reps=200,
+                                  clocks_for=device)
+        roof = _tensor_roof(torch, peaks, dur, mhz, B, n_out, n_in, device)
     else:
-        y = None
         dur = _time_launches(torch, lambda: ctx.linear_fwd(x, w))
         nbytes = 8.0 * B * n_in + 8.0 * n_in * n_out + 8.0 * B * n_out
         achieved = nbytes / (dur * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm"], "traffic": None, "kernel": "skinny_fwd_k (fp32)",
                 "shape": [B, n_out, n_in], "ms_per_launch": dur, "peak_note": "copy bandwidth, of " + peaks["source"]}
-    roof["step_gemm_tflops"] = _gemm_flops(kw, gbatch, args.workload) / (step_ms * 1e-3) / 1e12
+    roof["step_gemm_tflops"] = _gemm_flops(kw, gbatch, workload) / (step_ms * 1e-3) / 1e12
     # HBM-bound kernels at the same activation shape: algorithmic bytes / time, against the measured copy bandwidth
-    if not args.workload.startswith("embed"):
+    if hbm_kernels and workload.startswith("embed"):
+        T, D, V, H = kw["tokens"], kw["dim"], kw["vocab"], kw["hidden"]
+        table = tuple(torch.randn(V, D, device="cuda") * 0.02 for _ in range(2))
+        dtable = tuple(torch.zeros(V, D, device="cuda") for _ in range(2))
+        tok = torch.randint(0, V, (B, T), device="cuda", dtype=torch.int32)
+        labels = torch.randint(0, V, (B,), device="cuda", dtype=torch.int32)
+        ge = tuple(torch.randn(B, T * D, device="cuda") for _ in range(2))
+        z = tuple(torch.randn(B, V, device="cuda") for _ in range(2))
+        yv, inv = ctx.softmax_fwd(z)
+        a = tuple(torch.randn(B, H, device="cuda") for _ in range(2))
+        cases = [("embed_fwd_k (gather)", lambda: ctx.embed_fwd(table, tok), 16.0 * B * T * D),
+                 ("embed_bwd (scatter-add of dz* rows into the table)", lambda: ctx.embed_bwd(ge, tok, dtable), 16.0 * B * T * D),
+                 ("softmax_fwd_k (L2 normalise)", lambda: ctx.softmax_fwd(z), 16.0 * B * V),
+                 ("softmax_bwd_k", lambda: ctx.softmax_bwd(z, z, inv), 24.0 * B * V),
+                 ("crossent_k (loss + dz* seed)", lambda: ctx.crossent(yv, labels), 16.0 * B * V),
+                 ("gelu_fwd_k", lambda: ctx.gelu_fwd(a), 16.0 * B * H),
+                 ("gelu_bwd_k", lambda: ctx.gelu_bwd(a, a), 24.0 * B * H)]
+        for name, fn, nbytes in cases:
+            d = _time_launches(torch, fn, reps=10)
+            gbs = nbytes / (d * 1e-3) / 1e9
+            hbm.append({"kernel": name, "GB/s": round(gbs, 1), "frac": round(gbs / peaks["hbm"], 3), "ms": round(d, 4)})
+        # the second product of the net at its shape (K = hidden)
+        x2 = tuple(torch.randn(B, H, device="cuda") for _ in range(2))
+        w2 = tuple(torch.randn(V, H, device="cuda") * H ** -0.5 for _ in range(2))
+        xs2, ws2 = ctx.split(x2), ctx.split(w2)
+        y2 = ctx._new(B, V)
+        d2 = _time_launches(torch, lambda: ctx.linear_fwd_split(xs2, ws2, B, H, V, out=y2), reps=10)
+        roof["second_gemm"] = {"shape": [B, V, H], "ms_per_launch": d2,
+                               "frac": 8.0 * B * H * V / (d2 * 1e-3) / 1e12 / roof["peak"]}
+    elif hbm_kernels:
         N = n_in
         u, g = x, tuple(torch.randn(B, N, device="cuda") for _ in range(2))
         h = tuple(torch.randn(N, device="cuda") for _ in range(2))
         a, yy = ctx.hadamard_gelu_fwd(u, h)
+        fft_name = "fft1024_pipe_k<-1> (FourierTrans forward)" if N == 1024 else "FourierTrans forward (N = %d)" % N
         cases = [("hadamard_gelu_fwd_k", lambda: ctx.hadamard_gelu_fwd(u, h), 24.0 * B * N),
                  ("colreduce_stage1_k<1> (gelu'+hadamard bwd + dh* partials)", lambda: ctx.hadamard_gelu_bwd(g, a, u, h), 32.0 * B * N),
-                 ("fft_rr_k / dft fwd", lambda: ctx.dft_fwd(u), 16.0 * B * N)]
+                 (fft_name, lambda: ctx.dft_fwd(u), 16.0 * B * N)]
         n_w = 2 * n_in * n_out * max(1, kw.get("blocks", 1))       # the whole weight arena of the net
         wflat = torch.randn(n_w, device="cuda")
         gflat = torch.randn(n_w, device="cuda")
@@ -267,13 +374,20 @@ def _roofline(args, kw, B, gbatch, step_ms, device):
     return roof
 
 
-def run_linear(args):
+def _median(v):
+    v = sorted(v)
+    return v[len(v) // 2]
+
+
+def run_linear(args, steps=None, repeats=None, quiet=False):
     """Config 2: one complex Linear layer, forward plus both backward products, through the C-ABI
     operators (operands split once per step, three tensor-core GEMMs).  Single GPU."""
     import torch
     from cnet_b200 import lib as cl
     from cnet_b200.ops import Context
-    _, kw, B, _ = WORKLOADS[args.workload]
+    _, kw, B, _ = WORKLOADS["linear_4096"]
+    steps = steps or args.steps
+    repeats = repeats or args.repeats
     n_in, n_out = kw["n_in"], kw["n_out"]
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         raise SystemExit("linear_4096 is a single-GPU workload")
@@ -305,73 +419,79 @@ def run_linear(args):
         step()
         host_y.copy_(y[0][:, 0], non_blocking=False)
 
-    def timed(fn, steps):
+    def timed(fn, n):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for _ in range(n):
             fn()
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
+
+    def walled(fn, n):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+        return 1e3 * (time.perf_counter() - t0)
 
     upload()
     for _ in range(max(3, args.warmup)):
         step()
     clocks = _Clocks(0)
     l0 = lib.cnb_launch_count()
-    ms = timed(step, args.steps)
-    launches = lib.cnb_launch_count() - l0
-    clk = clocks.stop()
+    ms = _median([timed(step, steps) for _ in range(repeats)])
+    launches = (lib.cnb_launch_count() - l0) // repeats
     e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
+    ms_e2e = _median([walled(e2e_step, steps) for _ in range(max(1, repeats // 3))])
+    clk = clocks.stop()
     # parity spot check against float64 on a sample of outputs
     xs = (x[0][:8].double() + 1j * x[1][:8].double())
     want = xs @ (w[0].double() + 1j * w[1].double()).T
     err = float(((y[0][:8].double() + 1j * y[1][:8].double()) - want).norm() / want.norm())
     peaks = _peaks()
-    per_step = ms / args.steps
+    per_step = ms / steps
     tflops = 3 * 8.0 * B * n_in * n_out / (per_step * 1e-3) / 1e12
     xs_, ws_ = ctx.split(x), ctx.split(w)
-    dur = _time_launches(torch, lambda: ctx.linear_fwd_split(xs_, ws_, B, n_in, n_out, out=y))
-    achieved = 8.0 * B * n_in * n_out / (dur * 1e-3) / 1e12
-    peak = peaks["bf16"] / 6.0
+    dur, mhz = _time_launches(torch, lambda: ctx.linear_fwd_split(xs_, ws_, B, n_in, n_out, out=y), reps=40, clocks_for=0)
+    roof = _tensor_roof(torch, peaks, dur, mhz, B, n_out, n_in, 0)
+    roof["step_gemm_tflops"] = tflops
     line = {
         "metric": "train samples/sec (fwd+bwd+update)", "value": B / (per_step * 1e-3), "unit": "samples/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
+        "n_gpus": 1, "steps": steps, "warmup": max(3, args.warmup), "repeats": repeats, "ms_per_step": per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "global_batch": B, **kw, "parallelism": "dp1",
+        "config": {"workload": "linear_4096", "global_batch": B, **kw, "parallelism": "dp1",
                    "note": "forward + dX* + dW* of one layer, no update (config 2 measures the three products)",
                    "l2": "operands and outputs (> 1 GB per step) exceed the 126 MB L2"},
-        "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
-                "h2d_bytes_per_step": sum(h.numel() * 4 for h in host), "d2h_bytes_per_step": B * 4},
-        "gpu_launches": int(launches), "clocks": clk,
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)), "kernel": "cgemm_tc_k (tcgen05 3xTF32)",
-                     "shape": [B, n_out, n_in], "ms_per_launch": dur, "step_gemm_tflops": tflops,
-                     "peak_note": "bf16 burst %.1f TFLOP/s / 6, of %s" % (peaks["bf16"], peaks["source"])},
-        "forward_relerr_vs_f64": err, "cpu_baseline": None,
+        "e2e": {"value": B / (ms_e2e / steps * 1e-3), "unit": "samples/s",
+                "h2d_bytes_per_step": sum(h.numel() * 4 for h in host), "d2h_bytes_per_step": B * 4,
+                "timed": "host wall clock, copies not pipelined"},
+        "gpu_launches": int(launches), "clocks": clk, "roofline": roof,
+        "forward_relerr_vs_f64": err,
     }
-    print(json.dumps(line))
     ctx.close()
+    del x, g, w, y, dx, dw
+    torch.cuda.empty_cache()
+    if not quiet:
+        line["cpu_baseline"] = None if args.no_cpu_baseline else cpu_baseline("linear_4096")
+        print(json.dumps(line))
+    return line
 
 
-def run_ours(args):
+def _measure(args, workload, steps, repeats, hbm_kernels=True):
+    """Times one workload on this rank's GPU (all ranks call it together) and returns the JSON line's fields."""
+    import gc
     import torch
     import torch.distributed as dist
     from cnet_b200 import lib as cl
     from cnet_b200.dp import DataParallelTrainer
-    from cnet_b200.ops import Context
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the path has no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    builder, kw, gbatch, kind = WORKLOADS[args.workload]
+    builder, kw, gbatch, kind = WORKLOADS[workload]
     assert gbatch % world == 0
     B = gbatch // world
     lib = cl.load()
@@ -398,20 +518,35 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(trainer.stream)          # the stream every kernel of the step is launched on
-        for _ in range(steps):
-            fn()
-        e1.record(trainer.stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
+    def over_ranks(ms):
         if world > 1:
             t = torch.tensor([ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
+
+    def timed(fn, n):
+        """Exactly n steps between barrier + synchronize on both sides: CUDA events on the launching stream."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(trainer.stream)          # the stream every kernel of the step is launched on
+        for _ in range(n):
+            fn()
+        e1.record(trainer.stream)
+        barrier()
+        return over_ranks(e0.elapsed_time(e1))
+
+    def walled(fn, n, finish):
+        """The same n steps by the host's clock, up to the arrival of the last step's losses."""
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        finish()
+        torch.cuda.synchronize()
+        ms = 1e3 * (time.perf_counter() - t0)
+        barrier()
+        return over_ranks(ms)
 
     trainer.upload(host_in, host_labels)
     trainer.step_resident()
@@ -421,12 +556,21 @@ def run_ours(args):
         trainer.step_resident()
     clocks = _Clocks(local) if rank == 0 else None
     l0 = lib.cnb_launch_count()
-    ms = timed(trainer.step_resident, args.steps)
-    launches = lib.cnb_launch_count() - l0
+    all_ms = [timed(trainer.step_resident, steps) for _ in range(repeats)]
+    ms = _median(all_ms)
+    launches = (lib.cnb_launch_count() - l0) // repeats
     if trainer.kernels_per_step():
-        launches = trainer.kernels_per_step() * args.steps      # replayed from the captured graph
-    clk = clocks.stop() if clocks else None
+        launches = trainer.kernels_per_step() * steps      # replayed from the captured graph
     trainer.net.sync()
+    # mean loss of the WHOLE batch under the weights all those updates produced (forward only)
+    with torch.cuda.stream(trainer.stream):
+        trainer.net.infer()
+    trainer.net.sync()
+    tot = torch.tensor([float(trainer.net.losses(B).astype(np.float64).sum())], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tot)
+    loss_global = float(tot.item()) / gbatch
+    updates = 1 + max(3, args.warmup) + repeats * steps
 
     # end to end: every step copies its batch from pinned host memory (on the copy stream, overlapping the
     # previous step) and brings its per-sample losses back to the host
@@ -440,27 +584,76 @@ def run_ours(args):
     trainer.prefetch(host_in, host_labels)
     for _ in range(2):
         e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
-    trainer.net.wait_losses()
+    e2e_ms = _median([walled(e2e_step, steps, trainer.net.wait_losses) for _ in range(max(1, repeats // 3))])
+    clk = clocks.stop() if clocks else None
     loss_mean = float(bufs[(it[0] - 1) & 1].mean())
+    per_step = ms / steps
+    out = {"value": gbatch / (per_step * 1e-3), "ms_per_step": per_step, "world": world, "B": B, "h2d": h2d,
+           "e2e_value": gbatch / (e2e_ms / steps * 1e-3), "launches": int(launches), "clocks": clk,
+           "loss_rank0": loss_mean, "loss_global": loss_global, "updates_before_loss_global": updates,
+           "ms_all": [round(m / steps, 5) for m in all_ms], "kw": kw, "gbatch": gbatch}
+    del trainer
+    gc.collect()
+    torch.cuda.empty_cache()
+    out["roofline"] = _roofline(workload, kw, B, gbatch, per_step, local, hbm_kernels) if rank == 0 else None
+    return out
 
-    roof = _roofline(args, kw, B, gbatch, ms / args.steps, local) if rank == 0 else None
 
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    m = _measure(args, args.workload, args.steps, args.repeats)
+    others = {}
+    if world == 1 and args.workload == "mixer_dp4096" and not args.no_workloads:
+        # the other benchmark configurations, briefly (5 steps x 3), so that each has a witnessed number
+        for name in ("classifier_b64", "linear_4096", "mixer_b512", "embed_lm_b1024"):
+            try:
+                if WORKLOADS[name][0] is None:
+                    ln = run_linear(args, steps=5, repeats=3, quiet=True)
+                    others[name] = {"value": ln["value"], "ms_per_step": ln["ms_per_step"], "e2e": ln["e2e"]["value"],
+                                    "kernel": ln["roofline"]["kernel"], "roofline_frac": ln["roofline"]["frac"],
+                                    "roofline_bound": "tensor", "gpu_launches_per_step": ln["gpu_launches"] // 5}
+                    continue
+                o = _measure(args, name, 5, 3, hbm_kernels=name.startswith("embed"))
+                r = o["roofline"]
+                others[name] = {"value": o["value"], "ms_per_step": o["ms_per_step"], "e2e": o["e2e_value"],
+                                "kernel": r["kernel"], "roofline_frac": r["frac"], "roofline_bound": r["bound"],
+                                "gpu_launches_per_step": o["launches"] // 5, "loss_global": o["loss_global"]}
+                if r.get("hbm_kernels"):
+                    others[name]["hbm_kernels"] = r["hbm_kernels"]
+                if r.get("second_gemm"):
+                    others[name]["second_gemm"] = r["second_gemm"]
+            except Exception as e:           # a side workload must not take the headline line with it
+                others[name] = {"error": "%s: %s" % (type(e).__name__, e)}
     if rank == 0:
-        per_step = ms / args.steps
         line = {
-            "metric": "train samples/sec (fwd+bwd+update)", "value": gbatch / (per_step * 1e-3), "unit": "samples/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": per_step,
+            "metric": "train samples/sec (fwd+bwd+update)", "value": m["value"], "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "repeats": args.repeats,
+            "ms_per_step": m["ms_per_step"], "ms_per_step_all": m["ms_all"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": args.workload, "global_batch": gbatch, "per_gpu_batch": B, **kw,
+            "config": {"workload": args.workload, "global_batch": m["gbatch"], "per_gpu_batch": m["B"], **m["kw"],
                        "parallelism": "dp%d" % world, "lr": LR, "cuda_graph": not args.no_graph,
                        "l2": "per-step working set (activations + gradients, > 1 GB) exceeds the 126 MB L2"},
-            "e2e": {"value": gbatch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * 4},
-            "gpu_launches": int(launches), "clocks": clk, "roofline": roof, "loss": loss_mean,
+            "e2e": {"value": m["e2e_value"], "unit": "samples/s",
+                    "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["B"] * 4,
+                    "timed": "host wall clock around the pipelined steps and the wait for the last losses"},
+            "gpu_launches": m["launches"], "clocks": m["clocks"], "roofline": m["roofline"],
+            "loss": m["loss_rank0"], "loss_global": m["loss_global"],
+            "updates_before_loss_global": m["updates_before_loss_global"],
             "cpu_baseline": cpu_baseline(args.workload) if world == 1 and not args.no_cpu_baseline else None,
         }
+        if others:
+            line["workloads"] = others
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -473,7 +666,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixer_dp4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--repeats", type=int, default=15,
+                    help="the K-step measurement is repeated this many times and the median reported")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--no-graph", action="store_true", help="launch the step kernel by kernel instead of as a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

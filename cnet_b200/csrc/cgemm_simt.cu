@@ -13,6 +13,7 @@ cgemm_simt_k(const float* __restrict__ a_re, const float* __restrict__ a_im, lon
              const float* __restrict__ b_re, const float* __restrict__ b_im, long sbn, long sbk, int conjB,
              const float* __restrict__ r_re, const float* __restrict__ r_im,
              float* __restrict__ d_re, float* __restrict__ d_im, int M, int N, int K, int accumulate) {
+    cnb_pdl_enter();
     __shared__ float As_r[TK][TM + 4], As_i[TK][TM + 4], Bs_r[TK][TN + 4], Bs_i[TK][TN + 4];
     int tid = threadIdx.x;
     int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -82,7 +83,7 @@ int cgemm_simt(cnb_ctx* ctx, const float* a_re, const float* a_im, long sam, lon
                float* d_re, float* d_im, int M, int N, int K, int accumulate, cudaStream_t st) {
     (void) ctx;
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
-    cgemm_simt_k<<<grid, 256, 0, st>>>(a_re, a_im, sam, sak, b_re, b_im, sbn, sbk, conjB, r_re, r_im, d_re, d_im,
+    cnb::launch(cgemm_simt_k, dim3(grid), dim3(256), 0, st, 1, a_re, a_im, sam, sak, b_re, b_im, sbn, sbk, conjB, r_re, r_im, d_re, d_im,
                                        M, N, K, accumulate);
     CNB_LAUNCH_CHECK("cgemm_simt");
     return CNB_OK;

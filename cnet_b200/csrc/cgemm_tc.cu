@@ -348,10 +348,19 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                      "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (warp == 0 && lane < 8) {   // descriptor fetch of the 8 operand maps, off the first TMA's critical path
+        const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_lo_re, &a_lo_im, &b_hi_re, &b_hi_im, &b_lo_re, &b_lo_im};
+        asm volatile("prefetch.tensormap [%0];" ::"l"(maps[lane]) : "memory");
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched no memory another kernel writes: under programmatic dependent launch it ran
+    // while the kernel before this one in the stream was finishing.  Operands, residual and old D are read
+    // (and D written) only after that kernel has completed.
+    cnb_pdl_trigger();
+    cnb_pdl_wait();
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -625,6 +634,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
 // hi = x with the low 13 mantissa bits cleared, lo = x - hi; optionally transposed ([R,C] -> [C,R]).
 __global__ void split_k(const float* __restrict__ s0, const float* __restrict__ s1, float* __restrict__ hi0,
                         float* __restrict__ hi1, float* __restrict__ lo0, float* __restrict__ lo1, size_t n) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * 4;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
         if (i + 3 < n) {
@@ -653,6 +663,7 @@ __global__ void split_k(const float* __restrict__ s0, const float* __restrict__ 
 __global__ void split_transpose_k(const float* __restrict__ s0, const float* __restrict__ s1,
                                   float* __restrict__ hi0, float* __restrict__ hi1, float* __restrict__ lo0,
                                   float* __restrict__ lo1, int R, int C) {
+    cnb_pdl_enter();
     __shared__ float t0[32][33], t1[32][33];
     int c = blockIdx.x * 32 + threadIdx.x;
     for (int k = threadIdx.y; k < 32; k += 8) {
@@ -726,6 +737,7 @@ int make_map_mn(CUtensorMap* m, const float* base, int rows, int K) {
 
 // Clears the two output planes of a product whose tiles are summed with atomics.
 __global__ void zero_pair_k(float* __restrict__ a, float* __restrict__ b, size_t n) {
+    cnb_pdl_enter();
     const size_t n4 = n / 4;
     const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
     const size_t tid = (size_t) blockIdx.x * blockDim.x + threadIdx.x, step = (size_t) gridDim.x * blockDim.x;
@@ -756,7 +768,7 @@ size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
 
 void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* const dst[4], size_t n, cudaStream_t st) {
     size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
-    split_k<<<(int) (blocks < cap ? blocks : cap), 256, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], n);
+    cnb::launch(split_k, dim3((unsigned) (blocks < cap ? blocks : cap)), dim3(256), 0, st, 1, s0, s1, dst[0], dst[1], dst[2], dst[3], n);
 }
 
 // The GEMM proper on operands that are already split: a[4] / b[4] = hi_re, hi_im, lo_re, lo_im planes,
@@ -798,12 +810,24 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     //  * few tiles and short runs: a cluster per tile (below); otherwise plain stream-K.
     // K > 4096 keeps to stream-K runs: one fp32 accumulation chain in tensor memory that long costs accuracy.
     const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
-    const bool whole_tiles = (tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0) || full_wave;
+    const bool whole_tiles = (tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0 && k_blocks <= 256) || full_wave;
     const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
     long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
     if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
     long upc = (total + ctas - 1) / ctas;
     if (whole_tiles) upc = k_blocks;
+    // The tensor core adds into its fp32 accumulator with truncation, so the error of one accumulation chain
+    // in tensor memory grows with its length: measured ~2e-6 of the accumulator's magnitude per k-block, which
+    // reached 1e-3 on a 443-k-block chain whose accumulator one large term dominated (the gradient of a loss
+    // through a K = 8192 product).  Runs are therefore capped at kMaxChain k-blocks (the partial tiles are summed
+    // outside, in fp32 round-to-nearest): several equal waves of CTAs instead of one persistent wave.
+    // Only K > 4096 gets here with longer runs; a whole tile of K <= 4096 is at most 256 k-blocks.
+    constexpr long kMaxChain = 64;
+    if (!whole_tiles && upc > kMaxChain && k_blocks > 256) {
+        const long waves = (total + (long) sms * kMaxChain - 1) / ((long) sms * kMaxChain);
+        ctas = (long) sms * waves;
+        upc = (total + ctas - 1) / ctas;
+    }
     ctas = (total + upc - 1) / upc;
     int whole_per_cta = 0;
     int clear_from_row = 0;                              // rows of D below this one are only ever stored whole
@@ -832,7 +856,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         const size_t plane = (size_t) M * N - first;
         const size_t vec = plane / 4 + 1;
         const int blocks = (int) std::min<size_t>((vec + 255) / 256, (size_t) ctx->sm_count * 8);
-        zero_pair_k<<<blocks, 256, 0, st>>>(d_re + first, d_im + first, plane);
+        cnb::launch(zero_pair_k, dim3(blocks), dim3(256), 0, st, 1, d_re + first, d_im + first, plane);
         CNB_LAUNCH_CHECK("zero_pair");
     }
     TcParams p;
@@ -843,25 +867,8 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     p.cluster = cluster;
     p.whole_per_cta = whole_per_cta;
     p.status = ctx->d_status;
-    if (cluster > 1) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned) ctas);
-        cfg.blockDim = dim3(NUM_THREADS);
-        cfg.dynamicSmemBytes = SMEM_BYTES;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned) cluster;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        CNB_CUDA(cudaLaunchKernelEx(&cfg, cgemm_tc_k, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
-                                    maps[7], p));
-    } else {
-        cgemm_tc_k<<<(int) ctas, NUM_THREADS, SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
-                                                               maps[6], maps[7], p);
-    }
+    CNB_CUDA(cnb::launch(cgemm_tc_k, dim3((unsigned) ctas), dim3(NUM_THREADS), SMEM_BYTES, st, cluster, maps[0], maps[1], maps[2],
+                         maps[3], maps[4], maps[5], maps[6], maps[7], p));
     CNB_LAUNCH_CHECK("cgemm_tc");
     return CNB_OK;
 }
@@ -882,7 +889,7 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
         bool al = ((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) == 0;
         if (trans && !(rows % 32 == 0 && al)) {   // source is [K, rows] with ragged rows: transpose while splitting
             dim3 grid((rows + 31) / 32, (K + 31) / 32), block(32, 8);
-            split_transpose_k<<<grid, block, 0, st>>>(s0, s1, dst[0], dst[1], dst[2], dst[3], K, rows);
+            cnb::launch(split_transpose_k, grid, block, 0, st, 1, s0, s1, dst[0], dst[1], dst[2], dst[3], K, rows);
         } else {
             if (!al) return set_error(CNB_ERR_ARG, "cgemm_tc: operand planes must be 16-byte aligned");
             *mn = trans;

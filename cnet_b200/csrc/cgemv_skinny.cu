@@ -32,6 +32,7 @@ template <int OT, int W>
 __global__ void __launch_bounds__(512)
 skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const float* __restrict__ wr,
              const float* __restrict__ wi, float* __restrict__ yr, float* __restrict__ yi, int B, int in, int out) {
+    cnb_pdl_enter();
     extern __shared__ __align__(16) float sw[];          // [out][in] re, then [out][in] im
     float* swr = sw;
     float* swi = sw + (size_t) out * in;
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(256, (OT * W > 40 ? 1 : 2))
 skinny_bwd_x_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ wr,
                const float* __restrict__ wi, float* __restrict__ dr, float* __restrict__ di, int B, int in, int out,
                int accumulate, int rows_per_chunk) {
+    cnb_pdl_enter();
     const int i = (blockIdx.x * 256 + threadIdx.x) * W;
     if (i >= in) return;
     float wre[OT][W], wim[OT][W];
@@ -166,6 +168,7 @@ __global__ void __launch_bounds__(256, (OT * W > 40 ? 1 : 2))
 skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi, const float* __restrict__ xr,
                       const float* __restrict__ xi, float* __restrict__ pr, float* __restrict__ pi, int B, int in,
                       int out, int rows_per_chunk) {
+    cnb_pdl_enter();
     __shared__ float sr[8][32 * W + 1], si[8][32 * W + 1];
     const int col = (blockIdx.x * 32 + threadIdx.x) * W;
     const int r0 = blockIdx.y * rows_per_chunk, r1 = min(B, r0 + rows_per_chunk);
@@ -220,6 +223,7 @@ skinny_bwd_w_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi
 // stage 2: 32 outputs x 8 chunk lanes per block, fixed summation order
 __global__ void skinny_bwd_w_stage2_k(const float* __restrict__ pr, const float* __restrict__ pi, float* __restrict__ dr,
                                       float* __restrict__ di, int chunks, size_t n, int accumulate) {
+    cnb_pdl_enter();
     __shared__ float sr[8][33], si[8][33];
     size_t e = (size_t) blockIdx.x * 32 + threadIdx.x;
     float a = 0.f, c = 0.f;
@@ -254,10 +258,10 @@ size_t skinny_workspace_bytes(int B, int in, int out, int sm_count) {
 // picks the instantiation whose output bound is the smallest one that covers `out`
 #define CNB_SKINNY_DISPATCH(KERNEL, W, ...)                                   \
     do {                                                                      \
-        if (out <= 4) KERNEL<4, W> __VA_ARGS__;                               \
-        else if (out <= 8) KERNEL<8, W> __VA_ARGS__;                          \
-        else if (out <= 10) KERNEL<10, W> __VA_ARGS__;                        \
-        else KERNEL<16, W> __VA_ARGS__;                                       \
+        if (out <= 4) cnb::launch(KERNEL<4, W>, __VA_ARGS__);                 \
+        else if (out <= 8) cnb::launch(KERNEL<8, W>, __VA_ARGS__);            \
+        else if (out <= 10) cnb::launch(KERNEL<10, W>, __VA_ARGS__);          \
+        else cnb::launch(KERNEL<16, W>, __VA_ARGS__);                         \
     } while (0)
 
 static bool aligned16(const void* a, const void* b, const void* c = nullptr, const void* d = nullptr) {
@@ -285,8 +289,8 @@ int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, 
     const long blocks = (pairs + warps - 1) / warps;
     const int grid = (int) std::max<long>(1, std::min<long>(blocks, ctx->sm_count));
     const int threads = warps * 32;
-    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, <<<grid, threads, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
-    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, <<<grid, threads, smem, st>>>(xr, xi, wr, wi, yr, yi, B, in, out));
+    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out);
+    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out);
     CNB_LAUNCH_CHECK("skinny_fwd");
     return CNB_OK;
 }
@@ -301,8 +305,8 @@ int skinny_bwd_x(cnb_ctx* ctx, const float* gr, const float* gi, const float* wr
     const int rows = (B + chunks - 1) / chunks;
     chunks = (B + rows - 1) / rows;
     const dim3 grid(col_blocks, chunks);
-    if (vec) CNB_SKINNY_DISPATCH(skinny_bwd_x_k, 4, <<<grid, 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate, rows));
-    else CNB_SKINNY_DISPATCH(skinny_bwd_x_k, 1, <<<grid, 256, 0, st>>>(gr, gi, wr, wi, dr, di, B, in, out, accumulate, rows));
+    if (vec) CNB_SKINNY_DISPATCH(skinny_bwd_x_k, 4, dim3(grid), dim3(256), 0, st, 1, gr, gi, wr, wi, dr, di, B, in, out, accumulate, rows);
+    else CNB_SKINNY_DISPATCH(skinny_bwd_x_k, 1, dim3(grid), dim3(256), 0, st, 1, gr, gi, wr, wi, dr, di, B, in, out, accumulate, rows);
     CNB_LAUNCH_CHECK("skinny_bwd_x");
     return CNB_OK;
 }
@@ -323,10 +327,10 @@ int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr
     float* pr = ws;
     float* pi = ws + (size_t) chunks * n;
     const dim3 grid(col_blocks, chunks), block(32, 8);
-    if (vec) CNB_SKINNY_DISPATCH(skinny_bwd_w_stage1_k, 4, <<<grid, block, 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows));
-    else CNB_SKINNY_DISPATCH(skinny_bwd_w_stage1_k, 1, <<<grid, block, 0, st>>>(gr, gi, xr, xi, pr, pi, B, in, out, rows));
+    if (vec) CNB_SKINNY_DISPATCH(skinny_bwd_w_stage1_k, 4, grid, block, 0, st, 1, gr, gi, xr, xi, pr, pi, B, in, out, rows);
+    else CNB_SKINNY_DISPATCH(skinny_bwd_w_stage1_k, 1, grid, block, 0, st, 1, gr, gi, xr, xi, pr, pi, B, in, out, rows);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage1");
-    skinny_bwd_w_stage2_k<<<(int) ((n + 31) / 32), dim3(32, 8), 0, st>>>(pr, pi, dr, di, chunks, n, accumulate);
+    cnb::launch(skinny_bwd_w_stage2_k, dim3((unsigned) ((n + 31) / 32)), dim3(32, 8), 0, st, 1, pr, pi, dr, di, chunks, n, accumulate);
     CNB_LAUNCH_CHECK("skinny_bwd_w_stage2");
     return CNB_OK;
 }

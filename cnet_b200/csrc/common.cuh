@@ -110,6 +110,57 @@ __device__ __forceinline__ float cnb_dgelu(float x) {
     return 0.5f * (1.0f + t) + 0.5f * x * sech2 * 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2);
 }
 
+// Programmatic dependent launch.  Every kernel of the step is launched with the "programmatic stream
+// serialization" attribute (cnb::launch below): it may be scheduled as soon as every CTA of the kernel before
+// it in the stream has called cnb_pdl_trigger() (or exited), so its launch latency and its set-up (barriers,
+// tensor memory, tables that no kernel writes) run under the predecessor's tail.  cnb_pdl_wait() returns when
+// the predecessor grid has completed and its memory is visible: nothing a predecessor writes or reads may be
+// touched before it.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void cnb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void cnb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void cnb_pdl_enter() { cnb_pdl_trigger(); cnb_pdl_wait(); }
+
+namespace cnb {
+
+bool pdl_enabled();                // CNB_PDL=0 in the environment launches every kernel fully serialised
+
+// Launch of a kernel that starts with cnb_pdl_enter() (or does its own trigger / wait); cluster > 1 adds a
+// thread-block cluster of that many CTAs along x.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster,
+                             bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    unsigned n = 0;
+    if (dependent && pdl_enabled()) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster > 1) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned) cluster;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, int cluster,
+                          Args... args) {
+    return launch_ex(kernel, grid, block, smem, st, cluster, true, args...);
+}
+
+}  // namespace cnb
+
 #define CNB_CHECK_ARG(cond, ...) \
     do { if (!(cond)) return cnb::set_error(CNB_ERR_ARG, __VA_ARGS__); } while (0)
 

@@ -2,6 +2,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -20,6 +21,11 @@ int set_error(int code, const char* fmt, ...) {
 }
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("CNB_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
 
 int ensure_scratch(cnb_ctx* ctx, size_t bytes, float** out) {
     if (bytes > ctx->scratch_bytes) {

@@ -50,6 +50,7 @@ template <int W>
 __global__ void hadamard_fwd_k(const float* __restrict__ ur, const float* __restrict__ ui,
                                const float* __restrict__ vr, const float* __restrict__ vi, int v_batched,
                                float* __restrict__ yr, float* __restrict__ yi, size_t total, int N) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         size_t j = v_batched ? i : i % N;
@@ -69,6 +70,7 @@ __global__ void hadamard_bwd_elem_k(const float* __restrict__ gr, const float* _
                                     const float* __restrict__ orr, const float* __restrict__ oi, int o_batched,
                                     float* __restrict__ dr, float* __restrict__ di, int accumulate,
                                     size_t total, int N) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         size_t j = o_batched ? i : i % N;
@@ -100,6 +102,7 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
                    float* __restrict__ pr, float* __restrict__ pi,
                    int B, int N, int rows_per_chunk,
                    int* __restrict__ done, float* __restrict__ dvr, float* __restrict__ dvi, int accumulate_v) {
+    cnb_pdl_enter();
     __shared__ float sr[8][32 * W + 1], si[8][32 * W + 1];
     __shared__ int s_last;
     const int col = (blockIdx.x * 32 + threadIdx.x) * W;
@@ -200,6 +203,7 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
 __global__ void colreduce_stage2_k(const float* __restrict__ pr, const float* __restrict__ pi,
                                    float* __restrict__ dr, float* __restrict__ di, int accumulate,
                                    int chunks, int N) {
+    cnb_pdl_enter();
     __shared__ float sr[8][33], si[8][33];
     int col = blockIdx.x * 32 + threadIdx.x;
     float a = 0.f, b = 0.f;
@@ -220,6 +224,7 @@ __global__ void colreduce_stage2_k(const float* __restrict__ pr, const float* __
 template <int W>
 __global__ void gelu_fwd_k(const float* __restrict__ zr, const float* __restrict__ zi,
                            float* __restrict__ yr, float* __restrict__ yi, size_t total) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         Pack<W> a = ld<W>(zr, i), b = ld<W>(zi, i);
@@ -233,6 +238,7 @@ template <int W>
 __global__ void gelu_bwd_k(const float* __restrict__ gr, const float* __restrict__ gi,
                            const float* __restrict__ zr, const float* __restrict__ zi,
                            float* __restrict__ dr, float* __restrict__ di, int accumulate, size_t total) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         Pack<W> a = ld<W>(gr, i), b = ld<W>(gi, i), x = ld<W>(zr, i), y = ld<W>(zi, i), r, s;
@@ -257,6 +263,7 @@ __global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* _
                                     float* __restrict__ ar, float* __restrict__ ai,
                                     float* __restrict__ yr, float* __restrict__ yi, size_t total, int N,
                                     float* __restrict__ sp, size_t np) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         size_t j = i % N;
@@ -288,6 +295,7 @@ template <int W>
 __global__ void crelu_k(const float* __restrict__ zr, const float* __restrict__ zi,
                         const float* __restrict__ sr, const float* __restrict__ si,
                         float* __restrict__ dr, float* __restrict__ di, int accumulate, size_t total) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         Pack<W> a = ld<W>(zr, i), b = ld<W>(zi, i), x = ld<W>(sr, i), y = ld<W>(si, i), r, s;
@@ -307,6 +315,7 @@ __global__ void crelu_k(const float* __restrict__ zr, const float* __restrict__ 
 template <int W>
 __global__ void adam_k(float* __restrict__ w, float* __restrict__ m, float* __restrict__ g, size_t total, float lr_hat,
                        float beta) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         Pack<W> a = ld<W>(w, i), b = ld<W>(m, i), c = ld<W>(g, i);
@@ -325,6 +334,7 @@ template <int W>
 __global__ void add2_k(const float* __restrict__ ur, const float* __restrict__ ui,
                        const float* __restrict__ vr, const float* __restrict__ vi,
                        float* __restrict__ yr, float* __restrict__ yi, size_t total) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         Pack<W> a = ld<W>(ur, i), b = ld<W>(ui, i), c = ld<W>(vr, i), d = ld<W>(vi, i);
@@ -336,6 +346,7 @@ __global__ void add2_k(const float* __restrict__ ur, const float* __restrict__ u
 
 template <int W>
 __global__ void sgd_k(float* __restrict__ w, float* __restrict__ g, size_t total, float lr, int zero_grad) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * W;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * W; i < total; i += stride) {
         Pack<W> a = ld<W>(w, i), b = ld<W>(g, i);
@@ -358,6 +369,7 @@ struct SplitSpans {
 
 __global__ void sgd_split_k(float* __restrict__ w, float* __restrict__ g, size_t total, float lr, int zero_grad,
                             const SplitSpans sp) {
+    cnb_pdl_enter();
     size_t stride = (size_t) gridDim.x * blockDim.x * 4;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += stride) {
         Pack<4> a = ld<4>(w, i), b = ld<4>(g, i);
@@ -417,13 +429,13 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
     dim3 grid(col_blocks, chunks), block(32, 8);
     // up to 64 column blocks: the last CTA of each column block finishes the sum in the same launch
     int* done = (col_blocks <= 64 && ctx->d_counters) ? ctx->d_counters + 64 * (ctx->counter_set++ & 7) : nullptr;
-#define CNB_COLREDUCE(MODE, W) colreduce_stage1_k<MODE, W><<<grid, block, 0, stm>>>(gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows, done, dvr, dvi, acc_v)
+#define CNB_COLREDUCE(MODE, W) cnb::launch(colreduce_stage1_k<MODE, W>, grid, block, 0, stm, 1, gr, gi, ar, ai, ur, ui, hr, hi, dur, dui, acc_u, pr, pi, B, N, rows, done, dvr, dvi, acc_v)
     if (mode == 0) { if (vec) CNB_COLREDUCE(0, 4); else CNB_COLREDUCE(0, 1); }
     else { if (vec) CNB_COLREDUCE(1, 4); else CNB_COLREDUCE(1, 1); }
 #undef CNB_COLREDUCE
     CNB_LAUNCH_CHECK("colreduce_stage1");
     if (!done) {
-        colreduce_stage2_k<<<(N + 31) / 32, dim3(32, 8), 0, stm>>>(pr, pi, dvr, dvi, acc_v, chunks, N);
+        cnb::launch(colreduce_stage2_k, dim3((N + 31) / 32), dim3(32, 8), 0, stm, 1, pr, pi, dvr, dvi, acc_v, chunks, N);
         CNB_LAUNCH_CHECK("colreduce_stage2");
     }
     return CNB_OK;
@@ -435,9 +447,9 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
 #define DISPATCH_W(vec_ok, KERNEL, total, ...)                                              \
     do {                                                                                    \
         if (vec_ok) {                                                                       \
-            KERNEL<4><<<grid_for(((total) + 3) / 4, 256, ctx->sm_count), 256, 0, stm>>>(__VA_ARGS__); \
+            cnb::launch(KERNEL<4>, dim3(grid_for(((total) + 3) / 4, 256, ctx->sm_count)), dim3(256), 0, stm, 1, __VA_ARGS__); \
         } else {                                                                            \
-            KERNEL<1><<<grid_for((total), 256, ctx->sm_count), 256, 0, stm>>>(__VA_ARGS__); \
+            cnb::launch(KERNEL<1>, dim3(grid_for((total), 256, ctx->sm_count)), dim3(256), 0, stm, 1, __VA_ARGS__); \
         }                                                                                   \
         CNB_LAUNCH_CHECK(#KERNEL);                                                          \
     } while (0)
@@ -608,7 +620,7 @@ int cnb_sgd_update_split(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, i
     }
     cudaStream_t stm = cnb::S(stream);
     size_t blocks = (n / 4 + 255) / 256, cap = (size_t) ctx->sm_count * 16;
-    sgd_split_k<<<(int) std::min(blocks, cap), 256, 0, stm>>>(w, g, n, lr, zero_grad, sp);
+    cnb::launch(sgd_split_k, dim3((unsigned) std::min(blocks, cap)), dim3(256), 0, stm, 1, w, g, n, lr, zero_grad, sp);
     CNB_LAUNCH_CHECK("sgd_split");
     return CNB_OK;
 }

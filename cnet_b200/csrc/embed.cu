@@ -8,6 +8,7 @@ template <int W>
 __global__ void embed_fwd_k(const float* __restrict__ tr, const float* __restrict__ ti,
                             const int32_t* __restrict__ tok, float* __restrict__ orr, float* __restrict__ oi,
                             size_t rows, int D, int V) {
+    cnb_pdl_enter();
     int per_row = D / W;
     size_t total = rows * per_row;
     for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t) gridDim.x * blockDim.x) {
@@ -33,6 +34,7 @@ __global__ void embed_fwd_k(const float* __restrict__ tr, const float* __restric
 __global__ void embed_bwd_k(const float* __restrict__ gr, const float* __restrict__ gi,
                             const int32_t* __restrict__ tok, float* __restrict__ dr, float* __restrict__ di,
                             size_t rows, int D, int V) {
+    cnb_pdl_enter();
     size_t total = rows * D;
     for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t) gridDim.x * blockDim.x) {
         size_t row = i / D;
@@ -58,8 +60,8 @@ int cnb_embed_fwd(cnb_ctx* ctx, const float* tab_re, const float* tab_im, const 
     size_t items = rows * (vec ? D / 4 : D);
     size_t blocks = (items + 255) / 256, cap = (size_t) ctx->sm_count * 16;
     int grid = (int) (blocks < cap ? blocks : cap);
-    if (vec) embed_fwd_k<4><<<grid, 256, 0, cnb::S(stream)>>>(tab_re, tab_im, tokens, out_re, out_im, rows, D, V);
-    else embed_fwd_k<1><<<grid, 256, 0, cnb::S(stream)>>>(tab_re, tab_im, tokens, out_re, out_im, rows, D, V);
+    if (vec) cnb::launch(embed_fwd_k<4>, dim3(grid), dim3(256), 0, cnb::S(stream), 1, tab_re, tab_im, tokens, out_re, out_im, rows, D, V);
+    else cnb::launch(embed_fwd_k<1>, dim3(grid), dim3(256), 0, cnb::S(stream), 1, tab_re, tab_im, tokens, out_re, out_im, rows, D, V);
     CNB_LAUNCH_CHECK("embed_fwd");
     return CNB_OK;
 }
@@ -72,7 +74,7 @@ int cnb_embed_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const int3
     size_t items = rows * D;
     size_t blocks = (items + 255) / 256, cap = (size_t) ctx->sm_count * 16;
     int grid = (int) (blocks < cap ? blocks : cap);
-    embed_bwd_k<<<grid, 256, 0, cnb::S(stream)>>>(g_re, g_im, tokens, dtab_re, dtab_im, rows, D, V);
+    cnb::launch(embed_bwd_k, dim3(grid), dim3(256), 0, cnb::S(stream), 1, g_re, g_im, tokens, dtab_re, dtab_im, rows, D, V);
     CNB_LAUNCH_CHECK("embed_bwd");
     return CNB_OK;
 }

@@ -26,6 +26,7 @@ template <int R, int SIGN>
 __global__ void __launch_bounds__(256, (R <= 32 ? 2 : 1))
 fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __restrict__ yr, float* __restrict__ yi,
          const float2* __restrict__ tw, int B, int accumulate, const FftEpilogue ep) {
+    cnb_pdl_enter();
     constexpr int N = R * R;
     constexpr int ROWS = 256 / R;                        // rows per block
     extern __shared__ float smem_f[];
@@ -163,7 +164,7 @@ __global__ void fft_twiddle_k(float2* __restrict__ tw, int R) {
 }
 
 template <int R>
-int launch(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, const float2* tw, int B, int inverse,
+int launch_rr(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, const float2* tw, int B, int inverse,
            int accumulate, const FftEpilogue& ep, cudaStream_t st) {
     constexpr int ROWS = 256 / R;
     size_t smem = (size_t) ROWS * 2 * R * (R + 1) * sizeof(float);
@@ -177,8 +178,8 @@ int launch(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi,
     int blocks = (B + ROWS - 1) / ROWS;
     int cap = ctx->sm_count * 8;
     if (blocks > cap) blocks = cap;
-    if (inverse) fft_rr_k<R, 1><<<blocks, 256, smem, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep);
-    else fft_rr_k<R, -1><<<blocks, 256, smem, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep);
+    if (inverse) cnb::launch(fft_rr_k<R, 1>, dim3(blocks), dim3(256), smem, st, 1, xr, xi, yr, yi, tw, B, accumulate, ep);
+    else cnb::launch(fft_rr_k<R, -1>, dim3(blocks), dim3(256), smem, st, 1, xr, xi, yr, yi, tw, B, accumulate, ep);
     CNB_LAUNCH_CHECK("fft_rr");
     return CNB_OK;
 }
@@ -193,8 +194,10 @@ static int fft_dispatch(cnb_ctx* ctx, const float* xr, const float* xi, float* y
                         int accumulate, const FftEpilogue& ep, cudaStream_t st) {
     // the inter-pass twiddle table lives in the arena; the map key -N keeps it apart from DFT matrices
     cnb_twiddle t;
+    bool fresh = false;            // the table is being made by the launch just before this one
     auto it = ctx->twiddles.find(-N);
     if (it == ctx->twiddles.end()) {
+        fresh = true;
         void* p = nullptr;
         int rc = cnb_alloc(ctx, (size_t) N * sizeof(float2), &p);
         if (rc != CNB_OK) return rc;
@@ -206,9 +209,9 @@ static int fft_dispatch(cnb_ctx* ctx, const float* xr, const float* xi, float* y
         t = it->second;
     }
     const float2* tw = reinterpret_cast<const float2*>(t.re);
-    if (N == 256) return launch<16>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
-    if (N == 1024) return fft1024_pipe(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
-    if (N == 4096) return launch<64>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
+    if (N == 256) return launch_rr<16>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
+    if (N == 1024) return fft1024_pipe(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st, fresh);
+    if (N == 4096) return launch_rr<64>(ctx, xr, xi, yr, yi, tw, B, inverse, accumulate, ep, st);
     return set_error(CNB_ERR_UNSUPPORTED, "fft: N=%d", N);
 }
 

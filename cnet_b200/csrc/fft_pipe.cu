@@ -97,8 +97,12 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
     float* out_i = sr + N;
     const long stride = (long) gridDim.x * WARPS;
     long row = blockIdx.x + (long) gridDim.x * w;
-    // the warp's barrier is set up and its first row requested by the same thread, before the twiddle table
-    // is staged: the first fetch runs under the staging
+    // The warp's barrier is set up and its first row requested by the same thread, before the twiddle table is
+    // staged: the first fetch runs under the staging.  Rows are fetched only after the kernel before this one
+    // in the stream has completed (a CTA of this size never shares an SM with the GEMM's or its own
+    // predecessor's, so there is nothing to gain from staging the table ahead of the wait).
+    cnb_pdl_trigger();
+    cnb_pdl_wait();
     if (t == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -194,7 +198,7 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
 namespace cnb {
 
 int fft1024_pipe(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, const float2* tw, int B,
-                 int inverse, int accumulate, const cnb_fft::FftEpilogue& ep, cudaStream_t st) {
+                 int inverse, int accumulate, const cnb_fft::FftEpilogue& ep, cudaStream_t st, bool /*fresh_table*/) {
     static bool attr_done[64] = {};                      // the attribute is per device
     if (!attr_done[ctx->device & 63]) {
         CNB_CUDA(cudaFuncSetAttribute(fft1024_pipe_k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -208,8 +212,8 @@ int fft1024_pipe(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, floa
     // kernels need SMs (cnb_set_gemm_sm_limit) it leaves the same SMs free instead of waiting for them
     const int sms = ctx->gemm_cta_limit > 0 && ctx->gemm_cta_limit < ctx->sm_count ? ctx->gemm_cta_limit : ctx->sm_count;
     int blocks = B < sms ? B : sms;
-    if (inverse) fft1024_pipe_k<1><<<blocks, THREADS, SMEM_BYTES, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep, ctx->d_status);
-    else fft1024_pipe_k<-1><<<blocks, THREADS, SMEM_BYTES, st>>>(xr, xi, yr, yi, tw, B, accumulate, ep, ctx->d_status);
+    if (inverse) CNB_CUDA(cnb::launch_ex(fft1024_pipe_k<1>, dim3(blocks), dim3(THREADS), SMEM_BYTES, st, 1, true, xr, xi, yr, yi, tw, B, accumulate, ep, ctx->d_status));
+    else CNB_CUDA(cnb::launch_ex(fft1024_pipe_k<-1>, dim3(blocks), dim3(THREADS), SMEM_BYTES, st, 1, true, xr, xi, yr, yi, tw, B, accumulate, ep, ctx->d_status));
     CNB_LAUNCH_CHECK("fft1024_pipe");
     return CNB_OK;
 }

@@ -56,6 +56,8 @@ struct FftEpilogue {
 
 namespace cnb {
 // N = 1024: persistent kernel fed and drained by bulk copies
+// fresh_table: `tw` is written by the launch just before this one (the kernel reads it before it waits for its
+// predecessor, so that one launch must be fully serialised)
 int fft1024_pipe(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, const float2* tw, int B,
-                 int inverse, int accumulate, const cnb_fft::FftEpilogue& ep, cudaStream_t st);
+                 int inverse, int accumulate, const cnb_fft::FftEpilogue& ep, cudaStream_t st, bool fresh_table);
 }  // namespace cnb

@@ -26,6 +26,7 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 
 __global__ void softmax_fwd_k(const float* __restrict__ zr, const float* __restrict__ zi,
                               float* __restrict__ yr, float* __restrict__ yi, float* __restrict__ inv_norm, int N) {
+    cnb_pdl_enter();
     __shared__ float sm[32];
     size_t base = (size_t) blockIdx.x * N;
     float s = 0.f;
@@ -47,6 +48,7 @@ __global__ void softmax_bwd_k(const float* __restrict__ gr, const float* __restr
                               const float* __restrict__ zr, const float* __restrict__ zi,
                               const float* __restrict__ inv_norm, float* __restrict__ dr, float* __restrict__ di,
                               int N, int accumulate) {
+    cnb_pdl_enter();
     __shared__ float sm[32];
     size_t base = (size_t) blockIdx.x * N;
     float s = 0.f;
@@ -66,6 +68,7 @@ __global__ void softmax_bwd_k(const float* __restrict__ gr, const float* __restr
 __global__ void crossent_k(const float* __restrict__ zr, const float* __restrict__ zi,
                            const int32_t* __restrict__ labels, float* __restrict__ loss,
                            float* __restrict__ dr, float* __restrict__ di, int M) {
+    cnb_pdl_enter();
     __shared__ float sm[32];
     size_t base = (size_t) blockIdx.x * M;
     float s = 0.f;
@@ -93,6 +96,7 @@ __global__ void crossent_k(const float* __restrict__ zr, const float* __restrict
 // L2Out: loss[b] = sum |z|^2; seed dz* = z
 __global__ void l2out_k(const float* __restrict__ zr, const float* __restrict__ zi, float* __restrict__ loss,
                         float* __restrict__ dr, float* __restrict__ di, int N) {
+    cnb_pdl_enter();
     __shared__ float sm[32];
     size_t base = (size_t) blockIdx.x * N;
     float s = 0.f;
@@ -119,7 +123,7 @@ int cnb_softmax_fwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float* y
                     float* inv_norm, int B, int N, void* stream) {
     CNB_CHECK_ARG(ctx && z_re && z_im && y_re && y_im && inv_norm, "cnb_softmax_fwd: null pointer");
     CNB_CHECK_ARG(B > 0 && N > 0, "cnb_softmax_fwd: B=%d N=%d", B, N);
-    softmax_fwd_k<<<B, threads_for(N), 0, cnb::S(stream)>>>(z_re, z_im, y_re, y_im, inv_norm, N);
+    cnb::launch(softmax_fwd_k, dim3(B), dim3(threads_for(N)), 0, cnb::S(stream), 1, z_re, z_im, y_re, y_im, inv_norm, N);
     CNB_LAUNCH_CHECK("softmax_fwd");
     return CNB_OK;
 }
@@ -130,7 +134,7 @@ int cnb_softmax_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im, const fl
     CNB_CHECK_ARG(ctx && g_re && g_im && z_re && z_im && inv_norm && dz_re && dz_im,
                   "cnb_softmax_bwd: null pointer");
     CNB_CHECK_ARG(B > 0 && N > 0, "cnb_softmax_bwd: B=%d N=%d", B, N);
-    softmax_bwd_k<<<B, threads_for(N), 0, cnb::S(stream)>>>(g_re, g_im, z_re, z_im, inv_norm, dz_re, dz_im, N,
+    cnb::launch(softmax_bwd_k, dim3(B), dim3(threads_for(N)), 0, cnb::S(stream), 1, g_re, g_im, z_re, z_im, inv_norm, dz_re, dz_im, N,
                                                            accumulate);
     CNB_LAUNCH_CHECK("softmax_bwd");
     return CNB_OK;
@@ -141,7 +145,7 @@ int cnb_crossent_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im, con
     CNB_CHECK_ARG(ctx && z_re && z_im && labels && loss, "cnb_crossent_fwd_bwd: null pointer");
     CNB_CHECK_ARG((dz_re == nullptr) == (dz_im == nullptr), "cnb_crossent_fwd_bwd: dz planes must be a pair");
     CNB_CHECK_ARG(B > 0 && M > 0, "cnb_crossent_fwd_bwd: B=%d M=%d", B, M);
-    crossent_k<<<B, threads_for(M), 0, cnb::S(stream)>>>(z_re, z_im, labels, loss, dz_re, dz_im, M);
+    cnb::launch(crossent_k, dim3(B), dim3(threads_for(M)), 0, cnb::S(stream), 1, z_re, z_im, labels, loss, dz_re, dz_im, M);
     CNB_LAUNCH_CHECK("crossent");
     return CNB_OK;
 }
@@ -151,7 +155,7 @@ int cnb_l2out_fwd_bwd(cnb_ctx* ctx, const float* z_re, const float* z_im, float*
     CNB_CHECK_ARG(ctx && z_re && z_im && loss, "cnb_l2out_fwd_bwd: null pointer");
     CNB_CHECK_ARG((dz_re == nullptr) == (dz_im == nullptr), "cnb_l2out_fwd_bwd: dz planes must be a pair");
     CNB_CHECK_ARG(B > 0 && N > 0, "cnb_l2out_fwd_bwd: B=%d N=%d", B, N);
-    l2out_k<<<B, threads_for(N), 0, cnb::S(stream)>>>(z_re, z_im, loss, dz_re, dz_im, N);
+    cnb::launch(l2out_k, dim3(B), dim3(threads_for(N)), 0, cnb::S(stream), 1, z_re, z_im, loss, dz_re, dz_im, N);
     CNB_LAUNCH_CHECK("l2out");
     return CNB_OK;
 }

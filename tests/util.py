@@ -209,13 +209,12 @@ def run_width_case(net, name, batch, weights=None, alloc=None, record=True, trai
     for lname, uid in spec.layers.items():
         if lname == "ce" or (uid in weight_uids and uid != spec.main):
             continue
-        try:
-            a = net.get_record(uid, 0)
-            g = net.get_record(uid, 1)
-        except Exception:          # tensor fused away on the device / not recorded
-            continue
-        _sampled(out, "act_" + lname, a, rows)
-        _sampled(out, "gstar_" + lname, g, rows)
+        for what, prefix in ((0, "act_"), (1, "gstar_")):
+            try:
+                t = net.get_record(uid, what)
+            except Exception:      # tensor fused away on the device / not recorded
+                continue
+            _sampled(out, prefix + lname, t, rows)
     if train:
         for lname, uid in spec.layers.items():
             if uid in weight_uids:
