@@ -80,6 +80,20 @@ __device__ __forceinline__ void row_store(float* dst, uint32_t src, int accumula
                      ::"l"(dst), "r"(src), "r"(N * 4) : "memory");
 }
 
+// Phase stamps of the first rows of one warp (a build with -DCNB_FFT_TIMING only; read back from the status block).
+#ifdef CNB_FFT_TIMING
+#define CNB_STAMP(k)                                                                              \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && w == 0 && t == 0 && stamp_row < 3) {                               \
+            long long c_;                                                                         \
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(c_)::"memory");                          \
+            status[800 + stamp_row * 12 + (k)] = (int) c_;                                        \
+        }                                                                                         \
+    } while (0)
+#else
+#define CNB_STAMP(k) do { } while (0)
+#endif
+
 template <int SIGN>
 __global__ void __launch_bounds__(THREADS, 1)
 fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __restrict__ yr,
@@ -108,26 +122,35 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (row < B) row_fetch(smem_u32(in_r), xr + row * N, xi + row * N, bar);
     }
-    for (int i = threadIdx.x; i < N; i += THREADS) tws[i] = tw[i];
+    // The table carries the transform's N^-1/2 = 1/32 (a power of two: the products are the same bits as
+    // scaling the result).
+    for (int i = threadIdx.x; i < N; i += THREADS) { const float2 f = tw[i]; tws[i] = make_float2(f.x * 0.03125f, f.y * 0.03125f); }
     __syncthreads();
 
-    const float scale = rsqrtf((float) N);
     uint32_t phase = 0;
     bool stored = false;
+#ifdef CNB_FFT_TIMING
+    int stamp_row = 0;
+#endif
     for (; row < B; row += stride) {
+        CNB_STAMP(0);
         const bool ok = row_wait(bar, phase, status);
         if (!__all_sync(0xffffffffu, ok)) break;
         phase ^= 1;
         float re[R], im[R];
 #pragma unroll
+        CNB_STAMP(1);
         for (int n1 = 0; n1 < R; ++n1) { re[n1] = in_r[n1 * R + t]; im[n1] = in_i[n1 * R + t]; }
         __syncwarp();
+        CNB_STAMP(2);
         const long next = row + stride;
         if (t == 0 && next < B) {                        // the staging buffer is free: fetch the next row now
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             row_fetch(smem_u32(in_r), xr + next * N, xi + next * N, bar);
         }
+        CNB_STAMP(3);
         fft_regs<R, SIGN>(re, im);
+        CNB_STAMP(4);
         if (stored) {                                    // the previous row must have left the work tile
             if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
@@ -141,25 +164,30 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
             si[k1 * (R + 1) + t] = re[p] * s + im[p] * c;
         }
         __syncwarp();
+        CNB_STAMP(5);
 #pragma unroll
         for (int n2 = 0; n2 < R; ++n2) { re[n2] = sr[t * (R + 1) + n2]; im[n2] = si[t * (R + 1) + n2]; }
+        CNB_STAMP(6);
         fft_regs<R, SIGN>(re, im);
         __syncwarp();                                    // the tile has been read by every lane
+        CNB_STAMP(7);
 #pragma unroll
         for (int p = 0; p < R; ++p) {
             const int k2 = bitrev<R>(p);                 // lane t holds X[t + R*k2]
-            re[p] *= scale; im[p] *= scale;
             out_r[k2 * R + t] = re[p];
             out_i[k2 * R + t] = im[p];
         }
+        CNB_STAMP(8);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
+        CNB_STAMP(9);
         if (t == 0) {
             row_store(yr + row * N, smem_u32(out_r), accumulate);
             row_store(yi + row * N, smem_u32(out_i), accumulate);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         stored = true;
+        CNB_STAMP(10);
         if (ep.hr) {
             // fused tail: y = gelu(u o h) and its hi/lo split, straight from the registers; a warp's
             // store covers 128 contiguous bytes
@@ -188,6 +216,10 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
                 }
             }
         }
+        CNB_STAMP(11);
+#ifdef CNB_FFT_TIMING
+        ++stamp_row;
+#endif
     }
     // shared memory stays allocated until the engine has read the last row out of it
     if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

@@ -74,8 +74,10 @@ class DataParallelTrainer:
         self.spec = builder(self.net, **builder_kwargs)
         for uid, (re, im) in configs.init_weights(self.spec, seed).items():
             self.net.set_values(uid, re, im)
-        self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream)
         self.comm = ("nccl" if self.world > 1 else "none") if comm == "auto" else comm
+        # several ranks over NCCL: the arena comes from NCCL's allocator, so the gradients can be a symmetric window
+        self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream,
+                          nccl_arena=self.world > 1 and self.comm == "nccl")
         self.reducer = GradBucketReducer() if self.comm == "torch" else None
         if self.world > 1 and self.comm == "nccl":
             box = [self.net.dp_unique_id() if self.rank == 0 else None]

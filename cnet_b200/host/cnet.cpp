@@ -420,6 +420,8 @@ CNet::~CNet() {
 	}
 	for (auto f : func_list_) delete f;
 	if (ctx_) cnb_destroy(ctx_);
+	nccl_.shutdown();                               // the window is deregistered before its memory goes
+	if (own_nccl_arena_) NcclGroup::memFree(own_nccl_arena_);
 }
 
 void CNet::setDevice(int device, size_t arena_bytes, void* ext_arena) {
@@ -656,6 +658,14 @@ bool CNet::allocateOnGpu(int B) {
 	}
 	if (fuse_) planFusion();
 	if (arena_bytes_ == 0) arena_bytes_ = requiredArenaBytes(B);
+	if (nccl_arena_ && !ext_arena_) {
+		cudaSetDevice(device_);
+		std::string err;
+		arena_bytes_ = (arena_bytes_ + ((size_t) 2 << 20) - 1) & ~(((size_t) 2 << 20) - 1);
+		own_nccl_arena_ = NcclGroup::memAlloc(arena_bytes_, &err);
+		if (!own_nccl_arena_) { fail(CNB_ERR_CUDA, "allocateOnGpu: " + err); return false; }
+		ext_arena_ = own_nccl_arena_;
+	}
 	int rc = ext_arena_ ? cnb_create_external(device_, ext_arena_, arena_bytes_, &ctx_)
 			: cnb_create(device_, arena_bytes_, &ctx_);
 	if (rc != CNB_OK) { fail(rc, "allocateOnGpu"); ctx_ = nullptr; return false; }
@@ -1030,6 +1040,21 @@ bool CNet::setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nran
 	if (!ctx_) { fail(CNB_ERR_ARG, "setDataParallel: allocateOnGpu first"); return false; }
 	cudaSetDevice(device_);
 	if (!nccl_.init(id, rank, nranks)) { fail(CNB_ERR_CUDA, "setDataParallel: " + nccl_.error()); return false; }
+	if (nccl_.active() && own_nccl_arena_) {
+		// weights and their gradients (allocated back to back, first in the arena) as one symmetric window:
+		// NCCL then reduces them with its symmetric-memory kernels (peer / in-switch access on the buffers
+		// themselves, no staging copies, fewer CTAs).  CNB_DP_SYMM=0 leaves the buffers unregistered.
+		const char* e = getenv("CNB_DP_SYMM");
+		if (!(e && e[0] == '0') && weight_base_ && wgrad_base_) {
+			uintptr_t lo = reinterpret_cast<uintptr_t>(weight_base_) & ~uintptr_t(4095);
+			uintptr_t hi = (reinterpret_cast<uintptr_t>(wgrad_base_ + wgrad_count_) + 4095) & ~uintptr_t(4095);
+			uintptr_t end = reinterpret_cast<uintptr_t>(own_nccl_arena_) + arena_bytes_;
+			if (hi > end) hi = end;
+			if (!nccl_.registerWindow(reinterpret_cast<void*>(lo), hi - lo)) {
+				fail(CNB_ERR_CUDA, "setDataParallel: " + nccl_.error()); return false;
+			}
+		}
+	}
 	if (nccl_.active()) {
 		// the GEMM is one CTA per SM and fills shared memory; keep a few SMs for NCCL's kernels so the
 		// bucket all-reduces really overlap the backward pass (CNB_DP_RESERVED_SMS overrides, 0 = none)

@@ -389,6 +389,8 @@ class CNet {
 	int device_ = 0;
 	size_t arena_bytes_ = 0;
 	void* ext_arena_ = nullptr;
+	bool nccl_arena_ = false;                       // the arena comes from NCCL's allocator (registrable as a symmetric window)
+	void* own_nccl_arena_ = nullptr;
 	int batch_ = 0;                                 // allocated batch
 	int cur_batch_ = 0;                             // rows of the batch in flight
 	bool fuse_ = true;
@@ -438,6 +440,10 @@ public:
 	CNet();
 	// device / arena to use; call before allocateOnGpu.  ext_arena != NULL: caller-owned memory.
 	void setDevice(int device, size_t arena_bytes, void* ext_arena = nullptr);
+	// Take the arena from NCCL's allocator (ncclMemAlloc) instead of cudaMalloc, so that setDataParallel can
+	// register the weight / gradient region with the communicator as a symmetric window.  Call before allocateOnGpu.
+	void setNcclArena(bool on) { nccl_arena_ = on; }
+	bool symmetricWindow() const { return nccl_.hasWindow(); }
 	void setStream(void* stream) { stream_ = stream; }
 	void setFusion(bool on) { fuse_ = on; }
 	void setBucketHook(BucketHook hook, void* user) { hook_ = hook; hook_user_ = user; }

@@ -124,6 +124,8 @@ SIGNATURES = {
     "cnh_dp_unique_id": (C.c_int, [C.c_char_p]),
     "cnh_dp_init": (C.c_int, [_vp, C.c_char_p, C.c_int, C.c_int]),
     "cnh_dp_async_error": (C.c_int, [_vp]),
+    "cnh_dp_use_nccl_arena": (C.c_int, [_vp, C.c_int]),
+    "cnh_dp_symmetric": (C.c_int, [_vp]),
     "cnh_capture_begin": (C.c_int, [_vp]),
     "cnh_capture_end": (C.c_int, [_vp]),
     "cnh_graph_launch": (C.c_int, [_vp]),

@@ -114,13 +114,18 @@ class Net:
         return self.lib.cnh_type_of(self.h, uid)
 
     # ----------------------------------------------------------------- device
-    def allocate(self, batch, fuse=True, stream=None):
-        """allocateOnGpu(batch): plan the batched tensors in one arena and upload the weights."""
+    def allocate(self, batch, fuse=True, stream=None, nccl_arena=False):
+        """allocateOnGpu(batch): plan the batched tensors in one arena and upload the weights.
+        nccl_arena: the host facade takes the arena from NCCL's allocator (for a symmetric window in dp_init)."""
         import torch
         if not torch.cuda.is_available():
             raise _lib.CnetError("no CUDA device: the path has no CPU fallback")
         need = self.arena_bytes or self.lib.cnh_required_arena(self.h, batch)
-        if self.use_torch_arena:
+        if nccl_arena:
+            torch.cuda.set_device(self.device)
+            self.lib.cnh_dp_use_nccl_arena(self.h, 1)
+            ext = None
+        elif self.use_torch_arena:
             torch.cuda.set_device(self.device)
             self.arena = torch.empty(need, dtype=torch.uint8, device="cuda:%d" % self.device)
             ext = self.arena.data_ptr()

@@ -81,6 +81,11 @@ void* cnh_context(cnh_net* net);                                             /* 
 int cnh_dp_unique_id(char* out128);
 int cnh_dp_init(cnh_net* net, const char* id128, int rank, int nranks);
 int cnh_dp_async_error(cnh_net* net);                                        /* 0 = communicator healthy */
+/* Before cnh_allocate (no external arena): take the arena from NCCL's allocator so that cnh_dp_init can
+ * register the weights and their gradients as a symmetric window (NCCL then runs its symmetric-memory
+ * kernels on the buffers themselves).  cnh_dp_symmetric: 1 once such a window is registered. */
+int cnh_dp_use_nccl_arena(cnh_net* net, int on);
+int cnh_dp_symmetric(cnh_net* net);
 /* CUDA graph of a step: begin; cnh_forward; cnh_backward; cnh_update; end; then cnh_graph_launch
  * replays it on the net's stream (replaces the per-launch cudaDeviceSynchronize cadence of
  * gpu/gpu_func.h:645-681).  Needs a non-default stream (cnh_set_stream). */

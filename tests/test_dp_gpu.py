@@ -1,6 +1,8 @@
-"""Data-parallel training on 2 GPUs (NCCL) against the single-GPU run of the same global batch:
-the per-step loss curve and the weights after the last update must agree to fp32 reassociation
-noise.  Needs two CUDA devices; skipped otherwise.  NVLS is switched off for the child ranks."""
+"""Data-parallel training on 2 GPUs (NCCL) against the single-GPU run of the same global batch, at the
+benchmark's own width: the token-mixing stack of 8 blocks of 1024, global batch 4096, SGD lr 0.01,
+200 steps from seed 0 (4 seeded batches in rotation).  The per-step loss curve (mean over the WHOLE
+batch) and the weights after the last update must agree to fp32 reassociation noise.  Needs two CUDA
+devices; skipped otherwise.  NVLS is switched off for the child ranks."""
 import os
 import socket
 
@@ -9,8 +11,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-KW = dict(n=256, blocks=2, m=10)
-GLOBAL_BATCH, STEPS, LR = 64, 6, 0.5
+KW = dict(n=1024, blocks=8, m=10)
+GLOBAL_BATCH, STEPS, LR, BATCHES = 4096, 200, 0.01, 4
 
 
 def _free_port():
@@ -35,8 +37,9 @@ def _train(rank, world, port, out):
     try:
         tr = DataParallelTrainer(configs.build_mixer, KW, global_batch=GLOBAL_BATCH, lr=LR, device=rank, seed=0)
         losses = []
+        data = [configs.make_batch(tr.spec, GLOBAL_BATCH, 0, step=s) for s in range(BATCHES)]
         for s in range(STEPS):
-            (xr, xi), labels = configs.make_batch(tr.spec, GLOBAL_BATCH, 0, step=s)
+            (xr, xi), labels = data[s % BATCHES]
             if s == 2:
                 tr.capture()            # the rest of the run replays the step as a CUDA graph
             l = tr.step((tr.shard(xr), tr.shard(xi)), tr.shard(labels))
@@ -45,7 +48,7 @@ def _train(rank, world, port, out):
                 dist.all_reduce(tot)
             losses.append(float(tot.item()) / GLOBAL_BATCH)
         tr.net.sync()
-        w = tr.net.get_values(tr.spec.layers["w1"])
+        w = tr.net.get_values(tr.spec.layers["w7"])
         h = tr.net.get_values(tr.spec.layers["h0"])
         out[(world, rank)] = (np.array(losses), w[0], w[1], h[0], h[1], tr.net.grad_arena()[2])
     finally:
@@ -65,7 +68,8 @@ def test_two_gpu_training_matches_single_gpu():
     one, r0, r1 = out[(1, 0)], out[(2, 0)], out[(2, 1)]
     assert one[5] >= 1
     assert np.linalg.norm(r0[0] - one[0]) / np.linalg.norm(one[0]) < 1e-4
-    assert one[0][-1] < one[0][0]
+    assert np.max(np.abs(r0[0] - one[0]) / one[0]) < 3e-4          # every single step, not only on average
+    assert one[0][-1] < 0.9 * one[0][0]                            # and the run did train
     for k in range(1, 5):
         assert np.array_equal(r0[k], r1[k])                     # replicas stay identical
         assert np.linalg.norm(r0[k] - one[k]) / np.linalg.norm(one[k]) < 1e-4
