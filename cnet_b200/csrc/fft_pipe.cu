@@ -155,13 +155,21 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
             if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
         }
+        // Eight table entries are read before the eight products that use them are stored: the compiler cannot
+        // move a shared-memory load above an earlier shared-memory store, so read one at a time every entry
+        // cost a full load latency between two stores (1500 of a row's 3700 clocks).
 #pragma unroll
-        for (int p = 0; p < R; ++p) {
-            const int k1 = bitrev<R>(p);                 // position p holds frequency k1
-            const float2 f = tws[k1 * R + t];            // e^{-2 pi i t k1/N}
-            const float c = f.x, s = SIGN < 0 ? f.y : -f.y;
-            sr[k1 * (R + 1) + t] = re[p] * c - im[p] * s;
-            si[k1 * (R + 1) + t] = re[p] * s + im[p] * c;
+        for (int p0 = 0; p0 < R; p0 += 8) {
+            float2 f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = tws[bitrev<R>(p0 + j) * R + t];   // e^{-2 pi i t k1/N} / 32
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = p0 + j, k1 = bitrev<R>(p);                         // position p holds frequency k1
+                const float c = f[j].x, s = SIGN < 0 ? f[j].y : -f[j].y;
+                sr[k1 * (R + 1) + t] = re[p] * c - im[p] * s;
+                si[k1 * (R + 1) + t] = re[p] * s + im[p] * c;
+            }
         }
         __syncwarp();
         CNB_STAMP(5);
