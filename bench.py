@@ -668,10 +668,15 @@ def main():
     ap.add_argument("--workload", default="mixer_dp4096", choices=sorted(WORKLOADS))
     ap.add_argument("--repeats", type=int, default=15,
                     help="the K-step measurement is repeated this many times and the median reported")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="override the workload's global batch (e.g. the per-rank batch of an N-GPU run on one GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="skip the short runs of the other configurations")
     ap.add_argument("--no-graph", action="store_true", help="launch the step kernel by kernel instead of as a CUDA graph")
     args = ap.parse_args()
+    if args.global_batch > 0:
+        b, kw, _, kind = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (b, kw, args.global_batch, kind)
     if args.impl == "reference":
         run_reference(args)
     elif WORKLOADS[args.workload][0] is None:

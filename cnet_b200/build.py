@@ -6,7 +6,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libcnet_b200.so")
-CSRC = ["context.cu", "elementwise.cu", "rowreduce.cu", "embed.cu", "cgemm_simt.cu", "cgemm_tc.cu", "linear.cu", "fft.cu", "fft_pipe.cu", "cgemv_skinny.cu"]
+CSRC = ["context.cu", "elementwise.cu", "rowreduce.cu", "embed.cu", "cgemm_simt.cu", "cgemm_tc.cu", "linear.cu", "fft.cu", "fft_pipe.cu", "cgemv_skinny.cu", "dp_allreduce.cu"]
 HOST = ["cnet.cpp", "capi.cpp", "dp_nccl.cpp", "model_saver.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]

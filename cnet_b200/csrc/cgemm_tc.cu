@@ -290,6 +290,14 @@ __device__ __forceinline__ void cluster_reduce(const TcParams& p, uint32_t smem_
     }
 }
 
+// Phase stamps of CTA 0 (a build with -DCNB_GEMM_TIMING only; read back from the status block): %globaltimer ns.
+#ifdef CNB_GEMM_TIMING
+#define CNB_GSTAMP(k, cond)                                                                        \
+    do { if (blockIdx.x == 0 && (cond)) p.status[900 + (k)] = (int) global_ns(); } while (0)
+#else
+#define CNB_GSTAMP(k, cond) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
            const __grid_constant__ CUtensorMap a_lo_re, const __grid_constant__ CUtensorMap a_lo_im,
@@ -297,6 +305,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
            const __grid_constant__ CUtensorMap b_lo_re, const __grid_constant__ CUtensorMap b_lo_im,
            const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
+    CNB_GSTAMP(0, threadIdx.x == 0);
     // operand stages need the alignment of their swizzle pattern; 1024 B covers every mode
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* stage_re = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
@@ -361,6 +370,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     // (and D written) only after that kernel has completed.
     cnb_pdl_trigger();
     cnb_pdl_wait();
+    CNB_GSTAMP(1, threadIdx.x == 0);
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -406,6 +416,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     uint32_t phase = (uint32_t) (it / STAGES) & 1;
                     ok = mbar_wait(full_bar(s), phase, abort_flag, p.status, 2);
                     if (!ok) break;
+                    CNB_GSTAMP(2, it == 0);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t st = smem_base + s * STAGE_BYTES;
 #pragma unroll
@@ -423,6 +434,26 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                         uint64_t a_hr = adesc(0), a_hi_ = adesc(1), a_lr = adesc(2), a_li = adesc(3);
                         uint64_t b_h = bdesc(4), b_l = bdesc(6);
                         uint32_t first = (kb == kb0 && j == 0) ? 0u : 1u;
+#ifdef CNB_GEMM_3M_PROBE
+                        // Throughput probe of the 3M (Gauss) form, results meaningless: nine 128 x 128 x 8 MMAs per
+                        // k-step (three real products x three TF32 terms) into three accumulators, in place of six
+                        // 128 x 256 x 8.  The operand planes of the stage stand in for the six planes per operand
+                        // that form would stage.
+                        {
+                            const uint32_t id128 = (idesc & ~(0x3Fu << 17)) | ((128u >> 3) << 17);
+                            const uint64_t b_hi_im = bdesc(5), b_li = bdesc(7);
+                            umma_tf32(tmem_base, a_lr, b_h, id128, first);
+                            umma_tf32(tmem_base, a_hr, b_l, id128, 1u);
+                            umma_tf32(tmem_base, a_hr, b_h, id128, 1u);
+                            umma_tf32(tmem_base + 128, a_li, b_hi_im, id128, first);
+                            umma_tf32(tmem_base + 128, a_hi_, b_li, id128, 1u);
+                            umma_tf32(tmem_base + 128, a_hi_, b_hi_im, id128, 1u);
+                            umma_tf32(tmem_base + 256, a_lr, b_hi_im, id128, first);
+                            umma_tf32(tmem_base + 256, a_hi_, b_l, id128, 1u);
+                            umma_tf32(tmem_base + 256, a_hr, b_hi_im, id128, 1u);
+                            continue;
+                        }
+#endif
                         umma_tf32(tmem_base, a_lr, b_h, idesc, first);      // small terms first
                         umma_tf32(tmem_base, a_hr, b_l, idesc, 1u);
                         umma_tf32(tmem_base, a_hr, b_h, idesc, 1u);
@@ -433,6 +464,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     umma_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                 }
                 if (ok) umma_commit(acc_full);
+                CNB_GSTAMP(3, true);
                 u += kb1 - kb0;
             }
         }
@@ -458,6 +490,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                 }
             }
             mbar_wait(acc_full, 0u, abort_flag, p.status, 3);
+            CNB_GSTAMP(4, et == 0);
             epi_bar_sync();
             if (!*abort_flag) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -483,6 +516,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     }
                 }
             }
+            CNB_GSTAMP(5, et == 0);
             u_end = u_begin;                             // nothing left for the loop below
         }
         bool live = true;
@@ -610,6 +644,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     if (p.cluster > 1) {
         // Every thread of every CTA of the cluster reaches both barriers, also after a bounded wait gave up.
         cluster_sync();                                  // all partial tiles are in shared memory
+        CNB_GSTAMP(6, threadIdx.x == 64);
         if (warp >= 2 && !*abort_flag) {
             const int tile = blockIdx.x / p.cluster;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
@@ -623,7 +658,9 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                 default: cluster_reduce<8>(p, smem_base, crank, m0, n0, et, vec_ok); break;
             }
         }
+        CNB_GSTAMP(7, threadIdx.x == 64);
         cluster_sync();                                  // no CTA leaves while a peer still reads its shared memory
+        CNB_GSTAMP(8, threadIdx.x == 64);
     }
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -285,9 +285,9 @@ int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, 
     // 2 rows per warp and pass; small batches take thinner CTAs so that the rows still spread over the SMs
     const long pairs = (B + 1) / 2;
     int warps = 16;
-    while (warps > 4 && pairs < (long) ctx->sm_count * warps / 2) warps /= 2;
+    while (warps > 4 && pairs < (long) usable_sms(ctx) * warps / 2) warps /= 2;
     const long blocks = (pairs + warps - 1) / warps;
-    const int grid = (int) std::max<long>(1, std::min<long>(blocks, ctx->sm_count));
+    const int grid = (int) std::max<long>(1, std::min<long>(blocks, usable_sms(ctx)));
     const int threads = warps * 32;
     if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out);
     else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out);
@@ -300,7 +300,7 @@ int skinny_bwd_x(cnb_ctx* ctx, const float* gr, const float* gi, const float* wr
     const bool vec = (in % 4 == 0) && aligned16(wr, wi, dr, di);
     const int w = vec ? 4 : 1;
     const int col_blocks = (in + 256 * w - 1) / (256 * w);
-    int chunks = std::max(1, ctx->sm_count * 2 / col_blocks);            // two CTAs per SM are resident
+    int chunks = std::max(1, usable_sms(ctx) * 2 / col_blocks);            // two CTAs per SM are resident
     chunks = std::min(chunks, B);
     const int rows = (B + chunks - 1) / chunks;
     chunks = (B + rows - 1) / rows;
@@ -316,7 +316,7 @@ int skinny_bwd_w(cnb_ctx* ctx, const float* gr, const float* gi, const float* xr
     const bool vec = (in % 4 == 0) && aligned16(xr, xi);
     int w = vec ? 4 : 1;
     int col_blocks = (in + 32 * w - 1) / (32 * w);
-    int chunks = (ctx->sm_count * 2 + col_blocks - 1) / col_blocks;      // two CTAs per SM are resident
+    int chunks = (usable_sms(ctx) * 2 + col_blocks - 1) / col_blocks;      // two CTAs per SM are resident
     chunks = std::max(1, std::min(chunks, std::min((B + 7) / 8, 128)));
     int rows = (B + chunks - 1) / chunks;
     chunks = (B + rows - 1) / rows;

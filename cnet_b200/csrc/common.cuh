@@ -41,6 +41,13 @@ extern thread_local int g_last_engine;
 
 inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// SMs a kernel sized as "one wave" should count on: all of them, or fewer while some are set aside for a
+// collective's kernels (cnb_set_gemm_sm_limit); sized for the whole device such a kernel would run a second,
+// nearly empty wave.
+inline int usable_sms(const cnb_ctx* ctx) {
+    return ctx->gemm_cta_limit > 0 && ctx->gemm_cta_limit < ctx->sm_count ? ctx->gemm_cta_limit : ctx->sm_count;
+}
+
 // fp32 SIMT complex GEMM on generic strides:
 //   D[m,n] (+)= sum_k A(m,k) * (conjB ? conj(B(n,k)) : B(n,k)) (+ R[m,n])
 //   A(m,k) = a[m*sam + k*sak], B(n,k) = b[n*sbn + k*sbk], D/R row-major with ld = N.

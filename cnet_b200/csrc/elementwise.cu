@@ -414,7 +414,7 @@ int colreduce_launch(cnb_ctx* ctx, int mode, const float* gr, const float* gi, c
                                     : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, colreduce_stage1_k<0, 1>, 256, 0));
         if (e != cudaSuccess || per_sm < 1) per_sm = 4;
     }
-    int chunks = std::max(1, ctx->sm_count * per_sm / col_blocks);
+    int chunks = std::max(1, cnb::usable_sms(ctx) * per_sm / col_blocks);
     int max_chunks = (B + 7) / 8;
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks > 128) chunks = 128;

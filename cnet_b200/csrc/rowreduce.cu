@@ -208,13 +208,10 @@ __global__ void __launch_bounds__(512) crossent_cached_k(const float* __restrict
     for (int v = 0; v < CACHE; ++v) {
         const int i = 4 * (threadIdx.x + v * blockDim.x);
         if (i < M) {
-            float4 p = scale4(a[v], co), q = scale4(b[v], co);
-            if (l >= i && l < i + 4) {                            // the label's own coefficient
-                const int k = l - i;
-                (&p.x)[k] = (&a[v].x)[k] * cl;
-                (&q.x)[k] = (&b[v].x)[k] * cl;
-            }
-            st4(dr, base + i, p); st4(di, base + i, q);
+            // the label's own coefficient (selects, not an indexed component: that would put the row in local memory)
+            const float c0 = (i == l) ? cl : co, c1 = (i + 1 == l) ? cl : co, c2 = (i + 2 == l) ? cl : co, c3 = (i + 3 == l) ? cl : co;
+            st4(dr, base + i, make_float4(a[v].x * c0, a[v].y * c1, a[v].z * c2, a[v].w * c3));
+            st4(di, base + i, make_float4(b[v].x * c0, b[v].y * c1, b[v].z * c2, b[v].w * c3));
         }
     }
 }

@@ -8,6 +8,8 @@ the backward; the fused SGD update runs after the last bucket with lr / global_b
 multi-GPU analogue of the reference's gpu_grad_from_clones + gpuUpdateInputs(l_rate / batch)
 (gpu/kernels.cpp:566-598, cnet.cpp:147).
 """
+import os
+
 import numpy as np
 
 from . import configs
@@ -74,10 +76,37 @@ class DataParallelTrainer:
         self.spec = builder(self.net, **builder_kwargs)
         for uid, (re, im) in configs.init_weights(self.spec, seed).items():
             self.net.set_values(uid, re, im)
-        self.comm = ("nccl" if self.world > 1 else "none") if comm == "auto" else comm
-        # several ranks over NCCL: the arena comes from NCCL's allocator, so the gradients can be a symmetric window
-        self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream,
-                          nccl_arena=self.world > 1 and self.comm == "nccl")
+        if comm == "auto":
+            comm = os.environ.get("CNB_DP_COMM", "nccl") if self.world > 1 else "none"
+        self.comm = comm
+        self.symm = None
+        if self.world > 1 and self.comm == "symm":
+            # the library's own all-reduce kernel on symmetric memory: torch only maps the arenas of all ranks into
+            # every process (peer pointers, a multicast address where the platform has one)
+            import torch.distributed._symmetric_memory as symm_mem
+            group = dist.group.WORLD
+            need = self.net.required_arena(self.local_batch)
+            sizes = torch.tensor([need], device="cuda", dtype=torch.int64)
+            dist.all_reduce(sizes, op=dist.ReduceOp.MAX)        # the same size (and so the same offsets) on every rank
+            arena = symm_mem.empty(int(sizes.item()), dtype=torch.uint8, device="cuda:%d" % device)
+            flags = symm_mem.empty(256, dtype=torch.int32, device="cuda:%d" % device)
+            flags.zero_()
+            ah, fh = symm_mem.rendezvous(arena, group), symm_mem.rendezvous(flags, group)
+            torch.cuda.synchronize()
+            dist.barrier()
+            self.symm = (arena, flags, ah, fh)
+            self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream, arena=arena)
+            mc = int(ah.multicast_ptr or 0)                     # 0 where the platform has no NVLink multicast
+            if os.environ.get("CNB_DP_MULTICAST", "1") == "0":
+                mc = 0
+            self.net.dp_set_symmetric(self.rank, self.world, mc, list(ah.buffer_ptrs), list(fh.buffer_ptrs),
+                                      int(os.environ.get("CNB_DP_CTAS", "0")))
+            self.multicast = bool(mc)
+            dist.barrier()
+        else:
+            # several ranks over NCCL: the arena comes from NCCL's allocator, so the gradients can be a symmetric window
+            self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream,
+                              nccl_arena=self.world > 1 and self.comm == "nccl")
         self.reducer = GradBucketReducer() if self.comm == "torch" else None
         if self.world > 1 and self.comm == "nccl":
             box = [self.net.dp_unique_id() if self.rank == 0 else None]
@@ -117,7 +146,7 @@ class DataParallelTrainer:
         communicator are set up outside the capture).
         """
         if self.comm == "torch" and self.world > 1:
-            raise RuntimeError("graph capture needs comm='nccl' (collectives issued by the host facade)")
+            raise RuntimeError("graph capture needs comm='nccl' or 'symm' (collectives issued by the host facade)")
         self.torch.cuda.synchronize()
         self.net.capture_begin()
         try:

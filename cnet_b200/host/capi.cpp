@@ -119,6 +119,11 @@ int cnh_dp_init(cnh_net* n, const char* id128, int rank, int nranks) {
 	n->net.setDataParallel(id128, rank, nranks); return status(n);
 }
 int cnh_dp_async_error(cnh_net* n) { return n->net.dataParallelError(); }
+int cnh_dp_allreduce_grads(cnh_net* n) { n->net.allReduceGradients(); return status(n); }
+int cnh_dp_set_symmetric(cnh_net* n, int rank, int world, void* multicast_base, void* const* arena_bases,
+                         void* const* flag_blocks, int ctas) {
+	n->net.setSymmetricPeers(rank, world, multicast_base, arena_bases, flag_blocks, ctas); return status(n);
+}
 int cnh_dp_use_nccl_arena(cnh_net* n, int on) { n->net.setNcclArena(on != 0); return 0; }
 int cnh_dp_symmetric(cnh_net* n) { return n->net.symmetricWindow() ? 1 : 0; }
 int cnh_capture_begin(cnh_net* n) { n->net.beginCapture(); return status(n); }

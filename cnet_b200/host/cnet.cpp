@@ -412,6 +412,11 @@ CNet::~CNet() {
 		cudaEventDestroy((cudaEvent_t) ev_side_fork_); cudaEventDestroy((cudaEvent_t) ev_side_join_);
 		cudaStreamDestroy((cudaStream_t) side_stream_);
 	}
+	if (sym_stream_) {
+		cudaStreamSynchronize((cudaStream_t) sym_stream_);
+		cudaEventDestroy((cudaEvent_t) ev_sym_fork_); cudaEventDestroy((cudaEvent_t) ev_sym_join_);
+		cudaStreamDestroy((cudaStream_t) sym_stream_);
+	}
 	if (copy_stream_) {
 		cudaStreamSynchronize((cudaStream_t) copy_stream_);
 		cudaEventDestroy((cudaEvent_t) ev_h2d_); cudaEventDestroy((cudaEvent_t) ev_commit_);
@@ -702,8 +707,9 @@ bool CNet::allocateOnGpu(int B) {
 		cnb_memset0(ctx_, wgrad_base_, total * sizeof(float), stream_);
 	}
 	size_t off = 0;
-	// fewer, larger buckets amortise the per-collective latency; the last one is exposed after backward
-	size_t bucket_floats = 9000000;
+	// Fewer, larger buckets amortise the per-collective latency; the last one is exposed after backward.  Four
+	// buckets of two blocks each at the benchmark net: 1.36 ms per step at 4 GPUs against 1.42 with eight, 1.46 with two.
+	size_t bucket_floats = 4500000;
 	if (const char* e = getenv("CNB_BUCKET_FLOATS")) bucket_floats = (size_t) atoll(e);
 	size_t bucket_begin = 0, bucket_first = 0;
 	for (size_t k = 0; k < weights.size(); ++k) {
@@ -1016,7 +1022,7 @@ void CNet::backward() {
 
 bool CNet::reduceBucket(size_t k) {
 	const Bucket& b = buckets_[k];
-	if ((nccl_.active() || hook_) && k == 0) {
+	if ((nccl_.active() || sym_active_ || hook_) && k == 0) {
 		// The arena accumulates until the update and is summed over the ranks in place: a second backward()
 		// before the update would reduce the already reduced part again (earlier micro-batches x ranks).
 		if (reduced_since_update_) {
@@ -1026,12 +1032,83 @@ bool CNet::reduceBucket(size_t k) {
 		}
 		reduced_since_update_ = true;
 	}
-	if (nccl_.active()) {
+	if (sym_active_) {
+		cudaStream_t cs = (cudaStream_t) sym_stream_;
+		if (cudaEventRecord((cudaEvent_t) ev_sym_fork_, (cudaStream_t) stream_) != cudaSuccess ||
+				cudaStreamWaitEvent(cs, (cudaEvent_t) ev_sym_fork_, 0) != cudaSuccess) {
+			fail(CNB_ERR_CUDA, "all-reduce: fork to the communication stream failed"); return false;
+		}
+		int rc = cnb_dp_allreduce(ctx_, &sym_, wgrad_base_ + b.begin, b.count, sym_stream_);
+		if (rc != CNB_OK) { fail(rc, "all-reduce"); return false; }
+		sym_pending_ = true;
+	} else if (nccl_.active()) {
 		if (!nccl_.allReduce(wgrad_base_ + b.begin, b.count, stream_)) { fail(CNB_ERR_CUDA, "all-reduce: " + nccl_.error()); return false; }
 	}
 	if (hook_) {
 		int rc = hook_(hook_user_, wgrad_base_ + b.begin, b.count, (int) k, (int) buckets_.size());
 		if (rc != 0) { fail(CNB_ERR_DEVICE, "gradient bucket hook returned " + std::to_string(rc)); return false; }
+	}
+	return true;
+}
+
+bool CNet::joinCollectives() {
+	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return false; }
+	if (sym_pending_) {
+		if (cudaEventRecord((cudaEvent_t) ev_sym_join_, (cudaStream_t) sym_stream_) != cudaSuccess ||
+				cudaStreamWaitEvent((cudaStream_t) stream_, (cudaEvent_t) ev_sym_join_, 0) != cudaSuccess) {
+			fail(CNB_ERR_CUDA, "all-reduce join: from the communication stream failed"); return false;
+		}
+		sym_pending_ = false;
+	}
+	return true;
+}
+
+bool CNet::allReduceGradients() {
+	if (!ctx_) { fail(CNB_ERR_ARG, "allReduceGradients: allocateOnGpu first"); return false; }
+	const bool hook_was = hook_ != nullptr;
+	BucketHook h = hook_;
+	hook_ = nullptr;                                // only the device collectives
+	bool flag = reduced_since_update_;
+	reduced_since_update_ = false;
+	bool ok = true;
+	for (size_t k = 0; k < buckets_.size() && ok; ++k) ok = reduceBucket(k);
+	reduced_since_update_ = flag;
+	if (hook_was) hook_ = h;
+	return ok && joinCollectives();
+}
+
+bool CNet::setSymmetricPeers(int rank, int world, void* multicast_base, void* const* arena_bases, void* const* flag_blocks, int ctas) {
+	if (!ctx_ || !ext_arena_) { fail(CNB_ERR_ARG, "setSymmetricPeers: allocateOnGpu on a caller-owned (symmetric) arena first"); return false; }
+	if (world < 1 || world > CNB_DP_MAX_RANKS || rank < 0 || rank >= world) { fail(CNB_ERR_ARG, "setSymmetricPeers: rank / world"); return false; }
+	if (world == 1) return true;
+	if (arena_bases[rank] != ext_arena_) { fail(CNB_ERR_ARG, "setSymmetricPeers: arena_bases[rank] is not this net's arena"); return false; }
+	for (const Bucket& b : buckets_)
+		if (b.begin % 4 || b.count % (4 * (size_t) world)) { fail(CNB_ERR_UNSUPPORTED, "setSymmetricPeers: a gradient bucket is not a multiple of 4 x world floats"); return false; }
+	cudaSetDevice(device_);
+	sym_ = cnb_dp_peers{};
+	sym_.rank = rank; sym_.world = world; sym_.multicast_base = multicast_base; sym_.arena_bytes = arena_bytes_; sym_.ctas = ctas;
+	for (int r = 0; r < world; ++r) { sym_.arena_base[r] = arena_bases[r]; sym_.flags[r] = flag_blocks[r]; }
+	void* p = nullptr;
+	int rc = cnb_alloc(ctx_, cnb_dp_state_bytes(), &p);
+	if (rc != CNB_OK) { fail(rc, "setSymmetricPeers: state"); return false; }
+	cnb_memset0(ctx_, p, cnb_dp_state_bytes(), stream_);
+	cnb_sync(ctx_, stream_);
+	sym_.state = p;
+	cudaStream_t st;
+	cudaEvent_t e0, e1;
+	if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess ||
+			cudaEventCreateWithFlags(&e0, cudaEventDisableTiming) != cudaSuccess ||
+			cudaEventCreateWithFlags(&e1, cudaEventDisableTiming) != cudaSuccess) {
+		fail(CNB_ERR_CUDA, "setSymmetricPeers: stream / events"); return false;
+	}
+	sym_stream_ = st; ev_sym_fork_ = e0; ev_sym_join_ = e1;
+	sym_active_ = true;
+	{   // SMs left to the reduction's CTAs during backward(), as for NCCL's
+		int reserve = ctas > 0 ? ctas : 6;
+		if (const char* e = getenv("CNB_DP_RESERVED_SMS")) reserve = atoi(e);
+		int sms = 0;
+		cnb_device_info(device_, &sms, nullptr, nullptr, nullptr);
+		if (reserve > 0 && sms > reserve) dp_gemm_ctas_ = sms - reserve;
 	}
 	return true;
 }
@@ -1058,7 +1135,10 @@ bool CNet::setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nran
 	if (nccl_.active()) {
 		// the GEMM is one CTA per SM and fills shared memory; keep a few SMs for NCCL's kernels so the
 		// bucket all-reduces really overlap the backward pass (CNB_DP_RESERVED_SMS overrides, 0 = none)
-		int reserve = 12;
+		// On a registered symmetric window NCCL reduces in the switch with a handful of CTAs (5 at 4 ranks); its
+		// copy-based kernels on unregistered buffers want more.  Measured at 4 GPUs, 1024 rows each: 6 reserved
+		// SMs 1.36 ms per step, 12: 1.45, none: 1.54.
+		int reserve = nccl_.hasWindow() ? 6 : 12;
 		if (const char* e = getenv("CNB_DP_RESERVED_SMS")) reserve = atoi(e);
 		int sms = 0;
 		cnb_device_info(device_, &sms, nullptr, nullptr, nullptr);
@@ -1082,7 +1162,7 @@ bool CNet::endCapture() {
 	if (!capturing_) { fail(CNB_ERR_ARG, "endCapture: no capture in progress"); return false; }
 	// a backward() captured without an update leaves collectives on the communication stream: bring it back
 	// into the capturing stream, or the capture cannot end
-	if (!nccl_.join(stream_)) fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error());
+	joinCollectives();
 	capturing_ = false;
 	graph_launches_ = cnb_launch_count() - graph_launches_;
 	cudaGraph_t g = nullptr;
@@ -1122,7 +1202,7 @@ void CNet::backward(int label) {
 void CNet::updateInputs(float lr) {
 	if (!ctx_ || !wgrad_count_) return;
 	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, 0);
-	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
+	if (!joinCollectives()) return;
 	// the new Linear weights leave the update already split, once, for the next forward and dX* products
 	std::vector<cnb_split_span> spans;
 	std::vector<Linear*> fused;
@@ -1156,7 +1236,7 @@ void CNet::adamUpdate(float lr, float beta, int t) {
 		return;
 	}
 	if (dp_gemm_ctas_ > 0) cnb_set_gemm_sm_limit(ctx_, 0);
-	if (!nccl_.join(stream_)) { fail(CNB_ERR_CUDA, "all-reduce join: " + nccl_.error()); return; }
+	if (!joinCollectives()) return;
 	if (!momentum_base_) {
 		void* p = nullptr;
 		int rc = cnb_alloc(ctx_, wgrad_count_ * sizeof(float), &p);

@@ -415,6 +415,13 @@ class CNet {
 	void* ev_side_join_ = nullptr;
 	int sm_count_ = 0;
 	NcclGroup nccl_;                                // native data parallelism (setDataParallel)
+	// data parallelism over symmetric memory with the library's own all-reduce kernel (setSymmetricPeers)
+	cnb_dp_peers sym_ = {};
+	bool sym_active_ = false, sym_pending_ = false;
+	void* sym_stream_ = nullptr;
+	void* ev_sym_fork_ = nullptr;
+	void* ev_sym_join_ = nullptr;
+	bool joinCollectives();                         // the compute stream waits for every collective in flight
 	void* graph_exec_ = nullptr;                    // cudaGraphExec_t of a captured step
 	bool capturing_ = false;
 	unsigned long long graph_launches_ = 0;         // kernels inside the captured step
@@ -452,7 +459,15 @@ public:
 	// updateInputs() waits for them; the caller passes lr / global_batch.
 	static bool ncclUniqueId(char out[kNcclUniqueIdBytes], std::string* err) { return NcclGroup::uniqueId(out, err); }
 	bool setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nranks);
+	// Data parallelism without NCCL in the data path: the arena of every rank is symmetric memory mapped into
+	// every process (base pointers, optional multicast address, a zeroed flag block per rank; see cnb_dp_allreduce).
+	// backward() then sums every finished gradient bucket with the library's own kernel on a communication
+	// stream; its CTAs run beside the GEMM's on the same SMs, so no SMs are set aside.  Call after allocateOnGpu.
+	bool setSymmetricPeers(int rank, int world, void* multicast_base, void* const* arena_bases, void* const* flag_blocks, int ctas);
 	int dataParallelError() { return nccl_.asyncError(); }
+	// Sums the whole weight-gradient arena over the ranks now (every bucket, then joins the compute stream):
+	// what backward() does bucket by bucket, as one call, for callers that drive the layers themselves.
+	bool allReduceGradients();
 	// CUDA graph of a step: beginCapture(); forward(); backward(); updateInputs(lr); endCapture();
 	// then launchGraph() replays it (same batch buffers, labels and learning rate).
 	bool beginCapture();

@@ -124,6 +124,10 @@ SIGNATURES = {
     "cnh_dp_unique_id": (C.c_int, [C.c_char_p]),
     "cnh_dp_init": (C.c_int, [_vp, C.c_char_p, C.c_int, C.c_int]),
     "cnh_dp_async_error": (C.c_int, [_vp]),
+    "cnh_dp_allreduce_grads": (C.c_int, [_vp]),
+    "cnh_dp_set_symmetric": (C.c_int, [_vp, C.c_int, C.c_int, _vp, C.POINTER(_vp), C.POINTER(_vp), C.c_int]),
+    "cnb_dp_state_bytes": (_sz, []),
+    "cnb_dp_allreduce": (C.c_int, [_vp, _vp, _P, _sz, _vp]),
     "cnh_dp_use_nccl_arena": (C.c_int, [_vp, C.c_int]),
     "cnh_dp_symmetric": (C.c_int, [_vp]),
     "cnh_capture_begin": (C.c_int, [_vp]),

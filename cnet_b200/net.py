@@ -114,14 +114,23 @@ class Net:
         return self.lib.cnh_type_of(self.h, uid)
 
     # ----------------------------------------------------------------- device
-    def allocate(self, batch, fuse=True, stream=None, nccl_arena=False):
+    def required_arena(self, batch):
+        return self.arena_bytes or self.lib.cnh_required_arena(self.h, batch)
+
+    def allocate(self, batch, fuse=True, stream=None, nccl_arena=False, arena=None):
         """allocateOnGpu(batch): plan the batched tensors in one arena and upload the weights.
-        nccl_arena: the host facade takes the arena from NCCL's allocator (for a symmetric window in dp_init)."""
+        nccl_arena: the host facade takes the arena from NCCL's allocator (for a symmetric window in dp_init).
+        arena: a uint8 CUDA tensor of at least required_arena(batch) bytes to use (e.g. symmetric memory)."""
         import torch
         if not torch.cuda.is_available():
             raise _lib.CnetError("no CUDA device: the path has no CPU fallback")
-        need = self.arena_bytes or self.lib.cnh_required_arena(self.h, batch)
-        if nccl_arena:
+        need = self.required_arena(batch)
+        if arena is not None:
+            assert arena.numel() >= need and arena.dtype == torch.uint8
+            self.arena = arena
+            need = arena.numel()
+            ext = arena.data_ptr()
+        elif nccl_arena:
             torch.cuda.set_device(self.device)
             self.lib.cnh_dp_use_nccl_arena(self.h, 1)
             ext = None
@@ -222,6 +231,17 @@ class Net:
         if _lib.load().cnh_dp_unique_id(buf) != 0:
             raise _lib.CnetError("ncclGetUniqueId failed (is libnccl.so.2 loadable?)")
         return buf.raw
+
+    def dp_set_symmetric(self, rank, world, multicast_ptr, arena_ptrs, flag_ptrs, ctas=0):
+        """setSymmetricPeers: every rank's arena and flag block as mapped in this process (symmetric memory)."""
+        a = (C.c_void_p * world)(*[C.c_void_p(int(x)) for x in arena_ptrs])
+        f = (C.c_void_p * world)(*[C.c_void_p(int(x)) for x in flag_ptrs])
+        self._check(self.lib.cnh_dp_set_symmetric(self.h, rank, world, C.c_void_p(int(multicast_ptr) or None), a, f, ctas),
+                    "setSymmetricPeers")
+
+    def dp_allreduce_grads(self):
+        """Sum the whole weight-gradient arena over the ranks now."""
+        self._check(self.lib.cnh_dp_allreduce_grads(self.h), "allReduceGradients")
 
     def capture_begin(self):
         self._check(self.lib.cnh_capture_begin(self.h), "beginCapture")

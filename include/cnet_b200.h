@@ -304,6 +304,30 @@ int cnb_sgd_update_split(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, i
 int cnb_adam_update(cnb_ctx* ctx, float* w, float* m, float* g, size_t n, float lr, float beta, int t,
                     void* stream);
 
+/* ------------------------------------------------------------- data parallelism
+ * Sum of `count` floats at `local` over the ranks of one NVSwitch domain, in place, by this library's own kernel
+ * on symmetric memory (no counterpart in the reference, which is single-GPU; the intra-GPU analogue is
+ * gpu_grad_from_clones, gpu/kernels.cpp:566-598).  The caller maps every rank's arena into this process (peer
+ * pointers, e.g. torch.distributed symmetric memory or cuMem handles) and, where the platform supports it, binds
+ * them to one multicast address; `flags` are CNB_DP_MAX_RANKS zeroed 32-bit words per rank in symmetric memory,
+ * `state` is cnb_dp_state_bytes() of zeroed local device memory.  Rank r sums its 1/world slice of the range over
+ * all ranks (in the switch with multimem.ld_reduce, else by loads from every peer) and writes it to all ranks.
+ * `local` must lie inside the arena, 16-byte aligned, count a multiple of 4 x world.  Every rank must make the
+ * same sequence of calls.  Waits on peers are bounded: a missing peer sets the error word read by
+ * cnb_check_device_status.  ctas = 0: one CTA per SM (256 threads, no shared memory: they run beside the GEMM's). */
+#define CNB_DP_MAX_RANKS 8
+typedef struct cnb_dp_peers {
+    int rank, world;
+    void* multicast_base;                    /* the arena at its multicast address, or NULL */
+    void* arena_base[CNB_DP_MAX_RANKS];      /* every rank's arena as mapped in this process; [rank] is the local one */
+    size_t arena_bytes;
+    void* flags[CNB_DP_MAX_RANKS];           /* every rank's flag block as mapped in this process */
+    void* state;                             /* local */
+    int ctas;
+} cnb_dp_peers;
+size_t cnb_dp_state_bytes(void);
+int cnb_dp_allreduce(cnb_ctx* ctx, const cnb_dp_peers* peers, float* local, size_t count, void* stream);
+
 /* Number of kernels this library has launched in this process (diagnostics / benches). */
 unsigned long long cnb_launch_count(void);
 

@@ -81,6 +81,14 @@ void* cnh_context(cnh_net* net);                                             /* 
 int cnh_dp_unique_id(char* out128);
 int cnh_dp_init(cnh_net* net, const char* id128, int rank, int nranks);
 int cnh_dp_async_error(cnh_net* net);                                        /* 0 = communicator healthy */
+/* Sums the whole weight-gradient arena over the ranks now, on the communication stream, and makes the net's
+ * stream wait for it: what cnh_backward does bucket by bucket, as one call. */
+int cnh_dp_allreduce_grads(cnh_net* net);
+/* Data parallelism with this library's own all-reduce kernel on symmetric memory (cnb_dp_allreduce) instead of
+ * NCCL: after cnh_allocate on a caller-owned arena that is symmetric memory, pass every rank's arena base as
+ * mapped in this process, the multicast address of the arena (or NULL) and one zeroed flag block per rank. */
+int cnh_dp_set_symmetric(cnh_net* net, int rank, int world, void* multicast_base, void* const* arena_bases,
+                         void* const* flag_blocks, int ctas);
 /* Before cnh_allocate (no external arena): take the arena from NCCL's allocator so that cnh_dp_init can
  * register the weights and their gradients as a symmetric window (NCCL then runs its symmetric-memory
  * kernels on the buffers themselves).  cnh_dp_symmetric: 1 once such a window is registered. */

@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _train(rank, world, port, out):
+def _train(rank, world, port, out, comm="auto"):
     import torch
     import torch.distributed as dist
     from cnet_b200 import configs
@@ -35,7 +35,7 @@ def _train(rank, world, port, out):
         os.environ["MASTER_PORT"] = str(port)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        tr = DataParallelTrainer(configs.build_mixer, KW, global_batch=GLOBAL_BATCH, lr=LR, device=rank, seed=0)
+        tr = DataParallelTrainer(configs.build_mixer, KW, global_batch=GLOBAL_BATCH, lr=LR, device=rank, seed=0, comm=comm)
         losses = []
         data = [configs.make_batch(tr.spec, GLOBAL_BATCH, 0, step=s) for s in range(BATCHES)]
         for s in range(STEPS):
@@ -50,22 +50,27 @@ def _train(rank, world, port, out):
         tr.net.sync()
         w = tr.net.get_values(tr.spec.layers["w7"])
         h = tr.net.get_values(tr.spec.layers["h0"])
-        out[(world, rank)] = (np.array(losses), w[0], w[1], h[0], h[1], tr.net.grad_arena()[2])
+        out[(world, rank, comm)] = (np.array(losses), w[0], w[1], h[0], h[1], tr.net.grad_arena()[2])
     finally:
         if world > 1:
             dist.destroy_process_group()
 
 
-def test_two_gpu_training_matches_single_gpu():
+@pytest.mark.parametrize("comm", ["nccl", "symm"])
+def test_two_gpu_training_matches_single_gpu(comm):
+    """comm = nccl: NCCL all-reduce on the registered symmetric window; symm: the library's own all-reduce kernel
+    on torch symmetric memory (multimem where the platform has it)."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_train, args=(1, 0, out), nprocs=1, join=True)
-    mp.spawn(_train, args=(2, _free_port(), out), nprocs=2, join=True)
-    one, r0, r1 = out[(1, 0)], out[(2, 0)], out[(2, 1)]
+    if (1, 0, "auto") not in _SINGLE:
+        mp.spawn(_train, args=(1, 0, out), nprocs=1, join=True)
+        _SINGLE[(1, 0, "auto")] = out[(1, 0, "auto")]
+    mp.spawn(_train, args=(2, _free_port(), out, comm), nprocs=2, join=True)
+    one, r0, r1 = _SINGLE[(1, 0, "auto")], out[(2, 0, comm)], out[(2, 1, comm)]
     assert one[5] >= 1
     assert np.linalg.norm(r0[0] - one[0]) / np.linalg.norm(one[0]) < 1e-4
     assert np.max(np.abs(r0[0] - one[0]) / one[0]) < 3e-4          # every single step, not only on average
@@ -73,3 +78,6 @@ def test_two_gpu_training_matches_single_gpu():
     for k in range(1, 5):
         assert np.array_equal(r0[k], r1[k])                     # replicas stay identical
         assert np.linalg.norm(r0[k] - one[k]) / np.linalg.norm(one[k]) < 1e-4
+
+
+_SINGLE = {}
