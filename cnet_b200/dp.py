@@ -77,23 +77,26 @@ class DataParallelTrainer:
         for uid, (re, im) in configs.init_weights(self.spec, seed).items():
             self.net.set_values(uid, re, im)
         if comm == "auto":
-            comm = os.environ.get("CNB_DP_COMM", "nccl") if self.world > 1 else "none"
+            # several ranks: the library's own all-reduce on symmetric memory where the platform maps it with a
+            # multicast address, else NCCL on a registered window (CNB_DP_COMM = symm | nccl forces one)
+            comm = os.environ.get("CNB_DP_COMM", "symm?") if self.world > 1 else "none"
         self.comm = comm
         self.symm = None
+        if self.world > 1 and self.comm in ("symm", "symm?"):
+            made = self._symmetric_arena(device)
+            ok = torch.tensor([1 if made and (self.comm == "symm" or made[2].multicast_ptr) else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)            # every rank takes the same path
+            if int(ok.item()) == 0:
+                if self.comm == "symm":
+                    raise RuntimeError("symmetric memory could not be set up on every rank")
+                made = None
+                self.comm = "nccl"
+            else:
+                self.comm = "symm"
         if self.world > 1 and self.comm == "symm":
             # the library's own all-reduce kernel on symmetric memory: torch only maps the arenas of all ranks into
             # every process (peer pointers, a multicast address where the platform has one)
-            import torch.distributed._symmetric_memory as symm_mem
-            group = dist.group.WORLD
-            need = self.net.required_arena(self.local_batch)
-            sizes = torch.tensor([need], device="cuda", dtype=torch.int64)
-            dist.all_reduce(sizes, op=dist.ReduceOp.MAX)        # the same size (and so the same offsets) on every rank
-            arena = symm_mem.empty(int(sizes.item()), dtype=torch.uint8, device="cuda:%d" % device)
-            flags = symm_mem.empty(256, dtype=torch.int32, device="cuda:%d" % device)
-            flags.zero_()
-            ah, fh = symm_mem.rendezvous(arena, group), symm_mem.rendezvous(flags, group)
-            torch.cuda.synchronize()
-            dist.barrier()
+            arena, flags, ah, fh = made
             self.symm = (arena, flags, ah, fh)
             self.net.allocate(self.local_batch, fuse=fuse, stream=self.stream.cuda_stream, arena=arena)
             mc = int(ah.multicast_ptr or 0)                     # 0 where the platform has no NVLink multicast
@@ -121,6 +124,27 @@ class DataParallelTrainer:
                 self.reducer.on_bucket(arena[off:off + 4 * count].view(torch.float32))
                 return 0
             self.net.set_bucket_hook(hook)
+
+    def _symmetric_arena(self, device):
+        """(arena, flags, arena handle, flags handle) in torch symmetric memory, or None if that fails here."""
+        import torch.distributed as dist
+        torch = self.torch
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            group = dist.group.WORLD
+            need = self.net.required_arena(self.local_batch)
+            sizes = torch.tensor([need], device="cuda", dtype=torch.int64)
+            dist.all_reduce(sizes, op=dist.ReduceOp.MAX)        # the same size (and so the same offsets) on every rank
+            arena = symm_mem.empty(int(sizes.item()), dtype=torch.uint8, device="cuda:%d" % device)
+            flags = symm_mem.empty(256, dtype=torch.int32, device="cuda:%d" % device)
+            flags.zero_()
+            ah, fh = symm_mem.rendezvous(arena, group), symm_mem.rendezvous(flags, group)
+            torch.cuda.synchronize()
+            return arena, flags, ah, fh
+        except Exception as e:                                   # no symmetric memory on this platform / build
+            import sys
+            print("cnet_b200: symmetric memory unavailable (%s: %s)" % (type(e).__name__, e), file=sys.stderr)
+            return None
 
     def upload(self, host_in, host_labels):
         """Copies this rank's shard (pinned host tensors or numpy arrays) to the device."""
