@@ -361,6 +361,15 @@ def _roofline(workload, kw, B, gbatch, step_ms, device, hbm_kernels=True):
         cases = [("hadamard_gelu_fwd_k", lambda: ctx.hadamard_gelu_fwd(u, h), 24.0 * B * N),
                  ("colreduce_stage1_k<1> (gelu'+hadamard bwd + dh* partials)", lambda: ctx.hadamard_gelu_bwd(g, a, u, h), 32.0 * B * N),
                  (fft_name, lambda: ctx.dft_fwd(u), 16.0 * B * N)]
+        if ctx.lib.cnb_dft_fused_ok(N):
+            # the forms that run inside the step: forward with the Hadamard + CGelu + hi/lo split tail (reads x; writes
+            # u and four split planes), backward accumulating into the gradient (reads g, read-modify-writes dx)
+            us, sp = ctx.dft_hadamard_gelu_fwd(u, h)
+            acc = ctx._new(B, N)
+            cases.append(("fft1024_pipe_k<-1> + Hadamard + CGelu + split tail (as in the step)" if N == 1024 else "FourierTrans forward + tail",
+                          lambda: ctx.dft_hadamard_gelu_fwd(u, h, u=us, split=sp), 32.0 * B * N))
+            cases.append(("fft1024_pipe_k<+1> backward, reduce-add into the gradient (as in the step)" if N == 1024 else "FourierTrans backward + accumulate",
+                          lambda: ctx.dft_bwd(g, out=acc), 24.0 * B * N))
         n_w = 2 * n_in * n_out * max(1, kw.get("blocks", 1))       # the whole weight arena of the net
         wflat = torch.randn(n_w, device="cuda")
         gflat = torch.randn(n_w, device="cuda")

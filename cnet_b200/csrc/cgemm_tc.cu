@@ -53,6 +53,7 @@ struct TcParams {
     int a_mn, b_mn;           // operand stored [K, rows] (MN-major) instead of [rows, K] (K-major)
     int cluster;              // > 1: that many CTAs of one cluster share a tile, each a slice of K
     int whole_per_cta;        // > 0: every CTA first takes that many whole tiles, then its run of the remaining units
+    int segments;             // > 0: CTA r takes k-segment r / tiles of tile r % tiles (units_per_cta k-blocks each)
     int* status;
 };
 
@@ -331,6 +332,16 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         u2_end = min(total_units, u2_begin + p.units_per_cta);
         u_begin = lead * blockIdx.x;
         u_end = u_begin + lead;
+    }
+    if (p.segments > 0) {
+        // Capped chains (K > 4096): consecutive CTAs take the SAME k-segment of consecutive tiles, so the CTAs that
+        // run together read the same columns of A and B and share them through L2 (tile-major runs had every CTA
+        // of a wave on its own k-range: 5.0 GB of DRAM reads for 0.8 GB of operands at 1024 x 2048 x 16384).
+        const long tiles = (long) tiles_m * tiles_n;
+        const long seg = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+        u_begin = tile * k_blocks + seg * p.units_per_cta;
+        u_end = min(u_begin + p.units_per_cta, (tile + 1) * k_blocks);
+        if (u_begin > u_end) u_begin = u_end;
     }
     const uint32_t crank = p.cluster > 1 ? cluster_rank() : 0;
     if (p.cluster > 1) {                                 // one tile per cluster, an even slice of its k-blocks per CTA
@@ -858,14 +869,17 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     // reached 1e-3 on a 443-k-block chain whose accumulator one large term dominated (the gradient of a loss
     // through a K = 8192 product).  Runs are therefore capped at kMaxChain k-blocks (the partial tiles are summed
     // outside, in fp32 round-to-nearest): several equal waves of CTAs instead of one persistent wave.
-    // Only K > 4096 gets here with longer runs; a whole tile of K <= 4096 is at most 256 k-blocks.
+    // Only K > 4096 gets here with longer runs; a whole tile of K <= 4096 is at most 256 k-blocks.  Each tile is cut
+    // into equal segments and the CTAs are numbered segment-major (see the kernel).
     constexpr long kMaxChain = 64;
+    int segments = 0;
     if (!whole_tiles && upc > kMaxChain && k_blocks > 256) {
-        const long waves = (total + (long) sms * kMaxChain - 1) / ((long) sms * kMaxChain);
-        ctas = (long) sms * waves;
-        upc = (total + ctas - 1) / ctas;
+        segments = (int) ((k_blocks + kMaxChain - 1) / kMaxChain);       // per tile, each at most kMaxChain k-blocks
+        upc = (k_blocks + segments - 1) / segments;
+        ctas = (long) tiles * segments;
+    } else {
+        ctas = (total + upc - 1) / upc;
     }
-    ctas = (total + upc - 1) / upc;
     int whole_per_cta = 0;
     int clear_from_row = 0;                              // rows of D below this one are only ever stored whole
     if (lead_whole) {
@@ -886,7 +900,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
             if ((long) tiles * c <= sms && k_blocks / c >= 4) { cluster = c; break; }
     }
     if (cluster > 1) { ctas = (long) tiles * cluster; upc = 0; }
-    bool splits_tiles = cluster == 1 && (lead_whole ? upc > 0 : (upc % k_blocks) != 0);
+    bool splits_tiles = cluster == 1 && (lead_whole ? upc > 0 : (segments > 0 || (upc % k_blocks) != 0));
     if (splits_tiles && !accumulate) {
         // one launch clears both planes (they need not be adjacent or in one allocation)
         const size_t first = (size_t) clear_from_row * N;
@@ -903,6 +917,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.cluster = cluster;
     p.whole_per_cta = whole_per_cta;
+    p.segments = segments;
     p.status = ctx->d_status;
     CNB_CUDA(cnb::launch(cgemm_tc_k, dim3((unsigned) ctas), dim3(NUM_THREADS), SMEM_BYTES, st, cluster, maps[0], maps[1], maps[2],
                          maps[3], maps[4], maps[5], maps[6], maps[7], p));

@@ -194,11 +194,23 @@ __global__ void __launch_bounds__(512) crossent_cached_k(const float* __restrict
         const int i = 4 * (threadIdx.x + v * blockDim.x);
         if (i < M) { a[v] = ld4(zr, base + i); b[v] = ld4(zi, base + i); s += dot4(a[v], a[v]) + dot4(b[v], b[v]); }
     }
-    s = block_sum(s, sm);
-    const float S = fmaxf(s, 1e-15f);
+    // the label's element is handed over by the thread that holds it (a global load after the reduction would
+    // put an L2 round trip on every row's critical path)
+    __shared__ float s_lab[2];
     int l = labels[blockIdx.x];
     l = min(max(l, 0), M - 1);
-    const float lr = zr[base + l], li = zi[base + l];
+#pragma unroll
+    for (int v = 0; v < CACHE; ++v) {
+        const int i = 4 * (threadIdx.x + v * blockDim.x);
+        if (i < M && l >= i && l < i + 4) {
+            const int k = l - i;
+            s_lab[0] = k == 0 ? a[v].x : k == 1 ? a[v].y : k == 2 ? a[v].z : a[v].w;
+            s_lab[1] = k == 0 ? b[v].x : k == 1 ? b[v].y : k == 2 ? b[v].z : b[v].w;
+        }
+    }
+    s = block_sum(s, sm);                                 // its barriers also publish s_lab
+    const float S = fmaxf(s, 1e-15f);
+    const float lr = s_lab[0], li = s_lab[1];
     const float m2 = lr * lr + li * li;
     if (threadIdx.x == 0) loss[blockIdx.x] = -logf(fmaxf(m2 / S, 1e-15f));
     if (dr == nullptr) return;

@@ -79,7 +79,10 @@ class DataParallelTrainer:
         if comm == "auto":
             # several ranks: the library's own all-reduce on symmetric memory where the platform maps it with a
             # multicast address, else NCCL on a registered window (CNB_DP_COMM = symm | nccl forces one)
-            comm = os.environ.get("CNB_DP_COMM", "symm?") if self.world > 1 else "none"
+            # The own kernel has run on 2 and 4 GPUs of this pool; no 8-GPU machine could be had to run it on, so
+            # 8 ranks take NCCL (on the same in-switch reduction) unless CNB_DP_COMM=symm asks otherwise.
+            default = "symm?" if self.world <= 4 else "nccl"
+            comm = os.environ.get("CNB_DP_COMM", default) if self.world > 1 else "none"
         self.comm = comm
         self.symm = None
         if self.world > 1 and self.comm in ("symm", "symm?"):

@@ -1128,7 +1128,8 @@ bool CNet::setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nran
 			uintptr_t end = reinterpret_cast<uintptr_t>(own_nccl_arena_) + arena_bytes_;
 			if (hi > end) hi = end;
 			if (!nccl_.registerWindow(reinterpret_cast<void*>(lo), hi - lo)) {
-				fail(CNB_ERR_CUDA, "setDataParallel: " + nccl_.error()); return false;
+				// not fatal: the all-reduce then runs NCCL's copy-based kernels on the unregistered arena
+				std::cerr << "cnet_b200: gradients not registered as a symmetric window (" << nccl_.error() << ")" << std::endl;
 			}
 		}
 	}

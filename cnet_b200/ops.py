@@ -114,6 +114,17 @@ class Context:
                    "dft_bwd")
         return dx
 
+    def dft_hadamard_gelu_fwd(self, x, h, u=None, split=None):
+        """FourierTrans forward with the Hadamard(h) -> CGelu tail in the same kernel: u = FFT(x) and the hi/lo
+        split planes of y = gelu(u o h) (y itself is hi + lo and is not stored).  Returns (u, split)."""
+        B, N = x[0].shape
+        u = u if u is not None else self._new(B, N)
+        if split is None:
+            split = self.torch.empty(self.lib.cnb_split_floats(B * N), dtype=self.torch.float32, device="cuda")
+        _lib.check(self.lib.cnb_dft_hadamard_gelu_fwd(self.h, _p(x[0]), _p(x[1]), _p(h[0]), _p(h[1]), _p(u[0]), _p(u[1]),
+                                                      None, None, _p(split), B, N, self._stream()), "dft_hadamard_gelu_fwd")
+        return u, split
+
     # ------------------------------------------------------------ element-wise
     def hadamard_fwd(self, u, v):
         B, N = u[0].shape
