@@ -7,14 +7,14 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libcnet_b200.so")
 CSRC = ["context.cu", "elementwise.cu", "rowreduce.cu", "embed.cu", "cgemm_simt.cu", "cgemm_tc.cu", "linear.cu", "fft.cu", "fft_pipe.cu", "cgemv_skinny.cu", "dp_allreduce.cu"]
-HOST = ["cnet.cpp", "capi.cpp", "dp_nccl.cpp", "model_saver.cpp"]
+HOST = ["cnet.cpp", "capi.cpp", "dp_nccl.cpp", "model_saver.cpp", "data_reader.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 
 
 def _sources():
     src = [os.path.join(HERE, "csrc", f) for f in CSRC] + [os.path.join(HERE, "host", f) for f in HOST]
-    deps = src + [os.path.join(HERE, "csrc", "common.cuh"), os.path.join(HERE, "host", "cnet.h"), os.path.join(HERE, "host", "dp_nccl.h"),
+    deps = src + [os.path.join(HERE, "csrc", "common.cuh"), os.path.join(HERE, "host", "cnet.h"), os.path.join(HERE, "host", "dp_nccl.h"), os.path.join(HERE, "host", "data_reader.h"),
                   os.path.join(HERE, "..", "include", "cnet_b200.h"),
                   os.path.join(HERE, "..", "include", "cnet_b200_host.h")]
     return src, deps

@@ -1,6 +1,7 @@
 // Flat C binding of the host facade (declared in include/cnet_b200_host.h).
 #include "../../include/cnet_b200_host.h"
 #include "cnet.h"
+#include "data_reader.h"
 
 using namespace cnet_b200;
 
@@ -130,5 +131,19 @@ int cnh_capture_begin(cnh_net* n) { n->net.beginCapture(); return status(n); }
 int cnh_capture_end(cnh_net* n) { n->net.endCapture(); return status(n); }
 int cnh_graph_launch(cnh_net* n) { n->net.launchGraph(); return status(n); }
 unsigned long long cnh_graph_kernel_count(cnh_net* n) { return n->net.graphKernelCount(); }
+
+// MnistDataReader (data/data.h:82-165) behind a handle
+void* cnh_mnist_open(const char* image_file, const char* label_file, int count) {
+	MnistDataReader* r = new MnistDataReader();
+	if (!r->Open(image_file, label_file, count) || !r->readData()) { delete r; return nullptr; }
+	return r;
+}
+void cnh_mnist_close(void* h) { delete static_cast<MnistDataReader*>(h); }
+int cnh_mnist_size(void* h) { return h ? static_cast<MnistDataReader*>(h)->size() : CNB_ERR_ARG; }
+int cnh_mnist_shuffle(void* h, unsigned seed) { if (!h) return CNB_ERR_ARG; static_cast<MnistDataReader*>(h)->shuffle(seed); return 0; }
+int cnh_mnist_has_next(void* h, int batch) { return h && static_cast<MnistDataReader*>(h)->hasNextBatch(batch) ? 1 : 0; }
+int cnh_mnist_next_batch(void* h, int batch, float* re, float* im, int* labels) {
+	return h && static_cast<MnistDataReader*>(h)->nextBatchInto(batch, re, im, labels) ? 0 : CNB_ERR_ARG;
+}
 
 }  // extern "C"

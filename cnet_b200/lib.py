@@ -130,6 +130,12 @@ SIGNATURES = {
     "cnb_dp_allreduce": (C.c_int, [_vp, _vp, _P, _sz, _vp]),
     "cnh_dp_use_nccl_arena": (C.c_int, [_vp, C.c_int]),
     "cnh_dp_symmetric": (C.c_int, [_vp]),
+    "cnh_mnist_open": (_vp, [C.c_char_p, C.c_char_p, C.c_int]),
+    "cnh_mnist_close": (None, [_vp]),
+    "cnh_mnist_size": (C.c_int, [_vp]),
+    "cnh_mnist_shuffle": (C.c_int, [_vp, C.c_uint]),
+    "cnh_mnist_has_next": (C.c_int, [_vp, C.c_int]),
+    "cnh_mnist_next_batch": (C.c_int, [_vp, C.c_int, _P, _P, _P]),
     "cnh_capture_begin": (C.c_int, [_vp]),
     "cnh_capture_end": (C.c_int, [_vp]),
     "cnh_graph_launch": (C.c_int, [_vp]),

@@ -102,6 +102,17 @@ int cnh_capture_end(cnh_net* net);
 int cnh_graph_launch(cnh_net* net);
 unsigned long long cnh_graph_kernel_count(cnh_net* net);
 
+/* MnistDataReader (data/data.h:82-165): `count` images / labels of the idx3 / idx1 files read into host memory the
+ * way the reference reads them (headers skipped unread, a pixel as a signed char, real = imaginary = that value);
+ * cnh_mnist_next_batch fills split planes [batch, 784] and labels [batch], wrapping around at the end like
+ * BatchedDataReader::nextBatch (data/data.h:58-68).  NULL / negative on failure. */
+void* cnh_mnist_open(const char* image_file, const char* label_file, int count);
+void cnh_mnist_close(void* reader);
+int cnh_mnist_size(void* reader);
+int cnh_mnist_shuffle(void* reader, unsigned seed);
+int cnh_mnist_has_next(void* reader, int batch);
+int cnh_mnist_next_batch(void* reader, int batch, float* re, float* im, int* labels);
+
 #ifdef __cplusplus
 }
 #endif
