@@ -273,6 +273,53 @@ def _time_launches(torch, fn, reps=20, clocks_for=None):
     return tot / reps
 
 
+L2_BYTES = 126 << 20
+
+
+def _nsets(nbytes, lo=3, hi=48):
+    """How many disjoint operand sets a kernel that touches nbytes per launch must rotate over so that a set
+    has left L2 (3 x L2 of other traffic) before it is used again."""
+    return int(min(hi, max(lo, -(-3 * L2_BYTES // max(1, int(nbytes))))))
+
+
+def _time_stream(torch, fns, launches=60, clocks_for=None):
+    """Average device time per launch, in ms, of the launches fns[0], fns[1], ... issued back to back on the
+    stream, round robin, between two CUDA events: each fns[k] works on operands of its own (together larger
+    than L2, so nothing is served from cache), as consecutive kernels of a step do.  A spin kernel queued first
+    keeps the GPU busy until the host has enqueued all of it, so host launch time is not in the figure."""
+    for _ in range(max(1, -(-3 // len(fns)))):
+        for f in fns:
+            f()
+    rounds = max(1, launches // len(fns))
+    torch.cuda.synchronize()
+    sampler = _Clocks(clocks_for, interval_ms=20) if clocks_for is not None else None
+    if hasattr(torch.cuda, "_sleep"):
+        torch.cuda._sleep(int(4e4 * rounds * len(fns)))       # ~20 us of head start per launch to come
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(rounds):
+        for f in fns:
+            f()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (rounds * len(fns))
+    if sampler is not None:
+        return ms, sampler.stop().get("sm_mhz")
+    return ms
+
+
+def _hbm_entry(torch, peaks, name, fns, nbytes):
+    """One HBM-bound kernel: in-stream average over rotating operand sets (the figure the fraction uses) and a
+    single launch between two events after an L2 flush (which adds the launch ramp and the events' own cost:
+    a kernel that does nothing measures ~5-8 us that way)."""
+    d = _time_stream(torch, fns)
+    single = _time_launches(torch, fns[0], reps=10)
+    gbs = nbytes / (d * 1e-3) / 1e9
+    return {"kernel": name, "GB/s": round(gbs, 1), "frac": round(gbs / peaks["hbm"], 3), "ms": round(d, 4),
+            "ms_single": round(single, 4), "frac_single": round(nbytes / (single * 1e-3) / 1e9 / peaks["hbm"], 3),
+            "operand_sets": len(fns)}
+
+
 def _tensor_roof(torch, peaks, dur, mhz, B, n_out, n_in, gpu_index):
     flops = 8.0 * B * n_in * n_out
     achieved = flops / (dur * 1e-3) / 1e12
@@ -309,11 +356,19 @@ def _roofline(workload, kw, B, gbatch, step_ms, device, hbm_kernels=True):
     w = tuple(torch.randn(n_out, n_in, device="cuda") * n_in ** -0.5 for _ in range(2))
     hbm = []
     if ctx.lib.cnb_linear_split_ok(B, n_in, n_out):
-        xs, ws = ctx.split(x), ctx.split(w)
-        y = ctx._new(B, n_out)
-        dur, mhz = _time_launches(torch, lambda: ctx.linear_fwd_split(xs, ws, B, n_in, n_out, out=y), reps=200,
-                                  clocks_for=device)
+        # operands pre-split; every launch of the timed run has activations and output of its own (the weights
+        # are shared, as a layer's are), so no launch finds its operands in L2
+        SG = _nsets(24.0 * B * n_in + 8.0 * B * n_out, hi=12)
+        ws = ctx.split(w)
+        xs = [ctx.split(tuple(torch.randn(B, n_in, device="cuda") for _ in range(2))) for _ in range(SG)]
+        ys = [ctx._new(B, n_out) for _ in range(SG)]
+        fns = [lambda k=k: ctx.linear_fwd_split(xs[k], ws, B, n_in, n_out, out=ys[k]) for k in range(SG)]
+        dur, mhz = _time_stream(torch, fns, launches=200, clocks_for=device)
         roof = _tensor_roof(torch, peaks, dur, mhz, B, n_out, n_in, device)
+        roof["ms_single"] = _time_launches(torch, fns[0], reps=20)
+        roof["timing"] = ("ms_per_launch: average of 200 launches back to back on the stream over %d operand sets (larger than L2 "
+                          "together); ms_single: one launch between two events after an L2 flush" % SG)
+        del xs, ys
     else:
         dur = _time_launches(torch, lambda: ctx.linear_fwd(x, w))
         nbytes = 8.0 * B * n_in + 8.0 * n_in * n_out + 8.0 * B * n_out
@@ -323,62 +378,113 @@ def _roofline(workload, kw, B, gbatch, step_ms, device, hbm_kernels=True):
                 "shape": [B, n_out, n_in], "ms_per_launch": dur, "peak_note": "copy bandwidth, of " + peaks["source"]}
     roof["step_gemm_tflops"] = _gemm_flops(kw, gbatch, workload) / (step_ms * 1e-3) / 1e12
     # HBM-bound kernels at the same activation shape: algorithmic bytes / time, against the measured copy bandwidth
+    import ctypes as C
+    L, H_, st = ctx.lib, ctx.h, ctx._stream()
+
+    def P(t):
+        return C.c_void_p(t.data_ptr())
+
+    def pair(*shape, fill=None):
+        t = ctx._new(*shape)
+        if fill == "randn":
+            for q in t:
+                q.normal_()
+        elif fill == "zero":
+            for q in t:
+                q.zero_()
+        return t
+
     if hbm_kernels and workload.startswith("embed"):
         T, D, V, H = kw["tokens"], kw["dim"], kw["vocab"], kw["hidden"]
         table = tuple(torch.randn(V, D, device="cuda") * 0.02 for _ in range(2))
-        dtable = tuple(torch.zeros(V, D, device="cuda") for _ in range(2))
-        tok = torch.randint(0, V, (B, T), device="cuda", dtype=torch.int32)
+        dtable = pair(V, D, fill="zero")
+        S = _nsets(16.0 * B * V)
+        tok = [torch.randint(0, V, (B, T), device="cuda", dtype=torch.int32) for _ in range(S)]
         labels = torch.randint(0, V, (B,), device="cuda", dtype=torch.int32)
-        ge = tuple(torch.randn(B, T * D, device="cuda") for _ in range(2))
-        z = tuple(torch.randn(B, V, device="cuda") for _ in range(2))
-        yv, inv = ctx.softmax_fwd(z)
-        a = tuple(torch.randn(B, H, device="cuda") for _ in range(2))
-        cases = [("embed_fwd_k (gather)", lambda: ctx.embed_fwd(table, tok), 16.0 * B * T * D),
-                 ("embed_bwd (scatter-add of dz* rows into the table)", lambda: ctx.embed_bwd(ge, tok, dtable), 16.0 * B * T * D),
-                 ("softmax_fwd_k (L2 normalise)", lambda: ctx.softmax_fwd(z), 16.0 * B * V),
-                 ("softmax_bwd_k", lambda: ctx.softmax_bwd(z, z, inv), 24.0 * B * V),
-                 ("crossent_k (loss + dz* seed)", lambda: ctx.crossent(yv, labels), 16.0 * B * V),
-                 ("gelu_fwd_k", lambda: ctx.gelu_fwd(a), 16.0 * B * H),
-                 ("gelu_bwd_k", lambda: ctx.gelu_bwd(a, a), 24.0 * B * H)]
-        for name, fn, nbytes in cases:
-            d = _time_launches(torch, fn, reps=10)
-            gbs = nbytes / (d * 1e-3) / 1e9
-            hbm.append({"kernel": name, "GB/s": round(gbs, 1), "frac": round(gbs / peaks["hbm"], 3), "ms": round(d, 4)})
+        ge = [pair(B, T * D, fill="randn") for _ in range(S)]          # embedding rows / their gradients
+        z = [pair(B, V, fill="randn") for _ in range(S)]
+        yv = [pair(B, V, fill="randn") for _ in range(S)]
+        inv = torch.ones(B, device="cuda")
+        loss = torch.empty(B, device="cuda")
+        SA = _nsets(16.0 * B * H)
+        a = [pair(B, H, fill="randn") for _ in range(SA)]
+        ya = [pair(B, H, fill="randn") for _ in range(SA)]
+        da = [pair(B, H) for _ in range(SA)]
+        gz = [pair(B, V, fill="randn") for _ in range(S)]
+        cases = [("embed_fwd_k (gather)",
+                  [lambda k=k: L.cnb_embed_fwd(H_, P(table[0]), P(table[1]), P(tok[k]), P(ge[k][0]), P(ge[k][1]), B, T, D, V, st) for k in range(S)],
+                  16.0 * B * T * D),
+                 ("embed_bwd (scatter-add of dz* rows into the table)",
+                  [lambda k=k: L.cnb_embed_bwd(H_, P(ge[k][0]), P(ge[k][1]), P(tok[k]), P(dtable[0]), P(dtable[1]), B, T, D, V, st) for k in range(S)],
+                  16.0 * B * T * D),
+                 ("softmax_fwd_k (L2 normalise)",
+                  [lambda k=k: L.cnb_softmax_fwd(H_, P(z[k][0]), P(z[k][1]), P(yv[k][0]), P(yv[k][1]), P(inv), B, V, st) for k in range(S)],
+                  16.0 * B * V),
+                 ("softmax_bwd_k",
+                  [lambda k=k: L.cnb_softmax_bwd(H_, P(gz[k][0]), P(gz[k][1]), P(z[k][0]), P(z[k][1]), P(inv), P(yv[k][0]), P(yv[k][1]), B, V, 0, st) for k in range(S)],
+                  24.0 * B * V),
+                 ("crossent_k (loss + dz* seed)",
+                  [lambda k=k: L.cnb_crossent_fwd_bwd(H_, P(z[k][0]), P(z[k][1]), P(labels), P(loss), P(yv[k][0]), P(yv[k][1]), B, V, st) for k in range(S)],
+                  16.0 * B * V),
+                 ("gelu_fwd_k",
+                  [lambda k=k: L.cnb_gelu_fwd(H_, P(a[k][0]), P(a[k][1]), P(ya[k][0]), P(ya[k][1]), C.c_size_t(B * H), st) for k in range(SA)],
+                  16.0 * B * H),
+                 ("gelu_bwd_k",
+                  [lambda k=k: L.cnb_gelu_bwd(H_, P(ya[k][0]), P(ya[k][1]), P(a[k][0]), P(a[k][1]), P(da[k][0]), P(da[k][1]), C.c_size_t(B * H), 0, st) for k in range(SA)],
+                  24.0 * B * H)]
+        for name, fns, nbytes in cases:
+            hbm.append(_hbm_entry(torch, peaks, name, fns, nbytes))
         # the second product of the net at its shape (K = hidden)
         x2 = tuple(torch.randn(B, H, device="cuda") for _ in range(2))
         w2 = tuple(torch.randn(V, H, device="cuda") * H ** -0.5 for _ in range(2))
         xs2, ws2 = ctx.split(x2), ctx.split(w2)
-        y2 = ctx._new(B, V)
-        d2 = _time_launches(torch, lambda: ctx.linear_fwd_split(xs2, ws2, B, H, V, out=y2), reps=10)
+        d2 = _time_stream(torch, [lambda k=k: ctx.linear_fwd_split(xs2, ws2, B, H, V, out=yv[k]) for k in range(S)], launches=20)
         roof["second_gemm"] = {"shape": [B, V, H], "ms_per_launch": d2,
                                "frac": 8.0 * B * H * V / (d2 * 1e-3) / 1e12 / roof["peak"]}
     elif hbm_kernels:
         N = n_in
-        u, g = x, tuple(torch.randn(B, N, device="cuda") for _ in range(2))
+        S = _nsets(16.0 * B * N)
+        u = [pair(B, N, fill="randn") for _ in range(S)]
+        g = [pair(B, N, fill="randn") for _ in range(S)]
+        a = [pair(B, N, fill="randn") for _ in range(S)]
+        o = [pair(B, N, fill="zero") for _ in range(S)]
         h = tuple(torch.randn(N, device="cuda") for _ in range(2))
-        a, yy = ctx.hadamard_gelu_fwd(u, h)
+        dh = pair(N)
         fft_name = "fft1024_pipe_k<-1> (FourierTrans forward)" if N == 1024 else "FourierTrans forward (N = %d)" % N
-        cases = [("hadamard_gelu_fwd_k", lambda: ctx.hadamard_gelu_fwd(u, h), 24.0 * B * N),
-                 ("colreduce_stage1_k<1> (gelu'+hadamard bwd + dh* partials)", lambda: ctx.hadamard_gelu_bwd(g, a, u, h), 32.0 * B * N),
-                 (fft_name, lambda: ctx.dft_fwd(u), 16.0 * B * N)]
-        if ctx.lib.cnb_dft_fused_ok(N):
+        cases = [("hadamard_gelu_fwd_k",
+                  [lambda k=k: L.cnb_hadamard_gelu_fwd(H_, P(u[k][0]), P(u[k][1]), P(h[0]), P(h[1]), P(a[k][0]), P(a[k][1]), P(o[k][0]), P(o[k][1]), B, N, st) for k in range(S)],
+                  24.0 * B * N),
+                 ("colreduce_stage1_k<1> (gelu'+hadamard bwd + dh* partials)",
+                  [lambda k=k: L.cnb_hadamard_gelu_bwd(H_, P(g[k][0]), P(g[k][1]), P(a[k][0]), P(a[k][1]), P(u[k][0]), P(u[k][1]), P(h[0]), P(h[1]), P(o[k][0]), P(o[k][1]), 0, P(dh[0]), P(dh[1]), 0, B, N, st) for k in range(S)],
+                  32.0 * B * N),
+                 ("colreduce_stage1_k<1>, a = u o h recomputed (as in the step)",
+                  [lambda k=k: L.cnb_hadamard_gelu_bwd(H_, P(g[k][0]), P(g[k][1]), None, None, P(u[k][0]), P(u[k][1]), P(h[0]), P(h[1]), P(o[k][0]), P(o[k][1]), 0, P(dh[0]), P(dh[1]), 0, B, N, st) for k in range(S)],
+                  24.0 * B * N),
+                 (fft_name,
+                  [lambda k=k: L.cnb_dft_fwd(H_, P(u[k][0]), P(u[k][1]), P(o[k][0]), P(o[k][1]), B, N, st) for k in range(S)],
+                  16.0 * B * N)]
+        if L.cnb_dft_fused_ok(N):
             # the forms that run inside the step: forward with the Hadamard + CGelu + hi/lo split tail (reads x; writes
             # u and four split planes), backward accumulating into the gradient (reads g, read-modify-writes dx)
-            us, sp = ctx.dft_hadamard_gelu_fwd(u, h)
-            acc = ctx._new(B, N)
+            sp = [torch.empty(L.cnb_split_floats(B * N), dtype=torch.float32, device="cuda") for _ in range(S)]
             cases.append(("fft1024_pipe_k<-1> + Hadamard + CGelu + split tail (as in the step)" if N == 1024 else "FourierTrans forward + tail",
-                          lambda: ctx.dft_hadamard_gelu_fwd(u, h, u=us, split=sp), 32.0 * B * N))
+                          [lambda k=k: L.cnb_dft_hadamard_gelu_fwd(H_, P(u[k][0]), P(u[k][1]), P(h[0]), P(h[1]), P(o[k][0]), P(o[k][1]), None, None, P(sp[k]), B, N, st) for k in range(S)],
+                          32.0 * B * N))
             cases.append(("fft1024_pipe_k<+1> backward, reduce-add into the gradient (as in the step)" if N == 1024 else "FourierTrans backward + accumulate",
-                          lambda: ctx.dft_bwd(g, out=acc), 24.0 * B * N))
+                          [lambda k=k: L.cnb_dft_bwd(H_, P(g[k][0]), P(g[k][1]), P(o[k][0]), P(o[k][1]), B, N, 1, st) for k in range(S)],
+                          24.0 * B * N))
         n_w = 2 * n_in * n_out * max(1, kw.get("blocks", 1))       # the whole weight arena of the net
-        wflat = torch.randn(n_w, device="cuda")
-        gflat = torch.randn(n_w, device="cuda")
-        cases.append(("sgd_k", lambda: ctx.sgd_update(wflat, gflat, 1e-3), 16.0 * wflat.numel()))
-        for name, fn, nbytes in cases:
-            d = _time_launches(torch, fn, reps=10)
-            gbs = nbytes / (d * 1e-3) / 1e9
-            hbm.append({"kernel": name, "GB/s": round(gbs, 1), "frac": round(gbs / peaks["hbm"], 3), "ms": round(d, 4)})
+        SW = _nsets(16.0 * n_w, lo=2)
+        wflat = [torch.randn(n_w, device="cuda") for _ in range(SW)]
+        gflat = [torch.randn(n_w, device="cuda") for _ in range(SW)]
+        cases.append(("sgd_k",
+                      [lambda k=k: L.cnb_sgd_update(H_, P(wflat[k]), P(gflat[k]), C.c_size_t(n_w), C.c_float(1e-3), 1, st) for k in range(SW)],
+                      16.0 * n_w))
+        for name, fns, nbytes in cases:
+            hbm.append(_hbm_entry(torch, peaks, name, fns, nbytes))
     roof["hbm_kernels"] = hbm
+    roof["hbm_timing"] = ("ms / frac: average of 60 launches back to back on the stream, each on operands of its own (operand_sets "
+                          "of them, together > 3 x L2); ms_single / frac_single: one launch between two events after an L2 flush")
     ctx.close()
     return roof
 

@@ -174,8 +174,36 @@ colreduce_stage1_k(const float* __restrict__ gr, const float* __restrict__ gi,
     if (!s_last) return;
     __threadfence();
     const int chunks = gridDim.y;
-    {
-        const int cx = t % (32 * W), lane8 = t / (32 * W);        // W = 4: 128 columns x 2 lanes; W = 1: 32 x 8
+    if constexpr (W == 4) {
+        // 32 threads x 16 bytes cover the 128 columns, 8 lanes share the chunks: a lane's loop is chunks / 8 long
+        // and its loads are independent, so the tail is a few L2 round trips instead of one per pair of chunks
+        const int cx = (t & 31) * 4, lane8 = t >> 5;
+        const int c = blockIdx.x * 128 + cx;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), d = a;
+        if (c < N) {
+#pragma unroll 4
+            for (int k = lane8; k < chunks; k += 8) {
+                const float4 x = __ldcg(reinterpret_cast<const float4*>(pr + (size_t) k * N + c));
+                const float4 y = __ldcg(reinterpret_cast<const float4*>(pi + (size_t) k * N + c));
+                a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                d.x += y.x; d.y += y.y; d.z += y.z; d.w += y.w;
+            }
+        }
+        sr[lane8][cx] = a.x; sr[lane8][cx + 1] = a.y; sr[lane8][cx + 2] = a.z; sr[lane8][cx + 3] = a.w;
+        si[lane8][cx] = d.x; si[lane8][cx + 1] = d.y; si[lane8][cx + 2] = d.z; si[lane8][cx + 3] = d.w;
+        __syncthreads();
+        if (t < 128) {
+            const int cc = blockIdx.x * 128 + t;
+            if (cc < N) {
+                float e = 0.f, f = 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { e += sr[k][t]; f += si[k][t]; }
+                if (accumulate_v) { e += dvr[cc]; f += dvi[cc]; }
+                dvr[cc] = e; dvi[cc] = f;
+            }
+        }
+    } else {
+        const int cx = t % (32 * W), lane8 = t / (32 * W);        // 32 columns x 8 lanes
         constexpr int LANES = 256 / (32 * W);
         const int c = blockIdx.x * 32 * W + cx;
         float a = 0.f, d = 0.f;

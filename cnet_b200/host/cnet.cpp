@@ -1139,7 +1139,7 @@ bool CNet::setDataParallel(const char id[kNcclUniqueIdBytes], int rank, int nran
 		// On a registered symmetric window NCCL reduces in the switch with a handful of CTAs (5 at 4 ranks); its
 		// copy-based kernels on unregistered buffers want more.  Measured at 4 GPUs, 1024 rows each: 6 reserved
 		// SMs 1.36 ms per step, 12: 1.45, none: 1.54.
-		int reserve = nccl_.hasWindow() ? 6 : 12;
+		int reserve = nccl_.hasWindow() ? (nranks >= 8 ? 8 : 6) : 12;     // 8 ranks: not measured here, one SM per peer
 		if (const char* e = getenv("CNB_DP_RESERVED_SMS")) reserve = atoi(e);
 		int sms = 0;
 		cnb_device_info(device_, &sms, nullptr, nullptr, nullptr);
