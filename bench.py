@@ -321,19 +321,27 @@ def _hbm_entry(torch, peaks, name, fns, nbytes):
 
 
 def _tensor_roof(torch, peaks, dur, mhz, B, n_out, n_in, gpu_index):
+    """Roofline of the split complex GEMM.  Every real product of the 8*M*N*K algorithmic flops passes the tensor
+    cores three times: hi.hi on the TF32 pipe and the two cross terms on the BF16 pipe, so the time per
+    algorithmic flop at peak is 1/TF32 + 2/BF16 (TF32 measured in this run, BF16 from the peaks file).
+    frac_3xtf32 = the same launch against the all-TF32 form's roofline (TF32 / 3), for comparison."""
     flops = 8.0 * B * n_in * n_out
     achieved = flops / (dur * 1e-3) / 1e12
     tf = _tf32_peak(torch, gpu_index)
-    peak = tf["tf32_tflops"] / 3.0          # 3xTF32: three TF32 MMAs per real product
-    derived = peaks["bf16"] / 6.0           # what the peaks file alone gives: TF32 = bf16 / 2
+    peak = 1.0 / (1.0 / tf["tf32_tflops"] + 2.0 / peaks["bf16"])
+    sustained = 1.0 / (1.0 / tf["tf32_tflops_sustained"] + 2.0 / (peaks["bf16_sustained"] or peaks["bf16"]))
+    derived = 1.0 / (2.0 / peaks["bf16"] + 2.0 / peaks["bf16"])      # what the peaks file alone gives: TF32 = bf16 / 2
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "frac_derived": achieved / derived, "peak_derived": derived,
-            "frac_sustained": achieved / (tf["tf32_tflops_sustained"] / 3.0),
-            "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)), "kernel": "cgemm_tc_k (tcgen05 3xTF32)",
+            "frac_sustained": achieved / sustained,
+            "frac_3xtf32": achieved / (tf["tf32_tflops"] / 3.0), "peak_3xtf32": tf["tf32_tflops"] / 3.0,
+            "traffic": NCU_TRAFFIC_BYTES.get((B, n_out, n_in)),
+            "kernel": "cgemm_tc_k (tcgen05: TF32 hi.hi + BF16 cross terms)",
             "shape": [B, n_out, n_in], "ms_per_launch": dur, "sm_mhz_during": mhz,
             "ms_x_mhz": (dur * mhz) if mhz else None, "tf32_peak": tf,
-            "peak_note": "dense TF32 measured in this run (cuBLAS 8192^3 burst %.1f TFLOP/s, sustained %.1f at %s MHz) / 3; "
-                         "frac_derived = against bf16 burst %.1f / 6 of %s"
+            "peak_note": "1 / (1/TF32 + 2/BF16): dense TF32 measured in this run (cuBLAS 8192^3 burst %.1f TFLOP/s, sustained "
+                         "%.1f at %s MHz), BF16 burst %.1f of %s; frac_derived = with TF32 taken as BF16 / 2; "
+                         "frac_3xtf32 = against TF32 / 3"
                          % (tf["tf32_tflops"], tf["tf32_tflops_sustained"], tf["sm_mhz_sustained"], peaks["bf16"],
                             peaks["source"])}
 
@@ -440,7 +448,8 @@ def _roofline(workload, kw, B, gbatch, step_ms, device, hbm_kernels=True):
         xs2, ws2 = ctx.split(x2), ctx.split(w2)
         d2 = _time_stream(torch, [lambda k=k: ctx.linear_fwd_split(xs2, ws2, B, H, V, out=yv[k]) for k in range(S)], launches=20)
         roof["second_gemm"] = {"shape": [B, V, H], "ms_per_launch": d2,
-                               "frac": 8.0 * B * H * V / (d2 * 1e-3) / 1e12 / roof["peak"]}
+                               "frac": 8.0 * B * H * V / (d2 * 1e-3) / 1e12 / roof["peak"],
+                               "frac_3xtf32": 8.0 * B * H * V / (d2 * 1e-3) / 1e12 / roof["peak_3xtf32"]}
     elif hbm_kernels:
         N = n_in
         S = _nsets(16.0 * B * N)

@@ -1,22 +1,29 @@
-// tcgen05 complex GEMM with a 3xTF32 error-compensated split, for sm_100a.
+// tcgen05 complex GEMM with an error-compensated operand split, for sm_100a.
 //
 //   D[m,n] (+)= sum_k A[m,k] * (conjB ? conj(B[n,k]) : B[n,k]) (+ R[m,n])
-//   A [M,K], B [N,K] complex, both K-major (row-major) fp32 re/im planes.
+//   A [M,K], B [N,K] complex, K-major (row-major) or MN-major ([K, rows]) split planes.
 //
 // Numerics.  Every fp32 operand x is split once, before the GEMM, into hi = x with the 13 low
 // mantissa bits cleared (exactly a TF32 value) and lo = x - hi (exact in fp32).  Each real
-// product is then three TF32 tensor-core MMAs with fp32 accumulation in tensor memory:
-// hi*hi + hi*lo + lo*hi (the dropped lo*lo term is ~2^-22 relative).
+// product is three tensor-core MMAs with fp32 accumulation in tensor memory:
+//     hi*hi                on the TF32 pipe (exact products), and
+//     hi*lo + lo*hi        on the BF16 pipe, from hi and lo rounded to bf16 (h16, l16).
+// The cross terms are 2^-10 of the product, so their bf16 rounding (2^-9 each factor) costs 2^-18 of the
+// product at worst, next to the 2^-20 of the dropped lo*lo term; fp32's exponent range is kept (no scaling).
+// A BF16 MMA of depth 16 takes the time of a TF32 MMA of depth 8, so a real product costs two TF32-equivalents
+// instead of the three of the all-TF32 form, for the same operand bytes (8 per real element).
 //
 // Tiling.  One CTA computes a 128 x 128 complex tile.  The B tile is staged as ONE 256-row
-// operand [B_re rows ; B_im rows], so every MMA is 128 x 256 x 8 and the complex structure
+// operand [B_re rows ; B_im rows], so every MMA is 128 x 256 and the complex structure
 // costs two accumulators instead of four MMA shapes:
 //     acc1 = A_re * [B_re ; B_im]^T      (TMEM columns   0..255)
 //     acc2 = A_im * [B_re ; B_im]^T      (TMEM columns 256..511)
 //     D_re = acc1[:, :128] -/+ acc2[:, 128:],   D_im = acc1[:, 128:] +/- acc2[:, :128]   (epilogue)
-// Per 16-deep k-block a stage holds 8 operand planes of 8 KB (A hi/lo re/im, B hi/lo re/im) =
-// 64 KB, 64-byte swizzled; 3 stages.  Each CTA issues its own plain TMA tile loads; their zero fill
-// handles every M/N/K edge.
+// Per 16-deep k-block a stage holds 8 operand slots of 8 KB = 64 KB; 3 stages:
+//     A hi_re, A hi_im (fp32, 64-byte swizzle),  A h16 [re ; im], A l16 [re ; im] (bf16, 32-byte swizzle),
+//     B hi_re, B hi_im,                          B h16 [re ; im], B l16 [re ; im];
+// per k-block and accumulator: 2 TF32 MMAs (k-steps of 8) + 2 BF16 MMAs (one k-step of 16).
+// Each CTA issues its own plain TMA tile loads; their zero fill handles every M/N/K edge.
 //
 // Scheduling.  Stream-K: the (tile, k-block) work units are cut into equal consecutive runs, one
 // per CTA and one CTA per SM, so every SM finishes together whatever the tile count; a tile whose
@@ -118,6 +125,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // MN-major operand tile (source stored [K, rows]): slabs of 32 rows-of-the-operand, each slab
 // 16 k-lines of 128 B.  The only layout the tensor core accepts for MN-major TF32 is the 128-byte
 // swizzle with 32-byte atomicity: atoms of 4 k-lines (512 B).  Leading byte offset = distance
@@ -141,6 +154,42 @@ __device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
     d |= (uint64_t) 1 << 46;                          // descriptor version of sm_100
     d |= (uint64_t) 4 << 61;                          // layout type: 64-byte swizzle
     return d;
+}
+
+// bf16 K-major operand tile, 32-byte swizzle: rows of 32 B (16 bf16 = one MMA's depth), 8-row groups 256 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((addr >> 4) & 0x3FFF);
+    d |= (uint64_t) 1 << 16;
+    d |= (uint64_t) (256 >> 4) << 32;
+    d |= (uint64_t) 1 << 46;
+    d |= (uint64_t) 6 << 61;                          // layout type: 32-byte swizzle
+    return d;
+}
+
+// bf16 MN-major operand tile (source stored [K, rows]): slabs of 64 rows-of-the-operand (128 B), each slab 16
+// k-lines; plain 128-byte swizzle, atoms of 8 k-lines (1 KB).  Leading byte offset = slab to slab (2 KB),
+// stride byte offset = k atom to k atom (1 KB).
+__device__ __forceinline__ uint64_t smem_desc_mn128_b16(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t) ((addr >> 4) & 0x3FFF);
+    d |= (uint64_t) (2048 >> 4) << 16;
+    d |= (uint64_t) (1024 >> 4) << 32;
+    d |= (uint64_t) 1 << 46;
+    d |= (uint64_t) 2 << 61;                          // layout type: 128-byte swizzle
+    return d;
+}
+
+// kind::f16 with bf16 operands, fp32 accumulate, M = 128, N = 256
+constexpr uint32_t kInstrDesc16 = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // kind::tf32, fp32 accumulate, A and B K-major, M = 128, N = 256
@@ -301,9 +350,9 @@ __device__ __forceinline__ void cluster_reduce(const TcParams& p, uint32_t smem_
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
-           const __grid_constant__ CUtensorMap a_lo_re, const __grid_constant__ CUtensorMap a_lo_im,
+           const __grid_constant__ CUtensorMap a_h16, const __grid_constant__ CUtensorMap a_l16,
            const __grid_constant__ CUtensorMap b_hi_re, const __grid_constant__ CUtensorMap b_hi_im,
-           const __grid_constant__ CUtensorMap b_lo_re, const __grid_constant__ CUtensorMap b_lo_im,
+           const __grid_constant__ CUtensorMap b_h16, const __grid_constant__ CUtensorMap b_l16,
            const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     CNB_GSTAMP(0, threadIdx.x == 0);
@@ -369,7 +418,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (warp == 0 && lane < 8) {   // descriptor fetch of the 8 operand maps, off the first TMA's critical path
-        const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_lo_re, &a_lo_im, &b_hi_re, &b_hi_im, &b_lo_re, &b_lo_im};
+        const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_h16, &a_l16, &b_hi_re, &b_hi_im, &b_h16, &b_l16};
         asm volatile("prefetch.tensormap [%0];" ::"l"(maps[lane]) : "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -386,7 +435,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_lo_re, &a_lo_im, &b_hi_re, &b_hi_im, &b_lo_re, &b_lo_im};
+            const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_h16, &a_l16, &b_hi_re, &b_hi_im, &b_h16, &b_l16};
             long it = 0;
             bool live = true;
             for (int pass = 0; pass < 2 && live; ++pass)
@@ -401,8 +450,14 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int r0 = q < 4 ? m0 : n0;
-                    if (q < 4 ? p.a_mn : p.b_mn) tma_load_3d(dst + q * PLANE_BYTES, maps[q], full_bar(s), 0, kb * BK, r0 / 32);
-                    else tma_load_2d(dst + q * PLANE_BYTES, maps[q], full_bar(s), kb * BK, r0);
+                    const bool mn = q < 4 ? p.a_mn : p.b_mn;
+                    if ((q & 3) < 2) {                   // an fp32 hi plane
+                        if (mn) tma_load_3d(dst + q * PLANE_BYTES, maps[q], full_bar(s), 0, kb * BK, r0 / 32);
+                        else tma_load_2d(dst + q * PLANE_BYTES, maps[q], full_bar(s), kb * BK, r0);
+                    } else {                             // a pair of bf16 planes [re ; im]
+                        if (mn) tma_load_4d(dst + q * PLANE_BYTES, maps[q], full_bar(s), 0, kb * BK, r0 / 64, 0);
+                        else tma_load_3d(dst + q * PLANE_BYTES, maps[q], full_bar(s), kb * BK, r0, 0);
+                    }
                 }
             }
         }
@@ -413,7 +468,8 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             long it = 0;
             int seg = 0;
             // bits 15 / 16 of the instruction descriptor: operand A / B is MN-major
-            const uint32_t idesc = kInstrDesc | (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
+            const uint32_t mn_bits = (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
+            const uint32_t idesc = kInstrDesc | mn_bits, idesc16 = kInstrDesc16 | mn_bits;
             for (int pass = 0; pass < 2; ++pass)
             for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue && ok; ++seg) {
                 int kb0 = (int) (u % k_blocks);
@@ -430,6 +486,24 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     CNB_GSTAMP(2, it == 0);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t st = smem_base + s * STAGE_BYTES;
+                    const uint32_t first = kb == kb0 ? 0u : 1u;
+                    {
+                        // the cross terms first (small terms first): one BF16 k-step covers the whole 16-deep block.
+                        // A slots 2 / 3 hold [re ; im] of h16 / l16 (4 KB each), B slots 6 / 7 the 256-row operands.
+                        auto a16 = [&](int slot, int im) {
+                            const uint32_t a = st + slot * PLANE_BYTES + im * (PLANE_BYTES / 2);
+                            return p.a_mn ? smem_desc_mn128_b16(a) : smem_desc_sw32(a);
+                        };
+                        auto b16 = [&](int slot) {
+                            const uint32_t a = st + slot * PLANE_BYTES;
+                            return p.b_mn ? smem_desc_mn128_b16(a) : smem_desc_sw32(a);
+                        };
+                        const uint64_t b_h16 = b16(6), b_l16 = b16(7);
+                        umma_bf16(tmem_base, a16(3, 0), b_h16, idesc16, first);          // lo(A_re) . hi(B)
+                        umma_bf16(tmem_base, a16(2, 0), b_l16, idesc16, 1u);             // hi(A_re) . lo(B)
+                        umma_bf16(tmem_base + 256, a16(3, 1), b_h16, idesc16, first);    // lo(A_im) . hi(B)
+                        umma_bf16(tmem_base + 256, a16(2, 1), b_l16, idesc16, 1u);       // hi(A_im) . lo(B)
+                    }
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
                         // one k-step = 8 TF32: 32 bytes along a K-major swizzled row, or one 1 KB atom of k-lines
@@ -438,39 +512,10 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                             uint32_t a = st + plane * PLANE_BYTES + ka;
                             return p.a_mn ? smem_desc_mn128(a) : smem_desc_sw64(a);
                         };
-                        auto bdesc = [&](int plane) {
-                            uint32_t a = st + plane * PLANE_BYTES + kbo;
-                            return p.b_mn ? smem_desc_mn128(a) : smem_desc_sw64(a);
-                        };
-                        uint64_t a_hr = adesc(0), a_hi_ = adesc(1), a_lr = adesc(2), a_li = adesc(3);
-                        uint64_t b_h = bdesc(4), b_l = bdesc(6);
-                        uint32_t first = (kb == kb0 && j == 0) ? 0u : 1u;
-#ifdef CNB_GEMM_3M_PROBE
-                        // Throughput probe of the 3M (Gauss) form, results meaningless: nine 128 x 128 x 8 MMAs per
-                        // k-step (three real products x three TF32 terms) into three accumulators, in place of six
-                        // 128 x 256 x 8.  The operand planes of the stage stand in for the six planes per operand
-                        // that form would stage.
-                        {
-                            const uint32_t id128 = (idesc & ~(0x3Fu << 17)) | ((128u >> 3) << 17);
-                            const uint64_t b_hi_im = bdesc(5), b_li = bdesc(7);
-                            umma_tf32(tmem_base, a_lr, b_h, id128, first);
-                            umma_tf32(tmem_base, a_hr, b_l, id128, 1u);
-                            umma_tf32(tmem_base, a_hr, b_h, id128, 1u);
-                            umma_tf32(tmem_base + 128, a_li, b_hi_im, id128, first);
-                            umma_tf32(tmem_base + 128, a_hi_, b_li, id128, 1u);
-                            umma_tf32(tmem_base + 128, a_hi_, b_hi_im, id128, 1u);
-                            umma_tf32(tmem_base + 256, a_lr, b_hi_im, id128, first);
-                            umma_tf32(tmem_base + 256, a_hi_, b_l, id128, 1u);
-                            umma_tf32(tmem_base + 256, a_hr, b_hi_im, id128, 1u);
-                            continue;
-                        }
-#endif
-                        umma_tf32(tmem_base, a_lr, b_h, idesc, first);      // small terms first
-                        umma_tf32(tmem_base, a_hr, b_l, idesc, 1u);
-                        umma_tf32(tmem_base, a_hr, b_h, idesc, 1u);
-                        umma_tf32(tmem_base + 256, a_li, b_h, idesc, first);
-                        umma_tf32(tmem_base + 256, a_hi_, b_l, idesc, 1u);
-                        umma_tf32(tmem_base + 256, a_hi_, b_h, idesc, 1u);
+                        const uint32_t bb = st + 4 * PLANE_BYTES + kbo;             // [B_re ; B_im] hi, 256 rows
+                        const uint64_t b_h = p.b_mn ? smem_desc_mn128(bb) : smem_desc_sw64(bb);
+                        umma_tf32(tmem_base, adesc(0), b_h, idesc, 1u);              // hi(A_re) . hi(B)
+                        umma_tf32(tmem_base + 256, adesc(1), b_h, idesc, 1u);        // hi(A_im) . hi(B)
                     }
                     umma_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                 }
@@ -679,40 +724,29 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     }
 }
 
-// hi = x with the low 13 mantissa bits cleared, lo = x - hi; optionally transposed ([R,C] -> [C,R]).
-__global__ void split_k(const float* __restrict__ s0, const float* __restrict__ s1, float* __restrict__ hi0,
-                        float* __restrict__ hi1, float* __restrict__ lo0, float* __restrict__ lo1, size_t n) {
+// The operand split (cnb_split_store*, common.cuh) of a pair of planes into a split buffer with plane pitch np.
+__global__ void split_k(const float* __restrict__ s0, const float* __restrict__ s1, float* __restrict__ sp, size_t np,
+                        size_t n) {
     cnb_pdl_enter();
+    const cnb_split_dst d0 = cnb_split_component(sp, np, 0), d1 = cnb_split_component(sp, np, 1);
     size_t stride = (size_t) gridDim.x * blockDim.x * 4;
     for (size_t i = ((size_t) blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
         if (i + 3 < n) {
-            float4 x = *reinterpret_cast<const float4*>(s0 + i), y = *reinterpret_cast<const float4*>(s1 + i);
-            float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w}, xh[4], yh[4], xl[4], yl[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                xh[k] = __uint_as_float(__float_as_uint(xs[k]) & 0xFFFFE000u); xl[k] = xs[k] - xh[k];
-                yh[k] = __uint_as_float(__float_as_uint(ys[k]) & 0xFFFFE000u); yl[k] = ys[k] - yh[k];
-            }
-            *reinterpret_cast<float4*>(hi0 + i) = make_float4(xh[0], xh[1], xh[2], xh[3]);
-            *reinterpret_cast<float4*>(hi1 + i) = make_float4(yh[0], yh[1], yh[2], yh[3]);
-            *reinterpret_cast<float4*>(lo0 + i) = make_float4(xl[0], xl[1], xl[2], xl[3]);
-            *reinterpret_cast<float4*>(lo1 + i) = make_float4(yl[0], yl[1], yl[2], yl[3]);
+            const float4 x = *reinterpret_cast<const float4*>(s0 + i), y = *reinterpret_cast<const float4*>(s1 + i);
+            cnb_split_store4(d0, i, x.x, x.y, x.z, x.w);
+            cnb_split_store4(d1, i, y.x, y.y, y.z, y.w);
         } else {
-            for (size_t j = i; j < n; ++j) {
-                float h = __uint_as_float(__float_as_uint(s0[j]) & 0xFFFFE000u);
-                hi0[j] = h; lo0[j] = s0[j] - h;
-                h = __uint_as_float(__float_as_uint(s1[j]) & 0xFFFFE000u);
-                hi1[j] = h; lo1[j] = s1[j] - h;
-            }
+            for (size_t j = i; j < n; ++j) { cnb_split_store1(d0, j, s0[j]); cnb_split_store1(d1, j, s1[j]); }
         }
     }
 }
 
+// the same, transposed while it is split ([R,C] -> [C,R])
 __global__ void split_transpose_k(const float* __restrict__ s0, const float* __restrict__ s1,
-                                  float* __restrict__ hi0, float* __restrict__ hi1, float* __restrict__ lo0,
-                                  float* __restrict__ lo1, int R, int C) {
+                                  float* __restrict__ sp, size_t np, int R, int C) {
     cnb_pdl_enter();
     __shared__ float t0[32][33], t1[32][33];
+    const cnb_split_dst d0 = cnb_split_component(sp, np, 0), d1 = cnb_split_component(sp, np, 1);
     int c = blockIdx.x * 32 + threadIdx.x;
     for (int k = threadIdx.y; k < 32; k += 8) {
         int r = blockIdx.y * 32 + k;
@@ -724,11 +758,8 @@ __global__ void split_transpose_k(const float* __restrict__ s0, const float* __r
         int cc = blockIdx.x * 32 + k;
         if (r < R && cc < C) {
             size_t o = (size_t) cc * R + r;
-            float x = t0[threadIdx.x][k], y = t1[threadIdx.x][k];
-            float xh = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-            float yh = __uint_as_float(__float_as_uint(y) & 0xFFFFE000u);
-            hi0[o] = xh; lo0[o] = x - xh;
-            hi1[o] = yh; lo1[o] = y - yh;
+            cnb_split_store1(d0, o, t0[threadIdx.x][k]);
+            cnb_split_store1(d1, o, t1[threadIdx.x][k]);
         }
     }
 }
@@ -783,6 +814,38 @@ int make_map_mn(CUtensorMap* m, const float* base, int rows, int K) {
     return CNB_OK;
 }
 
+// A pair of bf16 planes (real, imaginary; np elements apart), each [rows, K] row-major, seen as [2][rows][K]: one
+// box {BK, 128, 2} brings the 128 rows of both planes, real then imaginary; 32-byte swizzle.
+int make_map16(CUtensorMap* m, const void* base, int rows, int K, size_t np) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t) K, (cuuint64_t) rows, 2u};
+    cuuint64_t strides[2] = {(cuuint64_t) K * 2u, (cuuint64_t) np * 2u};
+    cuuint32_t box[3] = {(cuuint32_t) BK, 128u, 2u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a bf16 [%d,%d] plane pair", (int) r, rows, K);
+    return CNB_OK;
+}
+
+// The same pair stored [K, rows] (rows contiguous, rows % 64 == 0), seen as [2][rows/64][K][64]: one box
+// {64, BK, 2, 2} brings two 64-row slabs of 16 k-lines of both planes, slab after slab (128-byte swizzle).
+int make_map16_mn(CUtensorMap* m, const void* base, int rows, int K, size_t np) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[4] = {64u, (cuuint64_t) K, (cuuint64_t) (rows / 64), 2u};
+    cuuint64_t strides[3] = {(cuuint64_t) rows * 2u, 128u, (cuuint64_t) np * 2u};
+    cuuint32_t box[4] = {64u, (cuuint32_t) BK, 2u, 2u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for an MN-major bf16 [%d,%d] plane pair", (int) r, K, rows);
+    return CNB_OK;
+}
+
 // Clears the two output planes of a product whose tiles are summed with atomics.
 __global__ void zero_pair_k(float* __restrict__ a, float* __restrict__ b, size_t n) {
     cnb_pdl_enter();
@@ -806,21 +869,22 @@ __global__ void zero_pair_k(float* __restrict__ a, float* __restrict__ b, size_t
 namespace cnb {
 
 bool cgemm_tc_shape_ok(int M, int N, int K) {
-    // TMA needs 16-byte row pitch; small or skinny problems are faster on the SIMT tiles
-    return (K % 4 == 0) && K >= 32 && M >= 64 && N >= 64;
+    // TMA needs a 16-byte row pitch (8 bf16); small or skinny problems are faster on the SIMT tiles
+    return (K % 8 == 0) && K >= 32 && M >= 64 && N >= 64;
 }
 
 size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
     return 4 * ((size_t) M * K + (size_t) N * K) * sizeof(float) + 4096;
 }
 
-void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* const dst[4], size_t n, cudaStream_t st) {
+void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* sp, size_t np, size_t n, cudaStream_t st) {
     size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
-    cnb::launch(split_k, dim3((unsigned) (blocks < cap ? blocks : cap)), dim3(256), 0, st, 1, s0, s1, dst[0], dst[1], dst[2], dst[3], n);
+    cnb::launch(split_k, dim3((unsigned) (blocks < cap ? blocks : cap)), dim3(256), 0, st, 1, s0, s1, sp, np, n);
 }
 
-// The GEMM proper on operands that are already split: a[4] / b[4] = hi_re, hi_im, lo_re, lo_im planes,
-// stored [rows, K] (major = 0) or [K, rows] (major = 1, needs rows % 32 == 0).
+// The GEMM proper on operands that are already split: a[4] / b[4] = the four slots of a split buffer (hi_re,
+// hi_im, [h16_re ; h16_im], [l16_re ; l16_im]; slot q+1 follows slot q at the plane pitch), elements stored
+// [rows, K] (major = 0) or [K, rows] (major = 1, needs rows % 64 == 0).
 int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
                       const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
                       int accumulate, cudaStream_t st) {
@@ -831,17 +895,25 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     }
     if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
         return set_error(CNB_ERR_ARG, "cgemm_tc: misaligned output");
-    if ((a_mn && M % 32) || (b_mn && N % 32))
-        return set_error(CNB_ERR_ARG, "cgemm_tc: an MN-major operand needs a multiple of 32 rows");
-    if ((!a_mn && K % 4) || (!b_mn && K % 4))
-        return set_error(CNB_ERR_ARG, "cgemm_tc: a K-major operand needs K %% 4 == 0");
+    if ((a_mn && M % 64) || (b_mn && N % 64))
+        return set_error(CNB_ERR_ARG, "cgemm_tc: an MN-major operand needs a multiple of 64 rows");
+    if ((!a_mn && K % 8) || (!b_mn && K % 8))
+        return set_error(CNB_ERR_ARG, "cgemm_tc: a K-major operand needs K %% 8 == 0");
     int rc;
     alignas(64) CUtensorMap maps[8];
+    const size_t npa = (size_t) (a[3] - a[2]), npb = (size_t) (b[3] - b[2]);     // plane pitch, elements
     for (int q = 0; q < 4; ++q) {
-        rc = a_mn ? make_map_mn(&maps[q], a[q], M, K) : make_map(&maps[q], a[q], M, K);
-        if (rc != CNB_OK) return rc;
-        rc = b_mn ? make_map_mn(&maps[4 + q], b[q], N, K) : make_map(&maps[4 + q], b[q], N, K);
-        if (rc != CNB_OK) return rc;
+        if (q < 2) {
+            rc = a_mn ? make_map_mn(&maps[q], a[q], M, K) : make_map(&maps[q], a[q], M, K);
+            if (rc != CNB_OK) return rc;
+            rc = b_mn ? make_map_mn(&maps[4 + q], b[q], N, K) : make_map(&maps[4 + q], b[q], N, K);
+            if (rc != CNB_OK) return rc;
+        } else {
+            rc = a_mn ? make_map16_mn(&maps[q], a[q], M, K, npa) : make_map16(&maps[q], a[q], M, K, npa);
+            if (rc != CNB_OK) return rc;
+            rc = b_mn ? make_map16_mn(&maps[4 + q], b[q], N, K, npb) : make_map16(&maps[4 + q], b[q], N, K, npb);
+            if (rc != CNB_OK) return rc;
+        }
     }
     int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int k_blocks = (K + BK - 1) / BK;
@@ -926,7 +998,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
 }
 
 // fp32 operands: split them into scratch first.  a_trans / b_trans say the source is stored
-// [K, rows]; it is then consumed MN-major in place (rows % 32 == 0) or transposed while it is split.
+// [K, rows]; it is then consumed MN-major in place (rows % 64 == 0) or transposed while it is split.
 int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans, const float* b_re,
                  const float* b_im, int b_trans, int conjB, const float* r_re, const float* r_im, float* d_re,
                  float* d_im, int M, int N, int K, int accumulate, cudaStream_t st, const float* b_split) {
@@ -934,18 +1006,19 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
     int rc = ensure_scratch(ctx, cgemm_tc_workspace_bytes(M, N, K), &ws);
     if (rc != CNB_OK) return rc;
     size_t na = ((size_t) M * K + 63) & ~size_t(63), nb = ((size_t) N * K + 63) & ~size_t(63);
-    float* ap[4] = {ws, ws + na, ws + 2 * na, ws + 3 * na};          // hi_re, hi_im, lo_re, lo_im
+    float* ap[4] = {ws, ws + na, ws + 2 * na, ws + 3 * na};          // the four slots of a split buffer
     float* bp[4] = {ws + 4 * na, ws + 4 * na + nb, ws + 4 * na + 2 * nb, ws + 4 * na + 3 * nb};
     int a_mn = 0, b_mn = 0;
     auto split = [&](const float* s0, const float* s1, float** dst, int rows, int trans, int* mn) -> int {
         bool al = ((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) == 0;
-        if (trans && !(rows % 32 == 0 && al)) {   // source is [K, rows] with ragged rows: transpose while splitting
+        const size_t np = (size_t) (dst[1] - dst[0]);
+        if (trans && !(rows % 64 == 0 && al)) {   // source is [K, rows] with ragged rows: transpose while splitting
             dim3 grid((rows + 31) / 32, (K + 31) / 32), block(32, 8);
-            cnb::launch(split_transpose_k, grid, block, 0, st, 1, s0, s1, dst[0], dst[1], dst[2], dst[3], K, rows);
+            cnb::launch(split_transpose_k, grid, block, 0, st, 1, s0, s1, dst[0], np, K, rows);
         } else {
             if (!al) return set_error(CNB_ERR_ARG, "cgemm_tc: operand planes must be 16-byte aligned");
             *mn = trans;
-            split_launch(ctx, s0, s1, dst, (size_t) rows * K, st);
+            split_launch(ctx, s0, s1, dst[0], np, (size_t) rows * K, st);
         }
         CNB_LAUNCH_CHECK("split");
         return CNB_OK;
@@ -963,8 +1036,7 @@ int split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float
     if (((reinterpret_cast<uintptr_t>(re) | reinterpret_cast<uintptr_t>(im) | reinterpret_cast<uintptr_t>(split)) & 15) != 0)
         return set_error(CNB_ERR_ARG, "split: planes must be 16-byte aligned");
     size_t np = (n + 63) & ~size_t(63);
-    float* dst[4] = {split, split + np, split + 2 * np, split + 3 * np};
-    split_launch(ctx, re, im, dst, n, st);
+    split_launch(ctx, re, im, split, np, n, st);
     CNB_LAUNCH_CHECK("split");
     return CNB_OK;
 }

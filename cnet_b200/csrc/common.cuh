@@ -1,5 +1,6 @@
 // Shared declarations of the device library: context, error plumbing, launch helpers.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -12,7 +13,7 @@
 struct cnb_twiddle {
     float* re = nullptr;   // [N, N] planes, F[p,q] = N^-1/2 e^{-2 pi i pq/N}
     float* im = nullptr;
-    float* split = nullptr;   // hi/lo TF32 planes of the matrix (made once), or null when the tiles cannot take it
+    float* split = nullptr;   // split buffer of the matrix (made once), or null when the tiles cannot take it
 };
 
 struct cnb_ctx {
@@ -70,11 +71,12 @@ int cgemm_tc_run(cnb_ctx* ctx, const float* a_re, const float* a_im, int a_trans
                  float* d_im, int M, int N, int K, int accumulate, cudaStream_t st,
                  const float* b_split = nullptr);
 size_t cgemm_tc_workspace_bytes(int M, int N, int K);
-// Operands already split into [hi_re, hi_im, lo_re, lo_im] planes; major 0 = [rows, K], 1 = [K, rows].
+// Operands already split: a[q] / b[q] = slot q of the split buffer (see cnb_split_component below); major 0 =
+// [rows, K], 1 = [K, rows].
 int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
                       const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
                       int accumulate, cudaStream_t st);
-// split = 4 consecutive planes of pad64(n) floats: hi_re, hi_im, lo_re, lo_im
+// split = 4 consecutive slots of pad64(n) floats (see cnb_split_component below)
 int split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, cudaStream_t st);
 
 // Skinny Linear (out <= 16): HBM-bound fp32 kernels.
@@ -115,6 +117,50 @@ __device__ __forceinline__ float cnb_dgelu(float x) {
     float t = cnb_tanh(0.7978845608028654f * (x + 0.044715f * x * x2));
     float sech2 = 1.0f - t * t;
     return 0.5f * (1.0f + t) + 0.5f * x * sech2 * 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2);
+}
+
+// The operand split of the tensor-core product.  x = hi + lo with hi = x cut to TF32 (low 13 mantissa bits
+// cleared) and lo = x - hi, exact in fp32.  A product x.y is taken as hi.hi on the TF32 pipe plus the two cross
+// terms hi.lo + lo.hi on the BF16 pipe, for which hi and lo are also kept rounded to bf16 (h16, l16).  A split
+// buffer of n elements is four slots of np = pad64(n) floats:
+//   slot 0: hi of the real plane (fp32)      slot 2: h16 of the real plane, then of the imaginary plane (bf16)
+//   slot 1: hi of the imaginary plane        slot 3: l16 of the real plane, then of the imaginary plane
+__device__ __forceinline__ float cnb_tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
+__device__ __forceinline__ unsigned short cnb_bf16_bits(float x) { return __bfloat16_as_ushort(__float2bfloat16_rn(x)); }
+
+struct cnb_split_dst {
+    float* hi;               // fp32 hi plane of this component (real or imaginary)
+    unsigned short* h16;     // its bf16 planes
+    unsigned short* l16;
+};
+
+// component c (0 = real, 1 = imaginary) of a split buffer with plane pitch np
+__host__ __device__ __forceinline__ cnb_split_dst cnb_split_component(float* sp, size_t np, int c) {
+    cnb_split_dst d;
+    d.hi = sp + (size_t) c * np;
+    d.h16 = reinterpret_cast<unsigned short*>(sp + 2 * np) + (size_t) c * np;
+    d.l16 = reinterpret_cast<unsigned short*>(sp + 3 * np) + (size_t) c * np;
+    return d;
+}
+
+__device__ __forceinline__ void cnb_split_store1(const cnb_split_dst& d, size_t i, float x) {
+    const float h = cnb_tf32_hi(x);
+    d.hi[i] = h;
+    d.h16[i] = cnb_bf16_bits(h);
+    d.l16[i] = cnb_bf16_bits(x - h);
+}
+
+// four consecutive elements, i % 4 == 0 (16-byte store of hi, 8-byte stores of the bf16 planes)
+__device__ __forceinline__ void cnb_split_store4(const cnb_split_dst& d, size_t i, float x0, float x1, float x2, float x3) {
+    const float h0 = cnb_tf32_hi(x0), h1 = cnb_tf32_hi(x1), h2 = cnb_tf32_hi(x2), h3 = cnb_tf32_hi(x3);
+    *reinterpret_cast<float4*>(d.hi + i) = make_float4(h0, h1, h2, h3);
+    uint2 a, b;
+    a.x = (uint32_t) cnb_bf16_bits(h0) | ((uint32_t) cnb_bf16_bits(h1) << 16);
+    a.y = (uint32_t) cnb_bf16_bits(h2) | ((uint32_t) cnb_bf16_bits(h3) << 16);
+    b.x = (uint32_t) cnb_bf16_bits(x0 - h0) | ((uint32_t) cnb_bf16_bits(x1 - h1) << 16);
+    b.y = (uint32_t) cnb_bf16_bits(x2 - h2) | ((uint32_t) cnb_bf16_bits(x3 - h3) << 16);
+    *reinterpret_cast<uint2*>(d.h16 + i) = a;
+    *reinterpret_cast<uint2*>(d.l16 + i) = b;
 }
 
 // Programmatic dependent launch.  Every kernel of the step is launched with the "programmatic stream

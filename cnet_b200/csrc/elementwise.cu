@@ -283,7 +283,7 @@ __global__ void gelu_bwd_k(const float* __restrict__ gr, const float* __restrict
     }
 }
 
-// sp != NULL: also emit the hi/lo TF32 split planes of y (4 planes of `np` floats) that the
+// sp != NULL: also emit the operand split of y (a split buffer with plane pitch `np`) that the
 // tensor-core GEMM of the consuming Linear reads, saving that layer's separate split pass.
 template <int W>
 __global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* __restrict__ ui,
@@ -306,13 +306,14 @@ __global__ void hadamard_gelu_fwd_k(const float* __restrict__ ur, const float* _
         for (int k = 0; k < W; ++k) { r.v[k] = gelu_f(r.v[k]); s.v[k] = gelu_f(s.v[k]); }
         st<W>(yr, i, r); st<W>(yi, i, s);
         if (sp) {
-            Pack<W> rh, rl, sh, sl;
+            const cnb_split_dst d0 = cnb_split_component(sp, np, 0), d1 = cnb_split_component(sp, np, 1);
+            if constexpr (W == 4) {
+                cnb_split_store4(d0, i, r.v[0], r.v[1], r.v[2], r.v[3]);
+                cnb_split_store4(d1, i, s.v[0], s.v[1], s.v[2], s.v[3]);
+            } else {
 #pragma unroll
-            for (int k = 0; k < W; ++k) {
-                rh.v[k] = __uint_as_float(__float_as_uint(r.v[k]) & 0xFFFFE000u); rl.v[k] = r.v[k] - rh.v[k];
-                sh.v[k] = __uint_as_float(__float_as_uint(s.v[k]) & 0xFFFFE000u); sl.v[k] = s.v[k] - sh.v[k];
+                for (int k = 0; k < W; ++k) { cnb_split_store1(d0, i + k, r.v[k]); cnb_split_store1(d1, i + k, s.v[k]); }
             }
-            st<W>(sp, i, rh); st<W>(sp + np, i, sh); st<W>(sp + 2 * np, i, rl); st<W>(sp + 3 * np, i, sl);
         }
     }
 }
@@ -385,13 +386,12 @@ __global__ void sgd_k(float* __restrict__ w, float* __restrict__ g, size_t total
     }
 }
 
-// The update with the hi/lo TF32 split of the new values written in the same pass for the spans of the
+// The update with the operand split of the new values written in the same pass for the spans of the
 // arena that are Linear weights (span begins and lengths are multiples of 4 floats).
 struct SplitSpans {
     size_t begin[CNB_MAX_SPLIT_SPANS];
     size_t count[CNB_MAX_SPLIT_SPANS];
-    float* hi[CNB_MAX_SPLIT_SPANS];
-    float* lo[CNB_MAX_SPLIT_SPANS];
+    cnb_split_dst dst[CNB_MAX_SPLIT_SPANS];
     int n;
 };
 
@@ -407,14 +407,7 @@ __global__ void sgd_split_k(float* __restrict__ w, float* __restrict__ g, size_t
         if (zero_grad) st<4>(g, i, b);
         for (int s = 0; s < sp.n; ++s) {
             if (i >= sp.begin[s] && i < sp.begin[s] + sp.count[s]) {
-                Pack<4> h, l;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    h.v[k] = __uint_as_float(__float_as_uint(a.v[k]) & 0xFFFFE000u);
-                    l.v[k] = a.v[k] - h.v[k];
-                }
-                st<4>(sp.hi[s], i - sp.begin[s], h);
-                st<4>(sp.lo[s], i - sp.begin[s], l);
+                cnb_split_store4(sp.dst[s], i - sp.begin[s], a.v[0], a.v[1], a.v[2], a.v[3]);
                 break;
             }
         }
@@ -642,9 +635,12 @@ int cnb_sgd_update_split(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, i
     sp.n = nspans;
     for (int k = 0; k < nspans; ++k) {
         CNB_CHECK_ARG(spans[k].begin % 4 == 0 && spans[k].count % 4 == 0 && spans[k].begin + spans[k].count <= n &&
-                      all_aligned(spans[k].hi, spans[k].lo) && spans[k].hi && spans[k].lo,
+                      all_aligned(spans[k].hi, spans[k].h16, spans[k].l16) && spans[k].hi && spans[k].h16 && spans[k].l16,
                       "cnb_sgd_update_split: span %d is not a 16-byte aligned range of the arena", k);
-        sp.begin[k] = spans[k].begin; sp.count[k] = spans[k].count; sp.hi[k] = spans[k].hi; sp.lo[k] = spans[k].lo;
+        sp.begin[k] = spans[k].begin; sp.count[k] = spans[k].count;
+        sp.dst[k].hi = spans[k].hi;
+        sp.dst[k].h16 = static_cast<unsigned short*>(spans[k].h16);
+        sp.dst[k].l16 = static_cast<unsigned short*>(spans[k].l16);
     }
     cudaStream_t stm = cnb::S(stream);
     size_t blocks = (n / 4 + 255) / 256, cap = (size_t) ctx->sm_count * 16;

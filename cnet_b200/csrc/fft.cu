@@ -126,13 +126,11 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                     const float4 h0 = *reinterpret_cast<const float4*>(ep.hr + e), h1 = *reinterpret_cast<const float4*>(ep.hi + e);
                     const float ur[4] = {vr.x, vr.y, vr.z, vr.w}, ui[4] = {vi.x, vi.y, vi.z, vi.w};
                     const float pr[4] = {h0.x, h0.y, h0.z, h0.w}, pi[4] = {h1.x, h1.y, h1.z, h1.w};
-                    float gr[4], gi[4], rh[4], rl[4], sh[4], sl[4];
+                    float gr[4], gi[4];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         gr[k] = cnb_gelu(ur[k] * pr[k] - ui[k] * pi[k]);
                         gi[k] = cnb_gelu(ur[k] * pi[k] + ui[k] * pr[k]);
-                        rh[k] = __uint_as_float(__float_as_uint(gr[k]) & 0xFFFFE000u); rl[k] = gr[k] - rh[k];
-                        sh[k] = __uint_as_float(__float_as_uint(gi[k]) & 0xFFFFE000u); sl[k] = gi[k] - sh[k];
                     }
                     const size_t o = (size_t) row * N + e;
                     if (ep.gr) {
@@ -140,10 +138,8 @@ fft_rr_k(const float* __restrict__ xr, const float* __restrict__ xi, float* __re
                         *reinterpret_cast<float4*>(ep.gi + o) = make_float4(gi[0], gi[1], gi[2], gi[3]);
                     }
                     if (ep.sp) {
-                        *reinterpret_cast<float4*>(ep.sp + o) = make_float4(rh[0], rh[1], rh[2], rh[3]);
-                        *reinterpret_cast<float4*>(ep.sp + ep.np + o) = make_float4(sh[0], sh[1], sh[2], sh[3]);
-                        *reinterpret_cast<float4*>(ep.sp + 2 * ep.np + o) = make_float4(rl[0], rl[1], rl[2], rl[3]);
-                        *reinterpret_cast<float4*>(ep.sp + 3 * ep.np + o) = make_float4(sl[0], sl[1], sl[2], sl[3]);
+                        cnb_split_store4(cnb_split_component(ep.sp, ep.np, 0), o, gr[0], gr[1], gr[2], gr[3]);
+                        cnb_split_store4(cnb_split_component(ep.sp, ep.np, 1), o, gi[0], gi[1], gi[2], gi[3]);
                     }
                 }
             }

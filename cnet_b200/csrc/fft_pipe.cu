@@ -197,12 +197,13 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
         stored = true;
         CNB_STAMP(10);
         if (ep.hr) {
-            // fused tail: y = gelu(u o h) and its hi/lo split, straight from the registers; a warp's
-            // store covers 128 contiguous bytes
+            // fused tail: y = gelu(u o h) and its operand split, straight from the registers; a warp's
+            // store covers 128 contiguous bytes of an fp32 plane, 64 of a bf16 plane
             const size_t o = (size_t) row * N + t;
             // h of the next position is requested before this position's stores (a load placed after them
             // would have to be issued after them: the compiler cannot tell that they do not alias)
             float hr_next = __ldg(ep.hr + t), hi_next = __ldg(ep.hi + t);      // bitrev(0) = 0
+            const cnb_split_dst sp_re = cnb_split_component(ep.sp, ep.np, 0), sp_im = cnb_split_component(ep.sp, ep.np, 1);
 #pragma unroll
             for (int p = 0; p < R; ++p) {
                 const int e = bitrev<R>(p) * R;
@@ -215,12 +216,8 @@ fft1024_pipe_k(const float* __restrict__ xr, const float* __restrict__ xi, float
                 const float gi = cnb_gelu(re[p] * hi + im[p] * hr);
                 if (ep.gr) { ep.gr[o + e] = gr; ep.gi[o + e] = gi; }
                 if (ep.sp) {
-                    const float rh = __uint_as_float(__float_as_uint(gr) & 0xFFFFE000u);
-                    const float sh = __uint_as_float(__float_as_uint(gi) & 0xFFFFE000u);
-                    ep.sp[o + e] = rh;
-                    ep.sp[ep.np + o + e] = sh;
-                    ep.sp[2 * ep.np + o + e] = gr - rh;
-                    ep.sp[3 * ep.np + o + e] = gi - sh;
+                    cnb_split_store1(sp_re, o + e, gr);
+                    cnb_split_store1(sp_im, o + e, gi);
                 }
             }
         }

@@ -191,7 +191,7 @@ int cnb_split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, f
 }
 
 int cnb_linear_split_ok(int B, int in, int out) {
-    return (B >= 64 && in >= 64 && out >= 64 && in % 32 == 0 && out % 32 == 0) ? 1 : 0;
+    return (B >= 64 && in >= 64 && out >= 64 && in % 64 == 0 && out % 64 == 0) ? 1 : 0;
 }
 
 namespace {

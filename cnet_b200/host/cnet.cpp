@@ -1213,8 +1213,11 @@ void CNet::updateInputs(float lr) {
 		const Vars& w = l->prev_func_[1]->out_;
 		const size_t np = cnb_split_floats((size_t) l->in2_len) / 4;
 		if (l->in2_len % 4 || w.real_ < weight_base_ || w.imag_ + l->in2_len > weight_base_ + wgrad_count_) continue;
-		spans.push_back({(size_t) (w.real_ - weight_base_), (size_t) l->in2_len, l->w_split_, l->w_split_ + 2 * np});
-		spans.push_back({(size_t) (w.imag_ - weight_base_), (size_t) l->in2_len, l->w_split_ + np, l->w_split_ + 3 * np});
+		// slots of the split buffer: hi_re, hi_im (fp32), then [h16_re ; h16_im] and [l16_re ; l16_im] as bf16
+		uint16_t* h16 = reinterpret_cast<uint16_t*>(l->w_split_ + 2 * np);
+		uint16_t* l16 = reinterpret_cast<uint16_t*>(l->w_split_ + 3 * np);
+		spans.push_back({(size_t) (w.real_ - weight_base_), (size_t) l->in2_len, l->w_split_, h16, l16});
+		spans.push_back({(size_t) (w.imag_ - weight_base_), (size_t) l->in2_len, l->w_split_ + np, h16 + np, l16 + np});
 		fused.push_back(l);
 	}
 	int rc = spans.empty()
@@ -1317,16 +1320,24 @@ bool CNet::readOutput(int uid, int what, float* re, float* im) {
 	if (what != 0 && f->grad_transient_) sr = nullptr;       // overwritten by the gradient of the Residual's operand
 	if (!sr) { fail(CNB_ERR_ARG, f->getName() + ": tensor not materialised (fused)"); return false; }
 	size_t n = (size_t) (f->batched_ ? cur_batch_ : 1) * f->out_size_;
-	if (what == 0 && f->value_split_) {                       // hi + lo is the value, exactly
+	if (what == 0 && f->value_split_) {
+		// Only the operand split of the value was stored: hi (the value cut to TF32) plus the bf16 rounding of
+		// the remainder gives it back to 2^-19 relative, which is what the consuming product saw of it.
 		const size_t np = cnb_split_floats((size_t) cur_batch_ * f->out_size_) / 4;   // plane pitch of the batch in flight
-		std::vector<float> lo(n);
+		std::vector<uint16_t> lo(n);
+		const uint16_t* l16 = reinterpret_cast<const uint16_t*>(f->value_split_ + 3 * np);
 		for (int q = 0; q < 2; ++q) {
 			float* dst = q ? im : re;
 			int rc = cnb_d2h(ctx_, dst, f->value_split_ + q * np, n * sizeof(float), stream_);
-			if (rc == CNB_OK) rc = cnb_d2h(ctx_, lo.data(), f->value_split_ + (2 + q) * np, n * sizeof(float), stream_);
+			if (rc == CNB_OK) rc = cnb_d2h(ctx_, lo.data(), l16 + q * np, n * sizeof(uint16_t), stream_);
 			if (rc == CNB_OK) rc = cnb_sync(ctx_, stream_);
 			if (rc != CNB_OK) { fail(rc, "readOutput"); return false; }
-			for (size_t k = 0; k < n; ++k) dst[k] += lo[k];
+			for (size_t k = 0; k < n; ++k) {
+				const uint32_t bits = (uint32_t) lo[k] << 16;
+				float v;
+				std::memcpy(&v, &bits, sizeof v);
+				dst[k] += v;
+			}
 		}
 		return true;
 	}

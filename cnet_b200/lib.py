@@ -21,7 +21,7 @@ BUCKET_HOOK = C.CFUNCTYPE(C.c_int, _vp, _vp, _sz, C.c_int, C.c_int)
 _P = _vp   # device or host pointer passed as an integer address
 class SplitSpan(C.Structure):
     """cnb_split_span of include/cnet_b200.h."""
-    _fields_ = [("begin", C.c_size_t), ("count", C.c_size_t), ("hi", C.c_void_p), ("lo", C.c_void_p)]
+    _fields_ = [("begin", C.c_size_t), ("count", C.c_size_t), ("hi", C.c_void_p), ("h16", C.c_void_p), ("l16", C.c_void_p)]
 
 
 SIGNATURES = {

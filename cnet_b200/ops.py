@@ -221,10 +221,12 @@ class Context:
         return dtable
 
     def sgd_update_split(self, w, g, lr, spans, zero_grad=True):
-        """spans: [(begin, count, hi_tensor, lo_tensor)]; the updated floats of each span also leave their split."""
+        """spans: [(begin, count, hi (float32), h16 (bfloat16), l16 (bfloat16))]; the updated floats of each span
+        also leave their operand split: hi = w cut to TF32, h16 = bf16(hi), l16 = bf16(w - hi)."""
         arr = (_lib.SplitSpan * len(spans))()
-        for k, (begin, count, hi, lo) in enumerate(spans):
-            arr[k].begin, arr[k].count, arr[k].hi, arr[k].lo = begin, count, hi.data_ptr(), lo.data_ptr()
+        for k, (begin, count, hi, h16, l16) in enumerate(spans):
+            arr[k].begin, arr[k].count = begin, count
+            arr[k].hi, arr[k].h16, arr[k].l16 = hi.data_ptr(), h16.data_ptr(), l16.data_ptr()
         _lib.check(self.lib.cnb_sgd_update_split(self.h, _p(w), _p(g), w.numel(), lr, int(zero_grad), arr, len(spans),
                                                  self._stream()), "sgd_update_split")
 

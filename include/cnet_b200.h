@@ -99,11 +99,15 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im,
  * gpu/reduce.cpp:594-598 and gpu/reducegrad.cpp:309-322. */
 size_t cnb_linear_workspace(int B, int in, int out);
 int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes);
-/* The same three products on operands the caller has split once (hi/lo TF32 planes): a tensor
+/* The same three products on operands the caller has split once: a tensor
  * used by several products (X by forward and dW*, G by dX* and dW*, W by forward and dX*) is then
  * read by the tensor-core GEMM in place, row-major for one product and as the transposed operand
- * for the other.  `split` buffers hold cnb_split_floats(n) floats: hi_re, hi_im, lo_re, lo_im.
- * Eligible when cnb_linear_split_ok (all dims >= 64, in and out multiples of 32).  Same reference
+ * for the other.  The split of x: hi = x cut to TF32, lo = x - hi; the product takes hi.hi on the TF32
+ * pipe and the cross terms hi.lo + lo.hi on the BF16 pipe from bf16 roundings of hi and lo.  A `split`
+ * buffer holds cnb_split_floats(n) = 4 np floats, np = n rounded up to 64: [0, np) hi of the real plane,
+ * [np, 2 np) hi of the imaginary plane (fp32), then as bf16: np values bf16(hi_re), np of bf16(hi_im),
+ * np of bf16(lo_re), np of bf16(lo_im).
+ * Eligible when cnb_linear_split_ok (all dims >= 64, in and out multiples of 64).  Same reference
  * call sites as cnb_linear_fwd / _bwd_x / _bwd_w above. */
 size_t cnb_split_floats(size_t n);
 int cnb_split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, void* stream);
@@ -218,7 +222,7 @@ int cnb_hadamard_gelu_fwd(cnb_ctx* ctx, const float* u_re, const float* u_im,
                           const float* h_re, const float* h_im,
                           float* a_re, float* a_im, float* y_re, float* y_im,
                           int B, int N, void* stream);
-/* Same, and when y_split != NULL also writes the hi/lo TF32 split planes of y
+/* Same, and when y_split != NULL also writes the operand split of y
  * (cnb_split_floats(B*N) floats) that cnb_linear_fwd_split / _bwd_w_split consume. */
 int cnb_hadamard_gelu_fwd_split(cnb_ctx* ctx, const float* u_re, const float* u_im,
                                 const float* h_re, const float* h_im,
@@ -290,11 +294,11 @@ int cnb_embed_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
 int cnb_sgd_update(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
                    void* stream);
 /* The same update; the floats of [begin, begin + count) of every span (the planes of Linear weights)
- * also leave their hi/lo TF32 split in hi[i - begin], lo[i - begin], so the products of the next step
- * need no split pass over the weights.  n, begins and counts are multiples of 4; at most
+ * also leave their operand split (see cnb_split_floats) in hi[i - begin] (fp32), h16[i - begin] and
+ * l16[i - begin] (bf16), so the products of the next step need no split pass over the weights.  n, begins and counts are multiples of 4; at most
  * CNB_MAX_SPLIT_SPANS spans.  Same reference call site as cnb_sgd_update. */
 #define CNB_MAX_SPLIT_SPANS 48
-typedef struct cnb_split_span { size_t begin; size_t count; float* hi; float* lo; } cnb_split_span;
+typedef struct cnb_split_span { size_t begin; size_t count; float* hi; void* h16; void* l16; } cnb_split_span;
 int cnb_sgd_update_split(cnb_ctx* ctx, float* w, float* g, size_t n, float lr, int zero_grad,
                          const cnb_split_span* spans, int nspans, void* stream);
 

@@ -55,7 +55,7 @@ def test_linear_three_products(ctx, B, n_in, n_out):
     y = _host(ctx.linear_fwd(_dev(x), _dev(w)))
     assert util.relerr(y, _pair(X @ W.T)) < 1e-5
     # square shapes run on the tcgen05 tiles, skinny / tiny ones on the fp32 SIMT tiles
-    want_engine = 4 if (n_out <= 16 and n_in >= 32) else 1 if (B >= 64 and n_out >= 64 and n_in >= 32 and n_in % 4 == 0) else 2
+    want_engine = 4 if (n_out <= 16 and n_in >= 32) else 1 if (B >= 64 and n_out >= 64 and n_in >= 32 and n_in % 8 == 0) else 2
     assert ctx.last_gemm_engine() == want_engine
     yr = _host(ctx.linear_fwd(_dev(x), _dev(w), res=_dev(r)))
     assert util.relerr(yr, _pair(X @ W.T + _c(r))) < 1e-5
@@ -194,7 +194,8 @@ def test_sgd_update(ctx):
 
 
 def test_sgd_update_with_weight_split(ctx):
-    """The fused update leaves hi + lo == the new weight exactly, hi a TF32 value, only inside the spans."""
+    """The fused update leaves the operand split of the new weight, only inside the spans: hi = the weight cut to
+    TF32, h16 = bf16(hi), l16 = bf16(weight - hi) (round to nearest even)."""
     import torch
     rng = np.random.default_rng(6)
     n = 1 << 16
@@ -202,15 +203,21 @@ def test_sgd_update_with_weight_split(ctx):
     g = rng.standard_normal(n).astype(np.float32)
     W, G = torch.from_numpy(w).cuda(), torch.from_numpy(g).cuda()
     spans = [(256, 4096), (8192, 1 << 15)]
-    outs = [(torch.full((c,), 7.0, device="cuda"), torch.full((c,), 7.0, device="cuda")) for _, c in spans]
-    ctx.sgd_update_split(W, G, 0.25, [(b, c, hi, lo) for (b, c), (hi, lo) in zip(spans, outs)])
+    outs = [(torch.full((c,), 7.0, device="cuda"), torch.full((c,), 7.0, device="cuda", dtype=torch.bfloat16),
+             torch.full((c,), 7.0, device="cuda", dtype=torch.bfloat16)) for _, c in spans]
+    ctx.sgd_update_split(W, G, 0.25, [(b, c) + o for (b, c), o in zip(spans, outs)])
     want = w - np.float32(0.25) * g
     assert np.array_equal(W.cpu().numpy(), want)
     assert float(G.abs().max()) == 0.0
-    for (b, c), (hi, lo) in zip(spans, outs):
-        h, l = hi.cpu().numpy(), lo.cpu().numpy()
-        assert np.array_equal(h + l, want[b:b + c])
-        assert not np.any(h.view(np.uint32) & np.uint32(0x1FFF))
+    for (b, c), (hi, h16, l16) in zip(spans, outs):
+        x = torch.from_numpy(want[b:b + c])
+        h = (x.view(torch.int32) & ~0x1FFF).view(torch.float32)
+        assert torch.equal(hi.cpu(), h)
+        assert torch.equal(h16.cpu(), h.to(torch.bfloat16))
+        assert torch.equal(l16.cpu(), (x - h).to(torch.bfloat16))
+        # together they give the weight back to 2^-18
+        back = hi.cpu() + l16.cpu().float()
+        assert float((back - x).abs().max() / x.abs().max()) < 2.0 ** -18
 
 
 def test_bad_arguments_are_rejected_not_fatal(ctx):
