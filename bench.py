@@ -473,7 +473,7 @@ def _roofline(workload, kw, B, gbatch, step_ms, device, hbm_kernels=True):
                   [lambda k=k: L.cnb_dft_fwd(H_, P(u[k][0]), P(u[k][1]), P(o[k][0]), P(o[k][1]), B, N, st) for k in range(S)],
                   16.0 * B * N)]
         if L.cnb_dft_fused_ok(N):
-            # the forms that run inside the step: forward with the Hadamard + CGelu + hi/lo split tail (reads x; writes
+            # the forms that run inside the step: forward with the Hadamard + CGelu + operand split tail (reads x; writes
             # u and four split planes), backward accumulating into the gradient (reads g, read-modify-writes dx)
             sp = [torch.empty(L.cnb_split_floats(B * N), dtype=torch.float32, device="cuda") for _ in range(S)]
             cases.append(("fft1024_pipe_k<-1> + Hadamard + CGelu + split tail (as in the step)" if N == 1024 else "FourierTrans forward + tail",

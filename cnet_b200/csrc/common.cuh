@@ -57,7 +57,7 @@ int cgemm_simt(cnb_ctx* ctx, const float* a_re, const float* a_im, long sam, lon
                const float* r_re, const float* r_im, float* d_re, float* d_im,
                int M, int N, int K, int accumulate, cudaStream_t st);
 
-// tcgen05 3xTF32 complex GEMM, K-major operands only:
+// tcgen05 complex GEMM on split operands, K-major operands only:
 //   D[m,n] (+)= sum_k A[m,k] * (conjB ? conj(B[n,k]) : B[n,k]) (+ R[m,n]); A [M,K], B [N,K] row-major.
 // Returns CNB_ERR_UNSUPPORTED when the shape does not fit its tiles.
 int cgemm_tc_nt(cnb_ctx* ctx, const float* a_re, const float* a_im,
@@ -94,7 +94,7 @@ bool fft_supported(int N);
 int fft_run(cnb_ctx* ctx, const float* xr, const float* xi, float* yr, float* yi, int B, int N, int inverse,
             int accumulate, cudaStream_t st);
 // Forward FFT whose epilogue also applies Hadamard(h) -> CGelu: u = FFT(x) -> (ur, ui); y = gelu(u o h) ->
-// (yr, yi) and, when sp != NULL, the hi/lo split planes of y.
+// (yr, yi) and, when sp != NULL, the operand split of y.
 int fft_hadamard_gelu(cnb_ctx* ctx, const float* xr, const float* xi, const float* hr, const float* hi, float* ur,
                       float* ui, float* yr, float* yi, float* sp, int B, int N, cudaStream_t st);
 

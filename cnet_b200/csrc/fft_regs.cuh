@@ -46,9 +46,9 @@ __device__ __forceinline__ void fft_regs(float (&re)[R], float (&im)[R]) {
 struct FftEpilogue {
     const float* hr = nullptr;      // h planes [N]; NULL = plain transform
     const float* hi = nullptr;
-    float* gr = nullptr;            // gelu(u o h) planes [B, N]; may be NULL when sp is given (hi + lo is the value)
+    float* gr = nullptr;            // gelu(u o h) planes [B, N]; may be NULL when sp is given (hi + l16 is the value to 2^-19)
     float* gi = nullptr;
-    float* sp = nullptr;            // hi/lo split of that (4 planes of np floats) or NULL
+    float* sp = nullptr;            // operand split of that (a split buffer with plane pitch np) or NULL
     size_t np = 0;
 };
 

@@ -1,5 +1,5 @@
 // Complex Linear (forward, dX*, dW*) and FourierTrans as a complex GEMM against a
-// twiddle matrix: shape dispatch between the tcgen05 3xTF32 tiles and the fp32 SIMT tiles.
+// twiddle matrix: shape dispatch between the tcgen05 tiles (split operands) and the fp32 SIMT tiles.
 #include <algorithm>
 #include <cmath>
 #include <vector>
@@ -51,7 +51,7 @@ int get_twiddle(cnb_ctx* ctx, int key, cudaStream_t st, cnb_twiddle* out) {
         CNB_LAUNCH_CHECK("tri_mask");
     }
     if (cnb::cgemm_tc_shape_ok(64, N, N) && (!cnb::fft_supported(N) || (key & kTriKey))) {
-        // the matrix is a constant: where the GEMM is the transform's engine, its hi/lo split is
+        // the matrix is a constant: where the GEMM is the transform's engine, its operand split is
         // made here, not by every product
         rc = cnb_alloc(ctx, cnb_split_floats((size_t) N * N) * sizeof(float), &p);
         if (rc != CNB_OK) return rc;
@@ -182,7 +182,7 @@ size_t cnb_linear_workspace(int B, int in, int out) {
     return w;
 }
 
-/* ---- operands split once by the caller (hi/lo TF32 planes), reused by several products ---- */
+/* ---- operands split once by the caller (fp32 hi, bf16 hi and lo), reused by several products ---- */
 size_t cnb_split_floats(size_t n) { return 4 * ((n + 63) & ~size_t(63)); }
 
 int cnb_split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, void* stream) {

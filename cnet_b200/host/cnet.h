@@ -141,7 +141,7 @@ public:
 	Vars out_;
 	bool batched_ = true;        // false: one row shared by the batch (weights)
 	bool grad_written_ = false;  // has a consumer already written dL/dz* of out_ in this backward?
-	const float* value_split_ = nullptr; // value planes are not stored: out = hi + lo of these 4 split planes
+	const float* value_split_ = nullptr; // value planes are not stored: out = hi + l16 of this split buffer (the value to 2^-19)
 	bool grad_transient_ = false; // dL/dz* planes are shared with a Residual operand and accumulated over in place
 	bool fused_away_ = false;    // a neighbour's fused kernel does this layer's work
 
@@ -267,7 +267,7 @@ class Linear : public CFunc {                       // impl/linear.h:11-156
 	int in1_len, in2_len;
 	CFunc* fused_residual_ = nullptr;               // Residual add done in the GEMM epilogue
 	int residual_operand_ = 0;                      // which Residual input is the other addend
-	// hi/lo TF32 split planes kept by the layer: x is split in forward() and reused by dW*, W is
+	// operand split buffers kept by the layer: x is split in forward() and reused by dW*, W is
 	// split when the weights change and reused by forward and dX*
 	float* x_split_ = nullptr;
 	float* w_split_ = nullptr;

@@ -70,7 +70,7 @@ class Context:
                                              B, n_in, n_out, acc, self._stream()), "linear_bwd_w")
         return dw
 
-    # operands split once (hi/lo TF32 planes) and reused by several products
+    # operands split once (fp32 hi, bf16 hi and lo) and reused by several products
     def split(self, x):
         n = x[0].numel()
         out = self.torch.empty(self.lib.cnb_split_floats(n), dtype=self.torch.float32, device="cuda")
@@ -115,8 +115,8 @@ class Context:
         return dx
 
     def dft_hadamard_gelu_fwd(self, x, h, u=None, split=None):
-        """FourierTrans forward with the Hadamard(h) -> CGelu tail in the same kernel: u = FFT(x) and the hi/lo
-        split planes of y = gelu(u o h) (y itself is hi + lo and is not stored).  Returns (u, split)."""
+        """FourierTrans forward with the Hadamard(h) -> CGelu tail in the same kernel: u = FFT(x) and the operand
+        split of y = gelu(u o h) (y itself is not stored).  Returns (u, split)."""
         B, N = x[0].shape
         u = u if u is not None else self._new(B, N)
         if split is None:

@@ -94,7 +94,7 @@ int cnb_linear_bwd_w(cnb_ctx* ctx, const float* g_re, const float* g_im,
                      float* dw_re, float* dw_im, int B, int in, int out,
                      int accumulate, void* stream);
 /* Scratch bytes the three products of a Linear(B, in, out) may take from the arena (operand
- * hi/lo split planes of the tensor-core GEMM), and a way to reserve the step's maximum up front
+ * split buffers of the tensor-core GEMM), and a way to reserve the step's maximum up front
  * so that no call on the step path grows the scratch region.  Replace the per-call cudaMalloc of
  * gpu/reduce.cpp:594-598 and gpu/reducegrad.cpp:309-322. */
 size_t cnb_linear_workspace(int B, int in, int out);
@@ -124,7 +124,7 @@ int cnb_linear_bwd_w_split(cnb_ctx* ctx, const float* g_split, const float* x_sp
  * all-reduce of a data-parallel job); 0 restores the full grid.  No reference counterpart. */
 int cnb_set_gemm_sm_limit(cnb_ctx* ctx, int max_ctas);
 /* Which GEMM engine the last cnb_linear_* call on this thread used:
- * 1 = tcgen05 3xTF32 tensor-core tiles, 2 = fp32 SIMT tiles (ragged shapes),
+ * 1 = tcgen05 tensor-core tiles (split operands: TF32 hi.hi + BF16 cross terms), 2 = fp32 SIMT tiles (ragged shapes),
  * 4 = skinny fp32 kernels (out <= 16, HBM-bound). */
 int cnb_last_gemm_engine(void);
 
@@ -141,8 +141,9 @@ int cnb_dft_bwd(cnb_ctx* ctx, const float* g_re, const float* g_im,
                 float* dx_re, float* dx_im, int B, int N, int accumulate, void* stream);
 /* FourierTrans -> Hadamard(shared h) -> CGelu in one pass over the row (N = 256, 1024, 4096, see
  * cnb_dft_fused_ok): u = DFT(x) is kept for the backward, y = gelu(u o h), optionally with the
- * hi/lo split planes of y for the Linear that follows; y_re = y_im = NULL is allowed when y_split
- * is given (hi + lo is y exactly, so a caller that only feeds the Linear need not store y twice).
+ * operand split of y for the Linear that follows; y_re = y_im = NULL is allowed when y_split
+ * is given (hi + l16 of the split is y to 2^-19, all the product sees of it, so a caller that only feeds the
+ * Linear need not store y twice).
  * The Hadamard product a = u o h is not stored: cnb_hadamard_gelu_bwd recomputes it when a_re == NULL.  Same reference kernels as
  * cnb_dft_fwd + cnb_hadamard_gelu_fwd. */
 int cnb_dft_fused_ok(int N);
