@@ -38,16 +38,26 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 16, STAGES = 3;
-constexpr int PLANE_BYTES = BM * BK * 4;             // 8 KB: one operand plane of one stage
-constexpr int STAGE_BYTES = 8 * PLANE_BYTES;         // 64 KB
+constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int PLANE_BYTES = BM * BK * 4;             // 8 KB: one operand slot of one stage
+// One CTA per tile: 8 slots (A: 4, B: 4) = 64 KB per stage, 3 stages.  A pair of CTAs per 256-row tile
+// (cta_group::2): each CTA stages its own 128 rows of A (4 slots) and one of the two halves of the stacked B
+// operand (B_re rows in the first CTA, B_im rows in the second: 2 slots) = 48 KB per stage, 4 stages.
+template <bool PAIR> struct Cfg {
+    static constexpr int STAGES = PAIR ? 4 : 3;
+    static constexpr int STAGE_BYTES = (PAIR ? 6 : 8) * PLANE_BYTES;
+    static constexpr int TILE_M = PAIR ? 2 * BM : BM;
+};
+constexpr int OPERAND_BYTES = 3 * 8 * PLANE_BYTES;   // 192 KB of operand stages in both forms
 constexpr int EPI_BYTES = 2 * 128 * 32 * 4;           // 32 KB: one epilogue round, re and im staging
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = OPERAND_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+static_assert(Cfg<false>::STAGES * Cfg<false>::STAGE_BYTES == OPERAND_BYTES && Cfg<true>::STAGES * Cfg<true>::STAGE_BYTES == OPERAND_BYTES, "stages");
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -62,6 +72,7 @@ struct TcParams {
     int whole_per_cta;        // > 0: every CTA first takes that many whole tiles, then its run of the remaining units
     int segments;             // > 0: CTA r takes k-segment r / tiles of tile r % tiles (units_per_cta k-blocks each)
     int* status;
+    // The pair form (cgemm_tc_k<true>) reads none of cluster / segments: its cluster is the CTA pair of one tile.
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
@@ -129,6 +140,35 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// The pair form's loads: the data goes to this CTA's shared memory, the completion bytes to the barrier `bar`,
+// a shared::cluster address that may lie in the peer CTA (the pair's first CTA collects both halves).
+__device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma2_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// shared::cluster address of `local_addr` (a shared::cta address of this CTA's layout) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // MN-major operand tile (source stored [K, rows]): slabs of 32 rows-of-the-operand, each slab
@@ -202,6 +242,33 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// The pair form: one MMA of the pair's first CTA multiplies the 256 rows of A held by both CTAs (128 each, at the
+// same shared-memory offsets) with the B operand whose two 128-row halves the two CTAs hold; each CTA's tensor
+// memory receives the accumulator rows of its own A.
+__device__ __forceinline__ void umma2_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short) 3) : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -348,6 +415,7 @@ __device__ __forceinline__ void cluster_reduce(const TcParams& p, uint32_t smem_
 #define CNB_GSTAMP(k, cond) do { } while (0)
 #endif
 
+template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ CUtensorMap a_hi_im,
            const __grid_constant__ CUtensorMap a_h16, const __grid_constant__ CUtensorMap a_l16,
@@ -357,32 +425,39 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     CNB_GSTAMP(0, threadIdx.x == 0);
     // operand stages need the alignment of their swizzle pattern; 1024 B covers every mode
+    constexpr int STAGES = Cfg<PAIR>::STAGES, STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES, TILE_M = Cfg<PAIR>::TILE_M;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    float* stage_re = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
+    float* stage_re = reinterpret_cast<float*>(smem + OPERAND_BYTES);
     float* stage_im = stage_re + 128 * 32;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OPERAND_BYTES + EPI_BYTES);
     // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulators ready, bars[2S+1] accumulators drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (p.N + BN - 1) / BN;
-    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tiles_m = (p.M + TILE_M - 1) / TILE_M;
     const int k_blocks = (p.K + BK - 1) / BK;
     const long total_units = (long) tiles_m * tiles_n * k_blocks;
+    // In the pair form the two CTAs of a cluster work through the same units (each on its own 128 rows of the
+    // 256-row tile): "CTA" below is the pair.
+    const uint32_t prank = PAIR ? cluster_rank() : 0u;
+    const long cta_idx = PAIR ? (long) (blockIdx.x >> 1) : (long) blockIdx.x;
+    const long cta_cnt = PAIR ? (long) (gridDim.x >> 1) : (long) gridDim.x;
+    const int row_off = PAIR ? (int) prank * BM : 0;
     // up to two consecutive runs of (tile, k-block) units per CTA
-    long u_begin = (long) blockIdx.x * p.units_per_cta;
+    long u_begin = cta_idx * p.units_per_cta;
     long u_end = min(total_units, u_begin + p.units_per_cta);
     long u2_begin = 0, u2_end = 0;
     if (p.whole_per_cta > 0) {
         const long lead = (long) p.whole_per_cta * k_blocks;             // whole tiles first ...
-        const long rest0 = lead * gridDim.x;                              // ... then a share of what is left
-        u2_begin = min(total_units, rest0 + (long) blockIdx.x * p.units_per_cta);
+        const long rest0 = lead * cta_cnt;                                // ... then a share of what is left
+        u2_begin = min(total_units, rest0 + cta_idx * p.units_per_cta);
         u2_end = min(total_units, u2_begin + p.units_per_cta);
-        u_begin = lead * blockIdx.x;
+        u_begin = lead * cta_idx;
         u_end = u_begin + lead;
     }
-    if (p.segments > 0) {
+    if (!PAIR && p.segments > 0) {
         // Capped chains (K > 4096): consecutive CTAs take the SAME k-segment of consecutive tiles, so the CTAs that
         // run together read the same columns of A and B and share them through L2 (tile-major runs had every CTA
         // of a wave on its own k-range: 5.0 GB of DRAM reads for 0.8 GB of operands at 1024 x 2048 x 16384).
@@ -392,8 +467,9 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         u_end = min(u_begin + p.units_per_cta, (tile + 1) * k_blocks);
         if (u_begin > u_end) u_begin = u_end;
     }
-    const uint32_t crank = p.cluster > 1 ? cluster_rank() : 0;
-    if (p.cluster > 1) {                                 // one tile per cluster, an even slice of its k-blocks per CTA
+    const bool split_cluster = !PAIR && p.cluster > 1;
+    const uint32_t crank = split_cluster ? cluster_rank() : 0;
+    if (split_cluster) {                                 // one tile per cluster, an even slice of its k-blocks per CTA
         const long tile = blockIdx.x / p.cluster;
         u_begin = tile * k_blocks + (long) k_blocks * crank / p.cluster;
         u_end = tile * k_blocks + (long) k_blocks * (crank + 1) / p.cluster;
@@ -408,14 +484,20 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 1);
+        mbar_init(acc_empty, PAIR ? 2 : 1);              // pair: the epilogues of both CTAs hand the accumulators back
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // whole warp: allocate all 512 tensor-memory columns (1 CTA per SM by shared-memory size)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {                            // the same warp of both CTAs of the pair
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     if (warp == 0 && lane < 8) {   // descriptor fetch of the 8 operand maps, off the first TMA's critical path
         const CUtensorMap* maps[8] = {&a_hi_re, &a_hi_im, &a_h16, &a_l16, &b_hi_re, &b_hi_im, &b_h16, &b_l16};
@@ -423,6 +505,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();                  // the peer's barriers exist before anything signals them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     // Everything above touched no memory another kernel writes: under programmatic dependent launch it ran
@@ -441,12 +524,39 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             for (int pass = 0; pass < 2 && live; ++pass)
             for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue; ++u, ++it) {
                 int tile = (int) (u / k_blocks), kb = (int) (u % k_blocks);
-                int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+                int m0 = (tile / tiles_n) * TILE_M + row_off, n0 = (tile % tiles_n) * BN;
                 int s = (int) (it % STAGES);
                 uint32_t phase = (uint32_t) (it / STAGES) & 1;
                 if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, 1)) { live = false; break; }
-                mbar_expect_tx(full_bar(s), STAGE_BYTES);
                 uint32_t dst = smem_base + s * STAGE_BYTES;
+                if constexpr (PAIR) {
+                    // Both CTAs fill their own stage; all completion bytes go to the full barrier of the pair's
+                    // first CTA, which expects the bytes of both.
+                    const uint32_t bar = map_to_rank(full_bar(s), 0);
+                    if (prank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {        // this CTA's 128 rows of A: hi_re, hi_im, h16 pair, l16 pair
+                        if (q < 2) {
+                            if (p.a_mn) tma2_load_3d(dst + q * PLANE_BYTES, maps[q], bar, 0, kb * BK, m0 / 32);
+                            else tma2_load_2d(dst + q * PLANE_BYTES, maps[q], bar, kb * BK, m0);
+                        } else {
+                            if (p.a_mn) tma2_load_4d(dst + q * PLANE_BYTES, maps[q], bar, 0, kb * BK, m0 / 64, 0);
+                            else tma2_load_3d(dst + q * PLANE_BYTES, maps[q], bar, kb * BK, m0, 0);
+                        }
+                    }
+                    // this CTA's half of the stacked B operand: the real planes (first CTA) or the imaginary ones
+                    const int c = (int) prank;
+                    uint32_t db = dst + 4 * PLANE_BYTES;
+                    if (p.b_mn) tma2_load_3d(db, maps[4 + c], bar, 0, kb * BK, n0 / 32);
+                    else tma2_load_2d(db, maps[4 + c], bar, kb * BK, n0);
+                    db += PLANE_BYTES;
+                    for (int q = 6; q < 8; ++q, db += PLANE_BYTES / 2) {      // h16, l16: boxes of one plane
+                        if (p.b_mn) tma2_load_4d(db, maps[q], bar, 0, kb * BK, n0 / 64, c);
+                        else tma2_load_3d(db, maps[q], bar, kb * BK, n0, c);
+                    }
+                    continue;
+                }
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int r0 = q < 4 ? m0 : n0;
@@ -462,14 +572,16 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer (pair: its first CTA only)
+        if (lane == 0 && prank == 0) {
             bool ok = true;
             long it = 0;
             int seg = 0;
             // bits 15 / 16 of the instruction descriptor: operand A / B is MN-major
             const uint32_t mn_bits = (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
-            const uint32_t idesc = kInstrDesc | mn_bits, idesc16 = kInstrDesc16 | mn_bits;
+            // pair: M = 256 over the two CTAs
+            const uint32_t m_bits = PAIR ? ((256u >> 4) << 24) - ((128u >> 4) << 24) : 0u;
+            const uint32_t idesc = (kInstrDesc | mn_bits) + m_bits, idesc16 = (kInstrDesc16 | mn_bits) + m_bits;
             for (int pass = 0; pass < 2; ++pass)
             for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue && ok; ++seg) {
                 int kb0 = (int) (u % k_blocks);
@@ -487,6 +599,36 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t st = smem_base + s * STAGE_BYTES;
                     const uint32_t first = kb == kb0 ? 0u : 1u;
+                    if constexpr (PAIR) {
+                        // slots: 0 / 1 A hi_re / hi_im, 2 / 3 A h16 / l16 [re ; im], 4 B hi, 5 B h16 then l16
+                        auto a16 = [&](int slot, int im) {
+                            const uint32_t a = st + slot * PLANE_BYTES + im * (PLANE_BYTES / 2);
+                            return p.a_mn ? smem_desc_mn128_b16(a) : smem_desc_sw32(a);
+                        };
+                        auto b16 = [&](int half) {
+                            const uint32_t a = st + 5 * PLANE_BYTES + half * (PLANE_BYTES / 2);
+                            return p.b_mn ? smem_desc_mn128_b16(a) : smem_desc_sw32(a);
+                        };
+                        const uint64_t b_h16 = b16(0), b_l16 = b16(1);
+                        umma2_bf16(tmem_base, a16(3, 0), b_h16, idesc16, first);
+                        umma2_bf16(tmem_base, a16(2, 0), b_l16, idesc16, 1u);
+                        umma2_bf16(tmem_base + 256, a16(3, 1), b_h16, idesc16, first);
+                        umma2_bf16(tmem_base + 256, a16(2, 1), b_l16, idesc16, 1u);
+#pragma unroll
+                        for (int j = 0; j < BK / 8; ++j) {
+                            const uint32_t ka = p.a_mn ? j * 1024 : j * 32, kbo = p.b_mn ? j * 1024 : j * 32;
+                            auto adesc = [&](int plane) {
+                                uint32_t a = st + plane * PLANE_BYTES + ka;
+                                return p.a_mn ? smem_desc_mn128(a) : smem_desc_sw64(a);
+                            };
+                            const uint32_t bb = st + 4 * PLANE_BYTES + kbo;
+                            const uint64_t b_h = p.b_mn ? smem_desc_mn128(bb) : smem_desc_sw64(bb);
+                            umma2_tf32(tmem_base, adesc(0), b_h, idesc, 1u);
+                            umma2_tf32(tmem_base + 256, adesc(1), b_h, idesc, 1u);
+                        }
+                        umma2_commit_both(empty_bar(s));     // the stage is free in both CTAs once these MMAs have read it
+                        continue;
+                    }
                     {
                         // the cross terms first (small terms first): one BF16 k-step covers the whole 16-deep block.
                         // A slots 2 / 3 hold [re ; im] of h16 / l16 (4 KB each), B slots 6 / 7 the 256-row operands.
@@ -519,7 +661,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     }
                     umma_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                 }
-                if (ok) umma_commit(acc_full);
+                if (ok) { if constexpr (PAIR) umma2_commit_both(acc_full); else umma_commit(acc_full); }
                 CNB_GSTAMP(3, true);
                 u += kb1 - kb0;
             }
@@ -535,7 +677,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
             ((reinterpret_cast<uintptr_t>(p.d_re) | reinterpret_cast<uintptr_t>(p.d_im) |
               reinterpret_cast<uintptr_t>(p.r_re) | reinterpret_cast<uintptr_t>(p.r_im)) & 15) == 0;
         int seg = 0;
-        if (p.cluster > 1) {
+        if (split_cluster) {
             // the whole k-slice is one segment; its partial sums go to shared memory for the cluster reduction
             {
                 const int tile = blockIdx.x / p.cluster, rows_per = BM / p.cluster;
@@ -580,7 +722,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         for (long u = pass ? u2_begin : u_begin, ue = pass ? u2_end : u_end; u < ue; ++seg) {
             int tile = (int) (u / k_blocks), kb0 = (int) (u % k_blocks);
             int kb1 = (int) min((long) k_blocks, kb0 + (ue - u));
-            int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            int m0 = (tile / tiles_n) * TILE_M + row_off, n0 = (tile % tiles_n) * BN;
             const bool partial = !(kb0 == 0 && kb1 == k_blocks);   // split tiles are summed with atomics
             const bool add_res = p.r_re != nullptr && kb0 == 0;
             // one row of the tile per epilogue thread, requested before the wait for the MMAs
@@ -649,7 +791,10 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 }
                 epi_bar_sync();
-                if (c0 + 32 == BN && et == 0) mbar_arrive(acc_empty);
+                if (c0 + 32 == BN && et == 0) {
+                    if constexpr (PAIR) mbar_arrive_cluster(map_to_rank(acc_empty, 0));   // the first CTA's MMA thread waits for both
+                    else mbar_arrive(acc_empty);
+                }
                 // coalesced write-out: each warp instruction covers 4 rows x 128 contiguous bytes
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -697,7 +842,13 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (p.cluster > 1) {
+    if constexpr (PAIR) {
+        // No CTA of the pair leaves (or frees tensor memory) while the other may still signal its barriers, read its
+        // shared memory (the first CTA's MMAs read the peer's operand stages) or write its tensor memory.  Every thread
+        // reaches this barrier, also after a bounded wait gave up.
+        cluster_sync();
+    }
+    if (split_cluster) {
         // Every thread of every CTA of the cluster reaches both barriers, also after a bounded wait gave up.
         cluster_sync();                                  // all partial tiles are in shared memory
         CNB_GSTAMP(6, threadIdx.x == 64);
@@ -720,7 +871,8 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     }
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -815,13 +967,14 @@ int make_map_mn(CUtensorMap* m, const float* base, int rows, int K) {
 }
 
 // A pair of bf16 planes (real, imaginary; np elements apart), each [rows, K] row-major, seen as [2][rows][K]: one
-// box {BK, 128, 2} brings the 128 rows of both planes, real then imaginary; 32-byte swizzle.
-int make_map16(CUtensorMap* m, const void* base, int rows, int K, size_t np) {
+// box {BK, 128, 2} brings the 128 rows of both planes, real then imaginary (planes_per_box = 1: of one plane);
+// 32-byte swizzle.
+int make_map16(CUtensorMap* m, const void* base, int rows, int K, size_t np, unsigned planes_per_box) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[3] = {(cuuint64_t) K, (cuuint64_t) rows, 2u};
     cuuint64_t strides[2] = {(cuuint64_t) K * 2u, (cuuint64_t) np * 2u};
-    cuuint32_t box[3] = {(cuuint32_t) BK, 128u, 2u};
+    cuuint32_t box[3] = {(cuuint32_t) BK, 128u, planes_per_box};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -832,12 +985,12 @@ int make_map16(CUtensorMap* m, const void* base, int rows, int K, size_t np) {
 
 // The same pair stored [K, rows] (rows contiguous, rows % 64 == 0), seen as [2][rows/64][K][64]: one box
 // {64, BK, 2, 2} brings two 64-row slabs of 16 k-lines of both planes, slab after slab (128-byte swizzle).
-int make_map16_mn(CUtensorMap* m, const void* base, int rows, int K, size_t np) {
+int make_map16_mn(CUtensorMap* m, const void* base, int rows, int K, size_t np, unsigned planes_per_box) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return cnb::set_error(CNB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[4] = {64u, (cuuint64_t) K, (cuuint64_t) (rows / 64), 2u};
     cuuint64_t strides[3] = {(cuuint64_t) rows * 2u, 128u, (cuuint64_t) np * 2u};
-    cuuint32_t box[4] = {64u, (cuuint32_t) BK, 2u, 2u};
+    cuuint32_t box[4] = {64u, (cuuint32_t) BK, 2u, planes_per_box};
     cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -890,7 +1043,8 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
                       int accumulate, cudaStream_t st) {
     static bool attr_set[64] = {};                       // the attribute is per device
     if (!attr_set[ctx->device & 63]) {
-        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set[ctx->device & 63] = true;
     }
     if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
@@ -899,29 +1053,8 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         return set_error(CNB_ERR_ARG, "cgemm_tc: an MN-major operand needs a multiple of 64 rows");
     if ((!a_mn && K % 8) || (!b_mn && K % 8))
         return set_error(CNB_ERR_ARG, "cgemm_tc: a K-major operand needs K %% 8 == 0");
-    int rc;
-    alignas(64) CUtensorMap maps[8];
-    const size_t npa = (size_t) (a[3] - a[2]), npb = (size_t) (b[3] - b[2]);     // plane pitch, elements
-    for (int q = 0; q < 4; ++q) {
-        if (q < 2) {
-            rc = a_mn ? make_map_mn(&maps[q], a[q], M, K) : make_map(&maps[q], a[q], M, K);
-            if (rc != CNB_OK) return rc;
-            rc = b_mn ? make_map_mn(&maps[4 + q], b[q], N, K) : make_map(&maps[4 + q], b[q], N, K);
-            if (rc != CNB_OK) return rc;
-        } else {
-            rc = a_mn ? make_map16_mn(&maps[q], a[q], M, K, npa) : make_map16(&maps[q], a[q], M, K, npa);
-            if (rc != CNB_OK) return rc;
-            rc = b_mn ? make_map16_mn(&maps[4 + q], b[q], N, K, npb) : make_map16(&maps[4 + q], b[q], N, K, npb);
-            if (rc != CNB_OK) return rc;
-        }
-    }
-    int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    int k_blocks = (K + BK - 1) / BK;
-    long total = (long) tiles * k_blocks;
-    long min_units = 8;                                  // do not split below 8 k-blocks per CTA
-    // leaving a few SMs free (gemm_cta_limit) lets a concurrent collective's kernels run beside the GEMM
-    const int sms = ctx->gemm_cta_limit > 0 ? std::min(ctx->gemm_cta_limit, ctx->sm_count) : ctx->sm_count;
-    // Schedule, by tile count (sms = the SMs this launch may fill):
+    // Schedule, by tile count ("CTA" = one CTA, or the CTA pair of a 256-row tile; sms = how many of them this launch
+    // may fill: leaving a few SMs free (gemm_cta_limit) lets a concurrent collective's kernels run beside the GEMM):
     //  * tiles >= 4 x SMs, or one nearly full wave of one-tile CTAs when D is not read: whole tiles, grid =
     //    tiles, plain stores, fixed summation order;
     //  * more tiles than SMs: persistent CTAs, one per SM; each takes tiles / SMs whole tiles and then an
@@ -929,51 +1062,88 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     //    and only the remainder needs atomics and a cleared output;
     //  * few tiles and short runs: a cluster per tile (below); otherwise plain stream-K.
     // K > 4096 keeps to stream-K runs: one fp32 accumulation chain in tensor memory that long costs accuracy.
-    const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
-    const bool whole_tiles = (tiles >= ctx->sm_count * 4 && ctx->gemm_cta_limit <= 0 && k_blocks <= 256) || full_wave;
-    const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
-    long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
-    if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
-    long upc = (total + ctas - 1) / ctas;
-    if (whole_tiles) upc = k_blocks;
-    // The tensor core adds into its fp32 accumulator with truncation, so the error of one accumulation chain
-    // in tensor memory grows with its length: measured ~2e-6 of the accumulator's magnitude per k-block, which
-    // reached 1e-3 on a 443-k-block chain whose accumulator one large term dominated (the gradient of a loss
-    // through a K = 8192 product).  Runs are therefore capped at kMaxChain k-blocks (the partial tiles are summed
-    // outside, in fp32 round-to-nearest): several equal waves of CTAs instead of one persistent wave.
-    // Only K > 4096 gets here with longer runs; a whole tile of K <= 4096 is at most 256 k-blocks.  Each tile is cut
-    // into equal segments and the CTAs are numbered segment-major (see the kernel).
-    constexpr long kMaxChain = 64;
-    int segments = 0;
-    if (!whole_tiles && upc > kMaxChain && k_blocks > 256) {
-        segments = (int) ((k_blocks + kMaxChain - 1) / kMaxChain);       // per tile, each at most kMaxChain k-blocks
-        upc = (k_blocks + segments - 1) / segments;
-        ctas = (long) tiles * segments;
-    } else {
-        ctas = (total + upc - 1) / upc;
+    struct Plan { long ctas, upc; int whole_per_cta, clear_from_row, cluster, segments; bool splits_tiles; };
+    const int k_blocks = (K + BK - 1) / BK;
+    auto plan = [&](bool pair) {
+        Plan q = {};
+        const int tile_m = pair ? 2 * BM : BM;
+        const int tiles = ((M + tile_m - 1) / tile_m) * ((N + BN - 1) / BN);
+        const long total = (long) tiles * k_blocks;
+        const long min_units = 8;                            // do not split below 8 k-blocks per CTA
+        const int all = pair ? ctx->sm_count / 2 : ctx->sm_count;
+        const int sms = ctx->gemm_cta_limit > 0 ? std::min(pair ? ctx->gemm_cta_limit / 2 : ctx->gemm_cta_limit, all) : all;
+        const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
+        const bool whole_tiles = (tiles >= all * 4 && ctx->gemm_cta_limit <= 0 && k_blocks <= 256) || full_wave;
+        const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
+        long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
+        if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
+        long upc = (total + ctas - 1) / ctas;
+        if (whole_tiles) upc = k_blocks;
+        // The tensor core adds into its fp32 accumulator with truncation, so the error of one accumulation chain
+        // in tensor memory grows with its length: measured ~2e-6 of the accumulator's magnitude per k-block, which
+        // reached 1e-3 on a 443-k-block chain whose accumulator one large term dominated (the gradient of a loss
+        // through a K = 8192 product).  Runs are therefore capped at kMaxChain k-blocks (the partial tiles are summed
+        // outside, in fp32 round-to-nearest): several equal waves of CTAs instead of one persistent wave.
+        // Only K > 4096 gets here with longer runs; a whole tile of K <= 4096 is at most 256 k-blocks.  Each tile is
+        // cut into equal segments and the CTAs are numbered segment-major (see the kernel).
+        constexpr long kMaxChain = 64;
+        if (!whole_tiles && upc > kMaxChain && k_blocks > 256) {
+            q.segments = (int) ((k_blocks + kMaxChain - 1) / kMaxChain);     // per tile, each at most kMaxChain k-blocks
+            upc = (k_blocks + q.segments - 1) / q.segments;
+            ctas = (long) tiles * q.segments;
+        } else {
+            ctas = (total + upc - 1) / upc;
+        }
+        if (lead_whole) {
+            ctas = sms;
+            q.whole_per_cta = tiles / sms;
+            const long rest = (long) (tiles - q.whole_per_cta * sms) * k_blocks;
+            upc = (rest + ctas - 1) / ctas;
+            q.clear_from_row = (q.whole_per_cta * sms / ((N + BN - 1) / BN)) * tile_m;   // rows below are only ever stored whole
+        }
+        // Few tiles (small batches): a cluster of 2, 4 or 8 CTAs takes one tile, every CTA a slice of K, and
+        // the partial tiles are summed through distributed shared memory: no atomics, no cleared output,
+        // a fixed summation order.
+        // Worth it while a stream-K run would be short (<= 48 k-blocks): with long runs the atomics are
+        // amortised and using every SM wins over the clusters' rounded-down CTA count.
+        q.cluster = 1;
+        if (!whole_tiles && !lead_whole && upc <= 48) {
+            for (int c = 8; c >= 2; c >>= 1)
+                if ((long) tiles * c <= sms && k_blocks / c >= 4) { q.cluster = c; break; }
+        }
+        if (q.cluster > 1) { ctas = (long) tiles * q.cluster; upc = 0; }
+        q.splits_tiles = q.cluster == 1 && (lead_whole ? upc > 0 : (q.segments > 0 || (upc % k_blocks) != 0));
+        q.ctas = ctas; q.upc = upc;
+        return q;
+    };
+    // The pair form (two CTAs, cta_group::2, per 256-row tile: each CTA stages half of the B operand, so a k-block
+    // costs 48 KB of shared-memory fill per CTA instead of 64 KB) takes the large launches: no SMs set aside, at
+    // least one whole pair tile of rows, K <= 4096, and a schedule that is not the K-split cluster.
+    static const bool pair_allowed = [] { const char* e = getenv("CNB_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    bool pair = pair_allowed && ctx->gemm_cta_limit <= 0 && M >= 2 * BM && k_blocks <= 256;
+    Plan q = plan(pair);
+    if (pair && (q.cluster > 1 || q.segments > 0)) { pair = false; q = plan(false); }
+    const long ctas = q.ctas, upc = q.upc;
+    const int whole_per_cta = q.whole_per_cta, clear_from_row = q.clear_from_row, cluster = q.cluster, segments = q.segments;
+
+    int rc;
+    alignas(64) CUtensorMap maps[8];
+    const size_t npa = (size_t) (a[3] - a[2]), npb = (size_t) (b[3] - b[2]);     // plane pitch, elements
+    const unsigned b_planes = pair ? 1u : 2u;            // pair: a CTA loads the real or the imaginary plane of B
+    for (int k = 0; k < 4; ++k) {
+        if (k < 2) {
+            rc = a_mn ? make_map_mn(&maps[k], a[k], M, K) : make_map(&maps[k], a[k], M, K);
+            if (rc != CNB_OK) return rc;
+            rc = b_mn ? make_map_mn(&maps[4 + k], b[k], N, K) : make_map(&maps[4 + k], b[k], N, K);
+            if (rc != CNB_OK) return rc;
+        } else {
+            rc = a_mn ? make_map16_mn(&maps[k], a[k], M, K, npa, 2u) : make_map16(&maps[k], a[k], M, K, npa, 2u);
+            if (rc != CNB_OK) return rc;
+            rc = b_mn ? make_map16_mn(&maps[4 + k], b[k], N, K, npb, b_planes) : make_map16(&maps[4 + k], b[k], N, K, npb, b_planes);
+            if (rc != CNB_OK) return rc;
+        }
     }
-    int whole_per_cta = 0;
-    int clear_from_row = 0;                              // rows of D below this one are only ever stored whole
-    if (lead_whole) {
-        ctas = sms;
-        whole_per_cta = tiles / sms;
-        const long rest = (long) (tiles - whole_per_cta * sms) * k_blocks;
-        upc = (rest + ctas - 1) / ctas;
-        clear_from_row = (whole_per_cta * sms / ((N + BN - 1) / BN)) * BM;
-    }
-    // Few tiles (small batches): a cluster of 2, 4 or 8 CTAs takes one tile, every CTA a slice of K, and
-    // the partial tiles are summed through distributed shared memory: no atomics, no cleared output,
-    // a fixed summation order.
-    // Worth it while a stream-K run would be short (<= 48 k-blocks): with long runs the atomics are
-    // amortised and using every SM wins over the clusters' rounded-down CTA count.
-    int cluster = 1;
-    if (!whole_tiles && !lead_whole && upc <= 48) {
-        for (int c = 8; c >= 2; c >>= 1)
-            if ((long) tiles * c <= sms && k_blocks / c >= 4) { cluster = c; break; }
-    }
-    if (cluster > 1) { ctas = (long) tiles * cluster; upc = 0; }
-    bool splits_tiles = cluster == 1 && (lead_whole ? upc > 0 : (segments > 0 || (upc % k_blocks) != 0));
-    if (splits_tiles && !accumulate) {
+    if (q.splits_tiles && !accumulate) {
         // one launch clears both planes (they need not be adjacent or in one allocation)
         const size_t first = (size_t) clear_from_row * N;
         const size_t plane = (size_t) M * N - first;
@@ -991,8 +1161,12 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     p.whole_per_cta = whole_per_cta;
     p.segments = segments;
     p.status = ctx->d_status;
-    CNB_CUDA(cnb::launch(cgemm_tc_k, dim3((unsigned) ctas), dim3(NUM_THREADS), SMEM_BYTES, st, cluster, maps[0], maps[1], maps[2],
-                         maps[3], maps[4], maps[5], maps[6], maps[7], p));
+    if (pair)
+        CNB_CUDA(cnb::launch(cgemm_tc_k<true>, dim3((unsigned) (2 * ctas)), dim3(NUM_THREADS), SMEM_BYTES, st, 2, maps[0], maps[1],
+                             maps[2], maps[3], maps[4], maps[5], maps[6], maps[7], p));
+    else
+        CNB_CUDA(cnb::launch(cgemm_tc_k<false>, dim3((unsigned) ctas), dim3(NUM_THREADS), SMEM_BYTES, st, cluster, maps[0], maps[1],
+                             maps[2], maps[3], maps[4], maps[5], maps[6], maps[7], p));
     CNB_LAUNCH_CHECK("cgemm_tc");
     return CNB_OK;
 }
