@@ -25,6 +25,13 @@
 // per k-block and accumulator: 2 TF32 MMAs (k-steps of 8) + 2 BF16 MMAs (one k-step of 16).
 // Each CTA issues its own plain TMA tile loads; their zero fill handles every M/N/K edge.
 //
+// CTA pairs.  The large launches (cgemm_tc_k<true>) give a 256 x 128 tile to a cluster of two CTAs that work as
+// one tensor core (cta_group::2): each CTA stages its own 128 rows of A and one half of the stacked B operand
+// (B_re rows in the first CTA, B_im rows in the second), i.e. 48 KB per k-block instead of 64 KB, four stages
+// instead of three.  The first CTA issues every MMA (M = 256); both CTAs load, drain their own accumulator rows
+// and write them out.  Completion bytes of both CTAs' loads go to the first CTA's full barrier; its
+// tcgen05.commit arrives on the stage's empty barrier (and on the "accumulators ready" barrier) of both.
+//
 // Scheduling.  Stream-K: the (tile, k-block) work units are cut into equal consecutive runs, one
 // per CTA and one CTA per SM, so every SM finishes together whatever the tile count; a tile whose
 // k-range is shared by several CTAs is summed with fp32 atomics into a pre-zeroed output.
