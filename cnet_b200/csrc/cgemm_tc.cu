@@ -79,7 +79,7 @@ struct TcParams {
     int whole_per_cta;        // > 0: every CTA first takes that many whole tiles, then its run of the remaining units
     int segments;             // > 0: CTA r takes k-segment r / tiles of tile r % tiles (units_per_cta k-blocks each)
     int* status;
-    // The pair form (cgemm_tc_k<true>) reads none of cluster / segments: its cluster is the CTA pair of one tile.
+    // The pair form (cgemm_tc_k<true>): cluster = K slices per tile, each slice a CTA pair (cluster of 2 * cluster CTAs).
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
@@ -273,9 +273,10 @@ __device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint
 }
 
 // arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
-__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+// (the pair = cluster ranks first_rank and first_rank + 1)
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar, uint32_t first_rank) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(bar), "h"((unsigned short) 3) : "memory");
+                 ::"r"(bar), "h"((unsigned short) (3u << first_rank)) : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -355,9 +356,11 @@ __device__ __forceinline__ float4 ld_peer(uint32_t local_addr, uint32_t rank) {
 // partial tiles (its own and its peers', through distributed shared memory), adds residual / old D and
 // stores.  Two 16-byte chunks per thread and round: every load of both (2 * CL peer loads per plane pair,
 // residual, old D) is issued before the first sum, so a round costs one round trip.  Fixed summation order.
+// The CL partial tiles sit in the CTAs of cluster rank peer0 + c * peer_step (one CTA per tile: 0 and 1; CTA pairs:
+// this CTA's rank in its pair and 2: the peers are the CTAs that hold the same 128 rows).
 template <int CL>
 __device__ __forceinline__ void cluster_reduce(const TcParams& p, uint32_t smem_base, uint32_t crank, int m0, int n0,
-                                               int et, bool vec_ok) {
+                                               int et, bool vec_ok, uint32_t peer0, uint32_t peer_step) {
     constexpr int ROWS = BM / CL;
     constexpr int U = CL <= 4 ? 2 : 1;                   // chunks per thread and round
     for (int base = et; base < ROWS * 32; base += 128 * U) {
@@ -377,7 +380,10 @@ __device__ __forceinline__ void cluster_reduce(const TcParams& p, uint32_t smem_
             if (!live[u]) continue;
             const uint32_t local = smem_base + 4u * (uint32_t) part_off(r, ch);
 #pragma unroll
-            for (int c = 0; c < CL; ++c) { xr[u][c] = ld_peer(local, (uint32_t) c); xi[u][c] = ld_peer(local + PART_PLANE_BYTES, (uint32_t) c); }
+            for (int c = 0; c < CL; ++c) {
+                const uint32_t peer = peer0 + (uint32_t) c * peer_step;
+                xr[u][c] = ld_peer(local, peer); xi[u][c] = ld_peer(local + PART_PLANE_BYTES, peer);
+            }
             if (vec_ok) {
                 if (p.r_re) { vr[u] = ld_global_now(p.r_re + o[u]); vi[u] = ld_global_now(p.r_im + o[u]); }
                 if (p.accumulate) {
@@ -448,7 +454,11 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
     const long total_units = (long) tiles_m * tiles_n * k_blocks;
     // In the pair form the two CTAs of a cluster work through the same units (each on its own 128 rows of the
     // 256-row tile): "CTA" below is the pair.
-    const uint32_t prank = PAIR ? cluster_rank() : 0u;
+    // Cluster ranks: one CTA per tile: rank = K slice (cluster split-K) or none; pairs: rank = 2 * K slice + place in
+    // the pair.
+    const uint32_t rank_all = (PAIR || p.cluster > 1) ? cluster_rank() : 0u;
+    const uint32_t prank = PAIR ? (rank_all & 1u) : 0u;
+    const uint32_t lead_rank = rank_all & ~1u;           // pairs: the pair's first CTA
     const long cta_idx = PAIR ? (long) (blockIdx.x >> 1) : (long) blockIdx.x;
     const long cta_cnt = PAIR ? (long) (gridDim.x >> 1) : (long) gridDim.x;
     const int row_off = PAIR ? (int) prank * BM : 0;
@@ -474,10 +484,11 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         u_end = min(u_begin + p.units_per_cta, (tile + 1) * k_blocks);
         if (u_begin > u_end) u_begin = u_end;
     }
-    const bool split_cluster = !PAIR && p.cluster > 1;
-    const uint32_t crank = split_cluster ? cluster_rank() : 0;
-    if (split_cluster) {                                 // one tile per cluster, an even slice of its k-blocks per CTA
-        const long tile = blockIdx.x / p.cluster;
+    const bool split_cluster = p.cluster > 1;
+    const uint32_t crank = split_cluster ? (PAIR ? rank_all >> 1 : rank_all) : 0;     // the K slice
+    const int cluster_ctas = p.cluster * (PAIR ? 2 : 1);
+    if (split_cluster) {                                 // one tile per cluster, an even slice of its k-blocks per CTA (pair)
+        const long tile = blockIdx.x / cluster_ctas;
         u_begin = tile * k_blocks + (long) k_blocks * crank / p.cluster;
         u_end = tile * k_blocks + (long) k_blocks * (crank + 1) / p.cluster;
     }
@@ -539,7 +550,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                 if constexpr (PAIR) {
                     // Both CTAs fill their own stage; all completion bytes go to the full barrier of the pair's
                     // first CTA, which expects the bytes of both.
-                    const uint32_t bar = map_to_rank(full_bar(s), 0);
+                    const uint32_t bar = map_to_rank(full_bar(s), lead_rank);
                     if (prank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {        // this CTA's 128 rows of A: hi_re, hi_im, h16 pair, l16 pair
@@ -633,7 +644,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                             umma2_tf32(tmem_base, adesc(0), b_h, idesc, 1u);
                             umma2_tf32(tmem_base + 256, adesc(1), b_h, idesc, 1u);
                         }
-                        umma2_commit_both(empty_bar(s));     // the stage is free in both CTAs once these MMAs have read it
+                        umma2_commit_both(empty_bar(s), lead_rank);  // the stage is free in both CTAs once these MMAs have read it
                         continue;
                     }
                     {
@@ -668,7 +679,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                     }
                     umma_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                 }
-                if (ok) { if constexpr (PAIR) umma2_commit_both(acc_full); else umma_commit(acc_full); }
+                if (ok) { if constexpr (PAIR) umma2_commit_both(acc_full, lead_rank); else umma_commit(acc_full); }
                 CNB_GSTAMP(3, true);
                 u += kb1 - kb0;
             }
@@ -687,8 +698,8 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         if (split_cluster) {
             // the whole k-slice is one segment; its partial sums go to shared memory for the cluster reduction
             {
-                const int tile = blockIdx.x / p.cluster, rows_per = BM / p.cluster;
-                const int row = (tile / tiles_n) * BM + (int) crank * rows_per + et, n0 = (tile % tiles_n) * BN;
+                const int tile = blockIdx.x / cluster_ctas, rows_per = BM / p.cluster;
+                const int row = (tile / tiles_n) * TILE_M + row_off + (int) crank * rows_per + et, n0 = (tile % tiles_n) * BN;
                 if (et < rows_per) {                     // the band of rows this CTA will write out
                     if (p.r_re) prefetch_tile_rows(p, p.r_re, p.r_im, row, n0);
                     if (p.accumulate) prefetch_tile_rows(p, p.d_re, p.d_im, row, n0);
@@ -799,7 +810,7 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
                 }
                 epi_bar_sync();
                 if (c0 + 32 == BN && et == 0) {
-                    if constexpr (PAIR) mbar_arrive_cluster(map_to_rank(acc_empty, 0));   // the first CTA's MMA thread waits for both
+                    if constexpr (PAIR) mbar_arrive_cluster(map_to_rank(acc_empty, lead_rank));   // the first CTA's MMA thread waits for both
                     else mbar_arrive(acc_empty);
                 }
                 // coalesced write-out: each warp instruction covers 4 rows x 128 contiguous bytes
@@ -849,10 +860,10 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if constexpr (PAIR) {
+    if (PAIR && !split_cluster) {
         // No CTA of the pair leaves (or frees tensor memory) while the other may still signal its barriers, read its
         // shared memory (the first CTA's MMAs read the peer's operand stages) or write its tensor memory.  Every thread
-        // reaches this barrier, also after a bounded wait gave up.
+        // reaches this barrier, also after a bounded wait gave up.  (With a K split the two barriers below do that.)
         cluster_sync();
     }
     if (split_cluster) {
@@ -860,16 +871,17 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         cluster_sync();                                  // all partial tiles are in shared memory
         CNB_GSTAMP(6, threadIdx.x == 64);
         if (warp >= 2 && !*abort_flag) {
-            const int tile = blockIdx.x / p.cluster;
-            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int tile = blockIdx.x / cluster_ctas;
+            const int m0 = (tile / tiles_n) * TILE_M + row_off, n0 = (tile % tiles_n) * BN;
             const int et = (warp - 2) * 32 + lane;
+            const uint32_t peer0 = PAIR ? prank : 0u, peer_step = PAIR ? 2u : 1u;
             const bool vec_ok = (p.N % 4 == 0) &&
                 ((reinterpret_cast<uintptr_t>(p.d_re) | reinterpret_cast<uintptr_t>(p.d_im) |
                   reinterpret_cast<uintptr_t>(p.r_re) | reinterpret_cast<uintptr_t>(p.r_im)) & 15) == 0;
             switch (p.cluster) {
-                case 2: cluster_reduce<2>(p, smem_base, crank, m0, n0, et, vec_ok); break;
-                case 4: cluster_reduce<4>(p, smem_base, crank, m0, n0, et, vec_ok); break;
-                default: cluster_reduce<8>(p, smem_base, crank, m0, n0, et, vec_ok); break;
+                case 2: cluster_reduce<2>(p, smem_base, crank, m0, n0, et, vec_ok, peer0, peer_step); break;
+                case 4: cluster_reduce<4>(p, smem_base, crank, m0, n0, et, vec_ok, peer0, peer_step); break;
+                default: cluster_reduce<8>(p, smem_base, crank, m0, n0, et, vec_ok, peer0, peer_step); break;
             }
         }
         CNB_GSTAMP(7, threadIdx.x == 64);
@@ -1078,10 +1090,12 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         const long total = (long) tiles * k_blocks;
         const long min_units = 8;                            // do not split below 8 k-blocks per CTA
         const int all = pair ? ctx->sm_count / 2 : ctx->sm_count;
-        // pairs while SMs are set aside: every SM taken by the other kernel may cost a pair its partner (a pair
-        // needs both SMs of a TPC), so count each of them twice
+        // Pairs under an SM limit: a pair needs both SMs of a TPC.  A few SMs set aside for a collective's kernel may
+        // each cost a pair its partner, so they are counted twice (6 set aside: 68 pairs); a limit that halves the
+        // device for two products side by side leaves half the pairs, less that margin.
+        const int set_aside = ctx->sm_count - ctx->gemm_cta_limit;
         const int sms = ctx->gemm_cta_limit > 0
-            ? std::min(pair ? std::max(1, ctx->gemm_cta_limit - ctx->sm_count / 2) : ctx->gemm_cta_limit, all) : all;
+            ? std::min(pair ? std::max(1, (ctx->gemm_cta_limit - std::min(set_aside, 8)) / 2) : ctx->gemm_cta_limit, all) : all;
         const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
         const bool whole_tiles = (tiles >= all * 4 && ctx->gemm_cta_limit <= 0 && k_blocks <= 256) || full_wave;
         const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
@@ -1118,7 +1132,9 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         // amortised and using every SM wins over the clusters' rounded-down CTA count.
         q.cluster = 1;
         if (!whole_tiles && !lead_whole && upc <= 48) {
-            for (int c = 8; c >= 2; c >>= 1)
+            // pairs: two slices at most (clusters of 8 CTAs do not all fit a GPC side by side: measured 0.043 ms
+            // against 0.025 at 512 x 1024 x 1024)
+            for (int c = pair ? 2 : 8; c >= 2; c >>= 1)
                 if ((long) tiles * c <= sms && k_blocks / c >= 4) { q.cluster = c; break; }
         }
         if (q.cluster > 1) { ctas = (long) tiles * q.cluster; upc = 0; }
@@ -1127,14 +1143,18 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         return q;
     };
     // The pair form (two CTAs, cta_group::2, per 256-row tile: each CTA stages half of the B operand, so a k-block
-    // costs 48 KB of shared-memory fill per CTA instead of 64 KB) takes the large launches: no SMs set aside, at
-    // least one whole pair tile of rows, K <= 4096, and a schedule that is not the K-split cluster.
+    // costs 48 KB of shared-memory fill per CTA instead of 64 KB): at least one whole pair tile of rows and K <= 4096;
+    // with few tiles, a cluster of 2 or 4 pairs per tile, each pair a slice of K.
     static const bool pair_allowed = [] { const char* e = getenv("CNB_GEMM_PAIR"); return !(e && e[0] == '0'); }();
     // beside a collective (SMs set aside): measured 2.145 -> 2.115 ms per step at 2 GPUs; CNB_GEMM_PAIR_DP=0 turns it off
     static const bool pair_beside_collective = [] { const char* e = getenv("CNB_GEMM_PAIR_DP"); return !(e && e[0] == '0'); }();
     bool pair = pair_allowed && (ctx->gemm_cta_limit <= 0 || pair_beside_collective) && M >= 2 * BM && k_blocks <= 256;
     Plan q = plan(pair);
-    if (pair && (q.cluster > 1 || q.segments > 0)) { pair = false; q = plan(false); }
+    if (pair && q.segments > 0) { pair = false; q = plan(false); }
+    if (pair && q.cluster > 1) {                         // K-split clusters: pairs only if they fill as many SMs
+        const Plan single = plan(false);
+        if (single.ctas > 2 * q.ctas) { pair = false; q = single; }
+    }
     const long ctas = q.ctas, upc = q.upc;
     const int whole_per_cta = q.whole_per_cta, clear_from_row = q.clear_from_row, cluster = q.cluster, segments = q.segments;
 
@@ -1174,7 +1194,7 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     p.segments = segments;
     p.status = ctx->d_status;
     if (pair)
-        CNB_CUDA(cnb::launch(cgemm_tc_k<true>, dim3((unsigned) (2 * ctas)), dim3(NUM_THREADS), SMEM_BYTES, st, 2, maps[0], maps[1],
+        CNB_CUDA(cnb::launch(cgemm_tc_k<true>, dim3((unsigned) (2 * ctas)), dim3(NUM_THREADS), SMEM_BYTES, st, 2 * cluster, maps[0], maps[1],
                              maps[2], maps[3], maps[4], maps[5], maps[6], maps[7], p));
     else
         CNB_CUDA(cnb::launch(cgemm_tc_k<false>, dim3((unsigned) ctas), dim3(NUM_THREADS), SMEM_BYTES, st, cluster, maps[0], maps[1],
