@@ -92,3 +92,32 @@ def test_weight_gradients_add_over_the_batch_at_full_size():
         num = np.sqrt(((got[0] - full[k][0]) ** 2).sum() + ((got[1] - full[k][1]) ** 2).sum())
         den = np.sqrt((full[k][0] ** 2).sum() + (full[k][1] ** 2).sum())
         assert num / den < 1e-4, k
+
+
+@pytest.mark.parametrize("B", [512, 1024])
+def test_small_batch_step_runs_at_the_expected_order_of_speed(B):
+    """Schedules of the tensor-core products are chosen per launch from the shape and the SMs a launch may fill; a
+    wrong count there (one CTA pair for a whole product) passes every numerical test and costs a factor of nine.
+    A step of the 8-block stack takes 0.8 ms at 512 rows and 1.2 ms at 1024: a loose bound catches the factor."""
+    import time
+    import torch
+    kw = dict(n=1024, blocks=8, m=10)
+    net = Net()
+    spec = configs.build_mixer(net, **kw)
+    for uid, (re, im) in configs.init_weights(spec, 0).items():
+        net.set_values(uid, re, im)
+    net.allocate(B)
+    (xr, xi), labels = configs.make_batch(spec, B, 0)
+    for _ in range(3):
+        net.run_batch(spec.main, x=(xr, xi), labels=labels)
+        net.update(0.01, B)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps = 10
+    for _ in range(steps):
+        net.run_batch(spec.main, x=(xr, xi), labels=labels)
+        net.update(0.01, B)
+    torch.cuda.synchronize()
+    ms = 1e3 * (time.perf_counter() - t0) / steps
+    # run_batch also uploads the batch and reads the losses back (a few hundred microseconds)
+    assert ms < 4.0, "a %d-row step took %.2f ms" % (B, ms)
