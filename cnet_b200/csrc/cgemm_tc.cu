@@ -474,12 +474,12 @@ cgemm_tc_k(const __grid_constant__ CUtensorMap a_hi_re, const __grid_constant__ 
         u_begin = lead * cta_idx;
         u_end = u_begin + lead;
     }
-    if (!PAIR && p.segments > 0) {
+    if (p.segments > 0) {
         // Capped chains (K > 4096): consecutive CTAs take the SAME k-segment of consecutive tiles, so the CTAs that
         // run together read the same columns of A and B and share them through L2 (tile-major runs had every CTA
         // of a wave on its own k-range: 5.0 GB of DRAM reads for 0.8 GB of operands at 1024 x 2048 x 16384).
         const long tiles = (long) tiles_m * tiles_n;
-        const long seg = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+        const long seg = cta_idx / tiles, tile = cta_idx % tiles;
         u_begin = tile * k_blocks + seg * p.units_per_cta;
         u_end = min(u_begin + p.units_per_cta, (tile + 1) * k_blocks);
         if (u_begin > u_end) u_begin = u_end;
@@ -1142,18 +1142,16 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         return q;
     };
     // The pair form (two CTAs, cta_group::2, per 256-row tile: each CTA stages half of the B operand, so a k-block
-    // costs 48 KB of shared-memory fill per CTA instead of 64 KB): at least one whole pair tile of rows and K <= 4096;
-    // with few tiles, a cluster of 2 or 4 pairs per tile, each pair a slice of K.
+    // costs 48 KB of shared-memory fill per CTA instead of 64 KB): at least one whole pair tile of rows; with few
+    // tiles, a cluster of two pairs per tile, each pair a slice of K.
     static const bool pair_allowed = [] { const char* e = getenv("CNB_GEMM_PAIR"); return !(e && e[0] == '0'); }();
     // beside a collective (SMs set aside): measured 2.145 -> 2.115 ms per step at 2 GPUs; CNB_GEMM_PAIR_DP=0 turns it off
     static const bool pair_beside_collective = [] { const char* e = getenv("CNB_GEMM_PAIR_DP"); return !(e && e[0] == '0'); }();
     // not under a limit that halves the device (two products side by side at small batches: measured 1.25 -> 1.31 ms
     // per step at 4 GPUs with pairs there)
     const bool small_reserve = ctx->gemm_cta_limit > 0 && ctx->sm_count - ctx->gemm_cta_limit <= 16;
-    bool pair = pair_allowed && (ctx->gemm_cta_limit <= 0 || (pair_beside_collective && small_reserve)) && M >= 2 * BM &&
-                k_blocks <= 256;
+    bool pair = pair_allowed && (ctx->gemm_cta_limit <= 0 || (pair_beside_collective && small_reserve)) && M >= 2 * BM;
     Plan q = plan(pair);
-    if (pair && q.segments > 0) { pair = false; q = plan(false); }
     if (pair && q.cluster > 1) {                         // K-split clusters: pairs only if they fill as many SMs
         const Plan single = plan(false);
         if (single.ctas > 2 * q.ctas) { pair = false; q = single; }
