@@ -1092,9 +1092,13 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         const int all = pair ? ctx->sm_count / 2 : ctx->sm_count;
         // Pairs under an SM limit (a few SMs set aside for a collective's kernel): a pair needs both SMs of a TPC and
         // each SM set aside may cost a pair its partner, so they are counted twice (6 set aside: 68 pairs).
+        // A limit of exactly half the device (two products side by side, no collective) leaves half the pairs, less
+        // a margin of 4.
         const int set_aside = ctx->sm_count - ctx->gemm_cta_limit;
+        const bool halved = ctx->gemm_cta_limit * 2 == ctx->sm_count;
+        const int pairs_left = halved ? ctx->gemm_cta_limit / 2 - 4 : (ctx->gemm_cta_limit - set_aside) / 2;
         const int sms = ctx->gemm_cta_limit > 0
-            ? std::min(pair ? std::max(1, (ctx->gemm_cta_limit - set_aside) / 2) : ctx->gemm_cta_limit, all) : all;
+            ? std::min(pair ? std::max(1, pairs_left) : ctx->gemm_cta_limit, all) : all;
         const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
         const bool whole_tiles = (tiles >= all * 4 && ctx->gemm_cta_limit <= 0 && k_blocks <= 256) || full_wave;
         const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
@@ -1149,7 +1153,8 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     static const bool pair_beside_collective = [] { const char* e = getenv("CNB_GEMM_PAIR_DP"); return !(e && e[0] == '0'); }();
     // not under a limit that halves the device (two products side by side at small batches: measured 1.25 -> 1.31 ms
     // per step at 4 GPUs with pairs there)
-    const bool small_reserve = ctx->gemm_cta_limit > 0 && ctx->sm_count - ctx->gemm_cta_limit <= 16;
+    const bool small_reserve = ctx->gemm_cta_limit > 0 &&
+        (ctx->sm_count - ctx->gemm_cta_limit <= 16 || ctx->gemm_cta_limit * 2 == ctx->sm_count);   // or exactly half, no collective
     bool pair = pair_allowed && (ctx->gemm_cta_limit <= 0 || (pair_beside_collective && small_reserve)) && M >= 2 * BM;
     Plan q = plan(pair);
     if (pair && q.cluster > 1) {                         // K-split clusters: pairs only if they fill as many SMs
