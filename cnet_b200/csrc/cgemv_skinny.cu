@@ -31,7 +31,8 @@ __device__ __forceinline__ void ldv(const float* p, float (&v)[1]) { v[0] = __ld
 template <int OT, int W>
 __global__ void __launch_bounds__(512)
 skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const float* __restrict__ wr,
-             const float* __restrict__ wi, float* __restrict__ yr, float* __restrict__ yi, int B, int in, int out) {
+             const float* __restrict__ wi, float* __restrict__ yr, float* __restrict__ yi, int B, int in, int out,
+             int row_warps) {
     cnb_pdl_enter();
     extern __shared__ __align__(16) float sw[];          // [out][in] re, then [out][in] im
     float* swr = sw;
@@ -46,9 +47,12 @@ skinny_fwd_k(const float* __restrict__ xr, const float* __restrict__ xi, const f
         for (int e = threadIdx.x; e < total; e += blockDim.x) { swr[e] = wr[e]; swi[e] = wi[e]; }
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31;
-    const long warp = ((long) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const long nwarps = ((long) gridDim.x * blockDim.x) >> 5;
+    // All warps of the CTA stage W; the first row_warps of them walk rows (small batches: few rows per SM, but the
+    // staging still wants the whole CTA: with 4 warps it was 20 of a 64-row launch's 21 us).
+    const int lane = threadIdx.x & 31, warp_in_cta = threadIdx.x >> 5;
+    if (warp_in_cta >= row_warps) return;
+    const long warp = (long) blockIdx.x * row_warps + warp_in_cta;
+    const long nwarps = (long) gridDim.x * row_warps;
     const int groups = in / W;
     for (long b0 = warp * 2; b0 < B; b0 += nwarps * 2) {
         const bool two = b0 + 1 < B;
@@ -288,9 +292,9 @@ int skinny_fwd(cnb_ctx* ctx, const float* xr, const float* xi, const float* wr, 
     while (warps > 4 && pairs < (long) usable_sms(ctx) * warps / 2) warps /= 2;
     const long blocks = (pairs + warps - 1) / warps;
     const int grid = (int) std::max<long>(1, std::min<long>(blocks, usable_sms(ctx)));
-    const int threads = warps * 32;
-    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out);
-    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out);
+    const int threads = 512;                             // every CTA stages W with 16 warps; `warps` of them take rows
+    if (vec) CNB_SKINNY_DISPATCH(skinny_fwd_k, 4, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out, warps);
+    else CNB_SKINNY_DISPATCH(skinny_fwd_k, 1, dim3(grid), dim3(threads), smem, st, 1, xr, xi, wr, wi, yr, yi, B, in, out, warps);
     CNB_LAUNCH_CHECK("skinny_fwd");
     return CNB_OK;
 }
