@@ -100,3 +100,25 @@ def test_reference_style_user_layer_compiles_and_is_refused(built_lib, tmp_path)
                     "-o", exe, "-L" + libdir, "-l:libcnet_b200.so", "-Wl,-rpath," + libdir], check=True, env=env)
     r = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout
+
+
+def test_struct_layouts_of_the_python_binding_match_the_header(tmp_path):
+    """cnb_split_span is passed by pointer through ctypes: size and field offsets of the Python mirror must be
+    what a C compiler makes of include/cnet_b200.h."""
+    import ctypes as C
+    import subprocess
+    from cnet_b200 import lib as L
+    here = os.path.dirname(os.path.abspath(__file__))
+    src = tmp_path / "layout.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "cnet_b200.h"\n'
+        'int main(void) {\n'
+        '  printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(cnb_split_span), offsetof(cnb_split_span, begin), offsetof(cnb_split_span, count),\n'
+        '         offsetof(cnb_split_span, hi), offsetof(cnb_split_span, h16), offsetof(cnb_split_span, l16));\n'
+        '  return 0;\n}\n')
+    exe = str(tmp_path / "layout")
+    subprocess.run(["gcc", "-I", os.path.join(here, "..", "include"), "-I/usr/local/cuda/include", str(src), "-o", exe], check=True)
+    out = subprocess.run([exe], stdout=subprocess.PIPE, text=True, check=True).stdout.split()
+    S = L.SplitSpan
+    want = [C.sizeof(S), S.begin.offset, S.count.offset, S.hi.offset, S.h16.offset, S.l16.offset]
+    assert [int(v) for v in out] == want
