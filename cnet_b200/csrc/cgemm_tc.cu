@@ -1036,42 +1036,11 @@ __global__ void zero_pair_k(float* __restrict__ a, float* __restrict__ b, size_t
     }
 }
 
-}  // namespace
+// The schedule of one product: which form (one CTA per tile or CTA pairs), how many CTAs, how the (tile, k-block)
+// units are dealt.  Host arithmetic only (also reachable as cnb_gemm_schedule, for tests that need no GPU).
+struct Schedule { bool pair; long ctas, upc; int whole_per_cta, clear_from_row, cluster, segments; bool splits_tiles; };
 
-namespace cnb {
-
-bool cgemm_tc_shape_ok(int M, int N, int K) {
-    // TMA needs a 16-byte row pitch (8 bf16); small or skinny problems are faster on the SIMT tiles
-    return (K % 8 == 0) && K >= 32 && M >= 64 && N >= 64;
-}
-
-size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
-    return 4 * ((size_t) M * K + (size_t) N * K) * sizeof(float) + 4096;
-}
-
-void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* sp, size_t np, size_t n, cudaStream_t st) {
-    size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
-    cnb::launch(split_k, dim3((unsigned) (blocks < cap ? blocks : cap)), dim3(256), 0, st, 1, s0, s1, sp, np, n);
-}
-
-// The GEMM proper on operands that are already split: a[4] / b[4] = the four slots of a split buffer (hi_re,
-// hi_im, [h16_re ; h16_im], [l16_re ; l16_im]; slot q+1 follows slot q at the plane pitch), elements stored
-// [rows, K] (major = 0) or [K, rows] (major = 1, needs rows % 64 == 0).
-int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
-                      const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
-                      int accumulate, cudaStream_t st) {
-    static bool attr_set[64] = {};                       // the attribute is per device
-    if (!attr_set[ctx->device & 63]) {
-        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        attr_set[ctx->device & 63] = true;
-    }
-    if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
-        return set_error(CNB_ERR_ARG, "cgemm_tc: misaligned output");
-    if ((a_mn && M % 64) || (b_mn && N % 64))
-        return set_error(CNB_ERR_ARG, "cgemm_tc: an MN-major operand needs a multiple of 64 rows");
-    if ((!a_mn && K % 8) || (!b_mn && K % 8))
-        return set_error(CNB_ERR_ARG, "cgemm_tc: a K-major operand needs K %% 8 == 0");
+Schedule choose_schedule(int M, int N, int K, int accumulate, int sm_count, int sm_limit) {
     // Schedule, by tile count ("CTA" = one CTA, or the CTA pair of a 256-row tile; sms = how many of them this launch
     // may fill: leaving a few SMs free (gemm_cta_limit) lets a concurrent collective's kernels run beside the GEMM):
     //  * tiles >= 4 x SMs, or one nearly full wave of one-tile CTAs when D is not read: whole tiles, grid =
@@ -1089,18 +1058,18 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
         const int tiles = ((M + tile_m - 1) / tile_m) * ((N + BN - 1) / BN);
         const long total = (long) tiles * k_blocks;
         const long min_units = 8;                            // do not split below 8 k-blocks per CTA
-        const int all = pair ? ctx->sm_count / 2 : ctx->sm_count;
+        const int all = pair ? sm_count / 2 : sm_count;
         // Pairs under an SM limit (a few SMs set aside for a collective's kernel): a pair needs both SMs of a TPC and
         // each SM set aside may cost a pair its partner, so they are counted twice (6 set aside: 68 pairs).
         // A limit of exactly half the device (two products side by side, no collective) leaves half the pairs, less
         // a margin of 4.
-        const int set_aside = ctx->sm_count - ctx->gemm_cta_limit;
-        const bool halved = ctx->gemm_cta_limit * 2 == ctx->sm_count;
-        const int pairs_left = halved ? ctx->gemm_cta_limit / 2 - 4 : (ctx->gemm_cta_limit - set_aside) / 2;
-        const int sms = ctx->gemm_cta_limit > 0
-            ? std::min(pair ? std::max(1, pairs_left) : ctx->gemm_cta_limit, all) : all;
+        const int set_aside = sm_count - sm_limit;
+        const bool halved = sm_limit * 2 == sm_count;
+        const int pairs_left = halved ? sm_limit / 2 - 4 : (sm_limit - set_aside) / 2;
+        const int sms = sm_limit > 0
+            ? std::min(pair ? std::max(1, pairs_left) : sm_limit, all) : all;
         const bool full_wave = !accumulate && tiles <= sms && (long) tiles * 100 >= (long) sms * 85 && k_blocks <= 256;
-        const bool whole_tiles = (tiles >= all * 4 && ctx->gemm_cta_limit <= 0 && k_blocks <= 256) || full_wave;
+        const bool whole_tiles = (tiles >= all * 4 && sm_limit <= 0 && k_blocks <= 256) || full_wave;
         const bool lead_whole = !whole_tiles && tiles > sms && k_blocks <= 256;
         long ctas = std::min<long>(sms, std::max<long>(1, total / min_units));
         if (whole_tiles) ctas = tiles;                        // many tiles: whole tiles, no atomics
@@ -1153,14 +1122,58 @@ int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const flo
     static const bool pair_beside_collective = [] { const char* e = getenv("CNB_GEMM_PAIR_DP"); return !(e && e[0] == '0'); }();
     // not under a limit that halves the device (two products side by side at small batches: measured 1.25 -> 1.31 ms
     // per step at 4 GPUs with pairs there)
-    const bool small_reserve = ctx->gemm_cta_limit > 0 &&
-        (ctx->sm_count - ctx->gemm_cta_limit <= 16 || ctx->gemm_cta_limit * 2 == ctx->sm_count);   // or exactly half, no collective
-    bool pair = pair_allowed && (ctx->gemm_cta_limit <= 0 || (pair_beside_collective && small_reserve)) && M >= 2 * BM;
+    const bool small_reserve = sm_limit > 0 &&
+        (sm_count - sm_limit <= 16 || sm_limit * 2 == sm_count);   // or exactly half, no collective
+    bool pair = pair_allowed && (sm_limit <= 0 || (pair_beside_collective && small_reserve)) && M >= 2 * BM;
     Plan q = plan(pair);
     if (pair && q.cluster > 1) {                         // K-split clusters: pairs only if they fill as many SMs
         const Plan single = plan(false);
         if (single.ctas > 2 * q.ctas) { pair = false; q = single; }
     }
+    Schedule r;
+    r.pair = pair; r.ctas = q.ctas; r.upc = q.upc; r.whole_per_cta = q.whole_per_cta; r.clear_from_row = q.clear_from_row;
+    r.cluster = q.cluster; r.segments = q.segments; r.splits_tiles = q.splits_tiles;
+    return r;
+}
+
+}  // namespace
+
+namespace cnb {
+
+bool cgemm_tc_shape_ok(int M, int N, int K) {
+    // TMA needs a 16-byte row pitch (8 bf16); small or skinny problems are faster on the SIMT tiles
+    return (K % 8 == 0) && K >= 32 && M >= 64 && N >= 64;
+}
+
+size_t cgemm_tc_workspace_bytes(int M, int N, int K) {
+    return 4 * ((size_t) M * K + (size_t) N * K) * sizeof(float) + 4096;
+}
+
+void split_launch(cnb_ctx* ctx, const float* s0, const float* s1, float* sp, size_t np, size_t n, cudaStream_t st) {
+    size_t blocks = (n / 4 + 255) / 256 + 1, cap = (size_t) ctx->sm_count * 16;
+    cnb::launch(split_k, dim3((unsigned) (blocks < cap ? blocks : cap)), dim3(256), 0, st, 1, s0, s1, sp, np, n);
+}
+
+// The GEMM proper on operands that are already split: a[4] / b[4] = the four slots of a split buffer (hi_re,
+// hi_im, [h16_re ; h16_im], [l16_re ; l16_im]; slot q+1 follows slot q at the plane pitch), elements stored
+// [rows, K] (major = 0) or [K, rows] (major = 1, needs rows % 64 == 0).
+int cgemm_tc_presplit(cnb_ctx* ctx, const float* const a[4], int a_mn, const float* const b[4], int b_mn, int conjB,
+                      const float* r_re, const float* r_im, float* d_re, float* d_im, int M, int N, int K,
+                      int accumulate, cudaStream_t st) {
+    static bool attr_set[64] = {};                       // the attribute is per device
+    if (!attr_set[ctx->device & 63]) {
+        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        CNB_CUDA(cudaFuncSetAttribute(cgemm_tc_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set[ctx->device & 63] = true;
+    }
+    if ((reinterpret_cast<uintptr_t>(d_re) | reinterpret_cast<uintptr_t>(d_im)) & 3)
+        return set_error(CNB_ERR_ARG, "cgemm_tc: misaligned output");
+    if ((a_mn && M % 64) || (b_mn && N % 64))
+        return set_error(CNB_ERR_ARG, "cgemm_tc: an MN-major operand needs a multiple of 64 rows");
+    if ((!a_mn && K % 8) || (!b_mn && K % 8))
+        return set_error(CNB_ERR_ARG, "cgemm_tc: a K-major operand needs K %% 8 == 0");
+    const Schedule q = choose_schedule(M, N, K, accumulate, ctx->sm_count, ctx->gemm_cta_limit);
+    const bool pair = q.pair;
     const long ctas = q.ctas, upc = q.upc;
     const int whole_per_cta = q.whole_per_cta, clear_from_row = q.clear_from_row, cluster = q.cluster, segments = q.segments;
 
@@ -1260,3 +1273,18 @@ int cgemm_tc_nt(cnb_ctx* ctx, const float* a_re, const float* a_im, const float*
 }
 
 }  // namespace cnb
+
+extern "C" int cnb_gemm_schedule(int M, int N, int K, int accumulate, int sm_count, int sm_limit, int* out8) {
+    if (!out8 || M <= 0 || N <= 0 || K <= 0 || sm_count <= 0)
+        return cnb::set_error(CNB_ERR_ARG, "cnb_gemm_schedule: M=%d N=%d K=%d sm_count=%d", M, N, K, sm_count);
+    const Schedule q = choose_schedule(M, N, K, accumulate, sm_count, sm_limit);
+    out8[0] = q.pair ? 1 : 0;
+    out8[1] = (int) (q.pair ? 2 * q.ctas : q.ctas);      // CTAs of the launch
+    out8[2] = q.cluster * (q.pair ? 2 : 1);              // CTAs per cluster (1: no cluster)
+    out8[3] = (int) q.upc;
+    out8[4] = q.whole_per_cta;
+    out8[5] = q.segments;
+    out8[6] = q.splits_tiles ? 1 : 0;
+    out8[7] = q.clear_from_row;
+    return CNB_OK;
+}

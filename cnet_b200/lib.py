@@ -79,6 +79,7 @@ SIGNATURES = {
     "cnb_embed_fwd": (C.c_int, [_vp] + [_P] * 5 + [C.c_int] * 4 + [_vp]),
     "cnb_embed_bwd": (C.c_int, [_vp] + [_P] * 5 + [C.c_int] * 4 + [_vp]),
     "cnb_sgd_update": (C.c_int, [_vp, _P, _P, _sz, C.c_float, C.c_int, _vp]),
+    "cnb_gemm_schedule": (C.c_int, [C.c_int] * 6 + [C.POINTER(C.c_int)]),
     "cnb_sgd_update_split": (C.c_int, [_vp, _P, _P, _sz, C.c_float, C.c_int, _vp, C.c_int, _vp]),
     "cnb_launch_count": (C.c_ulonglong, []),
     # host facade

@@ -109,6 +109,12 @@ int cnb_reserve_scratch(cnb_ctx* ctx, size_t bytes);
  * np of bf16(lo_re), np of bf16(lo_im).
  * Eligible when cnb_linear_split_ok (all dims >= 64, in and out multiples of 64).  Same reference
  * call sites as cnb_linear_fwd / _bwd_x / _bwd_w above. */
+/* The schedule cnb_linear_*_split / the tensor-core products would choose for an M x N x K product on a device
+ * of sm_count SMs of which the launch may fill sm_limit (0: all): host arithmetic only, no device needed (no
+ * reference counterpart; for tests and tuning).  out8 = {CTA pairs (cta_group::2) or not, CTAs of the launch,
+ * CTAs per cluster, k-blocks per run, whole tiles per CTA before the shared remainder, k-segments per tile
+ * (capped chains), tiles summed with atomics or not, first row of the output that atomics touch}. */
+int cnb_gemm_schedule(int M, int N, int K, int accumulate, int sm_count, int sm_limit, int* out8);
 size_t cnb_split_floats(size_t n);
 int cnb_split_planes(cnb_ctx* ctx, const float* re, const float* im, size_t n, float* split, void* stream);
 int cnb_linear_split_ok(int B, int in, int out);
