@@ -120,4 +120,4 @@ def test_small_batch_step_runs_at_the_expected_order_of_speed(B):
     torch.cuda.synchronize()
     ms = 1e3 * (time.perf_counter() - t0) / steps
     # run_batch also uploads the batch and reads the losses back (a few hundred microseconds)
-    assert ms < 4.0, "a %d-row step took %.2f ms" % (B, ms)
+    assert ms < 5.0, "a %d-row step took %.2f ms" % (B, ms)
