@@ -9,7 +9,8 @@
 //     hi*hi                on the TF32 pipe (exact products), and
 //     hi*lo + lo*hi        on the BF16 pipe, from hi and lo rounded to bf16 (h16, l16).
 // The cross terms are 2^-10 of the product, so their bf16 rounding (2^-9 each factor) costs 2^-18 of the
-// product at worst, next to the 2^-20 of the dropped lo*lo term; fp32's exponent range is kept (no scaling).
+// product per cross term at worst (2^-19.5 rms for both), next to the 2^-20 of the dropped lo*lo term; fp32's
+// exponent range is kept (no scaling).
 // A BF16 MMA of depth 16 takes the time of a TF32 MMA of depth 8, so a real product costs two TF32-equivalents
 // instead of the three of the all-TF32 form, for the same operand bytes (8 per real element).
 //
