@@ -60,3 +60,17 @@ def test_bench_shapes_take_cta_pairs_on_a_whole_device(lib):
     assert s["pair"] and s["ctas"] == 128 and s["cluster_ctas"] == 4, s
     s = _schedule(lib, 1024, 1024, 1024, 1, 71)            # half a device beside a collective: no pairs
     assert not s["pair"], s
+
+
+def test_small_and_ragged_products(lib):
+    s = _schedule(lib, 64, 784, 784, 0, 0)                 # the classifier's DFT as a product: 7 tiles, clusters of 8 along K
+    assert not s["pair"] and s["cluster_ctas"] == 8 and s["ctas"] == 56, s
+    s = _schedule(lib, 2500, 1064, 520, 0, 0)              # ragged M / N / K: pairs cover the last 256-row tile partly
+    assert s["pair"] and s["ctas"] % 2 == 0 and s["ctas"] <= 148, s
+    s = _schedule(lib, 300, 1024, 1024, 0, 0)              # 16 pair tiles cannot fill the device with two pairs each
+    assert not s["pair"] and s["ctas"] >= 96, s
+    s = _schedule(lib, 1024, 2048, 16384, 0, 0)            # K > 4096: chains capped at 64 k-blocks, segment-major
+    assert s["segments"] == 16 and s["run"] == 64 and s["atomics"], s
+    for bad in ((0, 8, 8), (8, 0, 8), (8, 8, 0)):
+        out = (C.c_int * 8)()
+        assert lib.cnb_gemm_schedule(bad[0], bad[1], bad[2], 0, SMS, 0, out) != 0
